@@ -1,0 +1,11 @@
+// libdramakernels: the B200 (sm_100a) replacement for the MoE / dense-GEMV part of the reference's
+// kernel archive. One translation unit; every exported symbol is declared in include/dramakernels.h.
+#include "common.cuh"
+#include "runtime.cuh"
+#include "gemv.cuh"
+#include "router.cuh"
+#include "moe_decode.cuh"
+#include "moe_prefill.cuh"
+
+namespace stack { static cudaError_t configure_all() { return cudaSuccess; } }
+namespace pfmma { static cudaError_t configure_all() { return cudaSuccess; } }

@@ -1,0 +1,204 @@
+"""Host-side orchestration of the MoE path, call for call as the reference's engine issues it.
+
+Decode: `MoeDecoder.record_step` collects one op per launch, chains each weight-streaming op's
+region to the op before it for L2 prefetch (the last wraps to the first), and is captured once
+into a graph that `step` replays — src/engine.rs:136-150 (`Op`), 674-708 (`record_step`),
+946-1042 (router + moe_decode per layer, x == res == y), 1047-1066 (`step`).
+
+Prefill: `moe_prefill` is src/engine.rs:544-604: cuBLAS router logits, dr_moe_topk, shared
+expert through dequant + cuBLAS, count, counts to the host, host exclusive scan, permute,
+grouped expert kernel, combine.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import numpy as np
+
+from . import ffi
+from .gpu import DevBuf, Graph, Stream, check, launched
+from .model import MoeLayer
+
+NULL = C.c_void_p(0)
+ROUTER_PREFETCH = False  # src/engine.rs:18: the router's own expert warm-up is compiled in but off
+GEMV_PREFETCH = True  # src/engine.rs:19
+
+
+@dataclass
+class Op:
+    """One recorded decode launch. `weights` is the region it streams (for the previous op to
+    prefetch); `run` gets the region of the next weight-streaming op to prefetch itself."""
+
+    weights: Optional[tuple[int, int]]
+    run: Callable[[C.c_void_p, int], None]
+
+
+class MoeDecoder:
+    """Batch-1 decode over a stack of MoE layers: x <- x + moe_l(rmsnorm(x)) for each layer."""
+
+    def __init__(self, layers: list[MoeLayer], topk: int = 8, eps: float = 1e-6, st: Stream | None = None) -> None:
+        self.l = ffi.lib()
+        self.st = st or Stream()
+        self.layers = layers
+        self.topk, self.eps = topk, eps
+        h, i, e = layers[0].hidden, layers[0].inter, layers[0].experts
+        self.hidden = h
+        f32 = 4
+        self.x = DevBuf((h) * f32)
+        self.rlog = DevBuf((e + 1) * f32)
+        self.idx = DevBuf(topk * 4)
+        self.wts = DevBuf(topk * f32)
+        self.sgate = DevBuf(f32)
+        self.act = DevBuf((topk + 1) * i * f32)
+        self.counter = DevBuf.zeros(16, self.st)
+        self.graph: Graph | None = None
+
+    def ops(self) -> list[Op]:
+        ops: list[Op] = []
+        l, st = self.l, self.st.raw
+        for layer in self.layers:
+            gq, gs = layer.gate_up.expert(0)
+            dq, ds = layer.down.expert(0)
+            sizes = (layer.gate_up.q_bytes_per_expert, layer.gate_up.sm_bytes_per_expert,
+                     layer.down.q_bytes_per_expert, layer.down.sm_bytes_per_expert)
+
+            def router(pf, pfb, layer=layer, gq=gq, gs=gs, dq=dq, ds=ds, sizes=sizes):
+                launched(
+                    l.dr_router_topk(
+                        layer.router.at(0), self.x.at(0), layer.post_norm.at(0), self.eps, self.rlog.at(0), layer.experts,
+                        self.topk, layer.hidden, self.idx.at(0), self.wts.at(0), self.sgate.at(0), self.counter.at(0),
+                        gq if ROUTER_PREFETCH else NULL, gs, dq, ds, *sizes, st,
+                    ),
+                    "router_topk",
+                )
+
+            ops.append(Op((layer.router.ptr, (layer.experts + 1) * layer.hidden * 2), router))
+            sgq, sgs = layer.shared_gate_up.rows(0)
+            sdq, sds = layer.shared_down.rows(0)
+
+            def decode(pf, pfb, layer=layer, gq=gq, gs=gs, dq=dq, ds=ds, sgq=sgq, sgs=sgs, sdq=sdq, sds=sds):
+                launched(
+                    l.dr_moe_decode(
+                        gq, gs, dq, ds, sgq, sgs, sdq, sds, self.x.at(0), self.idx.at(0), self.wts.at(0), self.sgate.at(0),
+                        self.x.at(0), self.act.at(0), self.x.at(0), layer.hidden, layer.inter, self.topk,
+                        layer.post_norm.at(0), self.eps, pf, pfb, st,
+                    ),
+                    "moe_decode",
+                )
+
+            ops.append(Op(None, decode))
+        return ops
+
+    def record_step(self) -> None:
+        ops = self.ops()
+        first = next((o.weights for o in ops if o.weights), None)
+        for k, op in enumerate(ops):
+            nxt = next((o.weights for o in ops[k + 1:] if o.weights), None) or first
+            if GEMV_PREFETCH and nxt:
+                op.run(C.c_void_p(nxt[0]), nxt[1])
+            else:
+                op.run(NULL, 0)
+
+    def capture(self) -> None:
+        self.graph = Graph(self.st, self.record_step)
+
+    def set_x(self, x: np.ndarray) -> None:
+        self.x.upload(x.astype(np.float32), self.st)
+
+    def step(self) -> np.ndarray:
+        """Replays the captured step on the current x and returns the new hidden state."""
+        assert self.graph is not None, "capture first"
+        self.graph.launch(self.st)
+        return self.x.download(np.float32, self.hidden, self.st)
+
+    def step_eager(self) -> np.ndarray:
+        self.record_step()
+        return self.x.download(np.float32, self.hidden, self.st)
+
+    def routing(self) -> tuple[np.ndarray, np.ndarray, float]:
+        """The last layer's idx, wts and sgate (for tests)."""
+        return (self.idx.download(np.int32, self.topk, self.st), self.wts.download(np.float32, self.topk, self.st),
+                float(self.sgate.download(np.float32, 1, self.st)[0]))
+
+
+class MoePrefill:
+    """The prefill-side MoE block over n <= max_rows rows, with the reference's buffers
+    (src/engine.rs:263-305): x f32, hn_b bf16, rlog, idx/wts/sgate, shared-expert temporaries,
+    counts/offsets/fill/slot_of, xp/ap/yp in expert-sorted order, and one bf16 weight buffer for
+    the dequantised int8 matrices."""
+
+    def __init__(self, layer: MoeLayer, max_rows: int, topk: int = 8, eps: float = 1e-6, st: Stream | None = None) -> None:
+        self.l = ffi.lib()
+        self.st = st or Stream()
+        self.layer, self.topk, self.eps, self.max_rows = layer, topk, eps, max_rows
+        h, i, e = layer.hidden, layer.inter, layer.experts
+        n = max_rows
+        self.blas = C.c_void_p()
+        check(self.l.dr_cublas_create(C.byref(self.blas), self.st.raw), "cublas_create")
+        self.x = DevBuf(n * h * 4)
+        self.hn_b = DevBuf(n * h * 2)
+        self.rlog = DevBuf(n * (e + 1) * 4)
+        self.idx = DevBuf(n * topk * 4)
+        self.wts = DevBuf(n * topk * 4)
+        self.sgate = DevBuf(n * 4)
+        self.shh = DevBuf(n * 2 * i * 4)
+        self.sh_act_b = DevBuf(n * i * 2)
+        self.sh_out = DevBuf(n * h * 4)
+        self.counts = DevBuf(e * 4)
+        self.offsets = DevBuf(e * 4)
+        self.fill = DevBuf(e * 4)
+        self.slot_of = DevBuf(n * topk * 4)
+        self.xp = DevBuf(n * topk * h * 2)
+        self.ap = DevBuf(n * topk * i * 2)
+        self.yp = DevBuf(n * topk * h * 4)
+        self.wbuf = DevBuf(2 * i * h * 2)
+        self.logit_bias: DevBuf | None = None  # tests: [E] f32 added to the router logits (not in the reference)
+
+    def gemm_q8(self, a, w, c, m: int, beta: float) -> None:
+        """C = A . dequant(W)^T + beta C for a q8 weight. src/engine.rs:351-355."""
+        q, s = w.rows(0)
+        launched(self.l.dr_dequant_q8(q, s, self.wbuf.at(0), w.n, w.k, self.st.raw), "dequant_q8")
+        check(self.l.dr_gemm(self.blas, a, self.wbuf.at(0), c, m, w.n, w.k, beta), "gemm")
+
+    def run(self, x: np.ndarray, logit_bias: np.ndarray | None = None) -> np.ndarray:
+        """x [n, H] f32 -> x + moe(rmsnorm(x, post_norm)). src/engine.rs:499-500 and 544-604."""
+        l, st, layer = self.l, self.st.raw, self.layer
+        n, h = x.shape
+        e, topk, i = layer.experts, self.topk, layer.inter
+        assert n <= self.max_rows
+        self.x.upload(x.astype(np.float32), self.st)
+        launched(l.dr_rmsnorm(self.x.at(0), layer.post_norm.at(0), NULL, self.hn_b.at(0), n, h, self.eps, st), "rmsnorm")
+        check(l.dr_gemm(self.blas, self.hn_b.at(0), layer.router.at(0), self.rlog.at(0), n, e + 1, h, 0.0), "gemm")
+        if logit_bias is not None:
+            # Test-only: popularity bias on the logits, applied on the host between the reference's two calls.
+            self.st.sync()
+            lg = self.rlog.download(np.float32, n * (e + 1), self.st).reshape(n, e + 1)
+            lg[:, :e] += logit_bias.astype(np.float32)
+            self.rlog.upload(lg, self.st)
+        launched(l.dr_moe_topk(self.rlog.at(0), n, e, topk, e + 1, self.idx.at(0), self.wts.at(0), self.sgate.at(0), st), "moe_topk")
+        # Shared expert.
+        self.gemm_q8(self.hn_b.at(0), layer.shared_gate_up, self.shh.at(0), n, 0.0)
+        launched(l.dr_swiglu_rows(self.shh.at(0), self.sh_act_b.at(0), n, i, st), "swiglu")
+        self.gemm_q8(self.sh_act_b.at(0), layer.shared_down, self.sh_out.at(0), n, 0.0)
+        # Group (row, k) pairs by expert.
+        self.counts.zero(self.st)
+        launched(l.dr_moe_count(self.idx.at(0), n * topk, self.counts.at(0), st), "moe_count")
+        counts = self.counts.download(np.int32, e, self.st)
+        offsets = (np.cumsum(counts) - counts).astype(np.int32)
+        self.offsets.upload(offsets, self.st)
+        self.fill.zero(self.st)
+        launched(
+            l.dr_moe_permute(self.idx.at(0), n, topk, self.offsets.at(0), self.fill.at(0), self.slot_of.at(0),
+                             self.hn_b.at(0), self.xp.at(0), h, st), "moe_permute")
+        gq, gs = layer.gate_up.expert(0)
+        dq, ds = layer.down.expert(0)
+        launched(
+            l.dr_moe_prefill(gq, gs, dq, ds, self.xp.at(0), self.offsets.at(0), self.counts.at(0), self.ap.at(0),
+                             self.yp.at(0), e, h, i, st), "moe_prefill")
+        launched(
+            l.dr_moe_combine(self.x.at(0), self.yp.at(0), self.slot_of.at(0), self.wts.at(0), self.sgate.at(0),
+                             self.sh_out.at(0), n, topk, h, st), "moe_combine")
+        return self.x.download(np.float32, n * h, self.st).reshape(n, h)

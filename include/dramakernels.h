@@ -1,0 +1,140 @@
+/* C ABI of libdramakernels.so — the sm_100a (B200) implementation of drama-rs's routed-expert MoE
+ * path and the dense weight-streaming GEMVs around it.
+ *
+ * Every function below has the name, argument order and argument meaning of the launcher it
+ * replaces in the reference's kernels/drama.cu, as bound by the reference's src/ffi.rs; each
+ * declaration cites both. A host that links the reference's libdramakernels.a can link this
+ * library for these symbols without source changes.
+ *
+ * Conventions (reference: src/gpu.rs:9-26, kernels/drama.cu:1-8):
+ *   - launchers return 0, -1 for a shape they do not support, or -2 when the per-device setup
+ *     has not run and cannot run now (first call made inside a stream capture without any of
+ *     dr_stream_create / dr_malloc / dr_cublas_create / dr_sample_init / drb_init before it);
+ *   - runtime wrappers return the cudaError_t as int;
+ *   - the stream is the last argument; nothing synchronises, allocates or reads device values
+ *     on the host inside a launcher, so every launcher can be captured in a CUDA graph;
+ *   - all buffers are owned by the caller; weight pointers must be 16-byte aligned.
+ *
+ * Weight formats (reference: src/model.rs:16-43, tools/convert.py:33-41, 92-101):
+ *   Q8: int8 [N, K] row-major + f16 scale [N, K/128];             w = q * scale
+ *   Q4: u8 [E, N, K/2], low nibble = even k, nibble 0..15
+ *       + f16 [E, N, K/64, 2] = (scale, min) per 64 inputs;       w = q * scale + min
+ */
+#ifndef DRAMAKERNELS_H
+#define DRAMAKERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* dr_stream;     /* cudaStream_t */
+typedef void* dr_graph_exec; /* cudaGraphExec_t */
+typedef uint16_t dr_bf16;    /* bfloat16 bit pattern */
+typedef uint16_t dr_half;    /* IEEE binary16 bit pattern */
+
+/* ---- runtime wrappers: kernels/drama.cu:1991-2037, src/ffi.rs:13-30 ------------------------ */
+const char* dr_error_string(int e);                             /* drama.cu:1998, ffi.rs:13 */
+int dr_last_error(void);                                        /* drama.cu:1991, ffi.rs:14 */
+int dr_malloc(void** p, size_t n);                              /* drama.cu:1999, ffi.rs:15 */
+int dr_free(void* p);                                           /* drama.cu:2000, ffi.rs:16 */
+int dr_host_alloc(void** p, size_t n);                          /* drama.cu:2001, ffi.rs:17 */
+int dr_host_free(void* p);                                      /* drama.cu:2002, ffi.rs:18 */
+int dr_h2d(void* d, const void* h, size_t n, dr_stream st);     /* drama.cu:2003, ffi.rs:19 */
+int dr_d2h(void* h, const void* d, size_t n, dr_stream st);     /* drama.cu:2006, ffi.rs:20 */
+int dr_d2d(void* d, const void* s, size_t n, dr_stream st);     /* drama.cu:2009, ffi.rs:21 */
+int dr_memset(void* d, int v, size_t n, dr_stream st);          /* drama.cu:2012, ffi.rs:22 */
+int dr_stream_create(dr_stream* s);                             /* drama.cu:2013, ffi.rs:23 */
+int dr_stream_sync(dr_stream s);                                /* drama.cu:2014, ffi.rs:24 */
+int dr_device_sync(void);                                       /* drama.cu:2015 */
+int dr_mem_info(size_t* free_b, size_t* total_b);               /* drama.cu:2016, ffi.rs:25 */
+int dr_graph_begin(dr_stream s);                                /* drama.cu:2018, ffi.rs:26 */
+int dr_graph_end(dr_stream s, dr_graph_exec* exec);             /* drama.cu:2019, ffi.rs:27 */
+int dr_graph_launch(dr_graph_exec exec, dr_stream s);           /* drama.cu:2027, ffi.rs:28 */
+int dr_graph_destroy(dr_graph_exec exec);                       /* drama.cu:2028, ffi.rs:29 */
+int dr_cublas_create(void** h, dr_stream s);                    /* drama.cu:2030, ffi.rs:30 */
+int dr_sample_init(void);                                       /* ffi.rs:105 (pre-capture hook only) */
+
+/* C[M,N] f32 = A[M,K] bf16 . W[N,K]^T bf16 + beta*C (cuBLAS). drama.cu:2040-2044, ffi.rs:31 */
+int dr_gemm(void* h, const dr_bf16* a, const dr_bf16* w, float* c, int m, int n, int k, float beta);
+
+/* ---- dense GEMVs, batch 1 ----------------------------------------------------------------- */
+
+/* y[n] = W[n] . x' (+ res[n]);  x' = rmsnorm(x, nw, eps) when nw != NULL, else x. y may alias res.
+ * K in {512, 2048, 4096, 6144, 8192}. pf/pf_bytes: a region to prefetch into L2 (the next kernel's
+ * weights), or NULL. drama.cu:222-240, 283-294; ffi.rs:33-36 */
+int dr_gemv_q8(const int8_t* w, const dr_half* s, const float* x, const float* res, float* y, int n, int k,
+               const float* nw, float eps, const char* pf, size_t pf_bytes, dr_stream st);
+
+/* y[j] = silu(W[j] . x') * (W[i + j] . x'), W is [2i, k]. K in {2048, 4096}.
+ * drama.cu:242-261, 296-305; ffi.rs:37-39 */
+int dr_gemv_q8_swiglu(const int8_t* w, const dr_half* s, const float* x, float* y, int i, int k, const float* nw,
+                      float eps, const char* pf, size_t pf_bytes, dr_stream st);
+
+/* y[n] = W[n] . x' for bf16 weights. K == 2048. drama.cu:263-279, 307-315; ffi.rs:40 */
+int dr_gemv_bf16(const dr_bf16* w, const float* x, float* y, int n, int k, const float* nw, float eps,
+                 const char* pf, size_t pf_bytes, dr_stream st);
+
+/* ---- routing ------------------------------------------------------------------------------ */
+
+/* Decode router: logits[0..e] = W[e+1, k] . rmsnorm(x); softmax over the first e, top-k in
+ * descending probability (ties to the lower index), wts renormalised, sgate = logits[e].
+ * counter: one zeroed u32 that is left zero. gu_q != NULL asks for an L2 prefetch of the chosen
+ * experts (sizes in bytes per expert). k == 2048, e <= 256, topk <= 32.
+ * drama.cu:371-461; ffi.rs:56-60 */
+int dr_router_topk(const dr_bf16* w, const float* x, const float* nw, float eps, float* logits, int e, int topk,
+                   int k, int* idx, float* wts, float* sgate, unsigned* counter, const char* gu_q, const char* gu_sm,
+                   const char* d_q, const char* d_sm, size_t gu_q_b, size_t gu_sm_b, size_t d_q_b, size_t d_sm_b,
+                   dr_stream st);
+
+/* Prefill routing over precomputed logits [rows, stride] (column e = shared gate).
+ * drama.cu:322-367, 463-468; ffi.rs:41 */
+int dr_moe_topk(const float* logits, int rows, int e, int topk, int stride, int* idx, float* wts, float* sgate,
+                dr_stream st);
+
+/* ---- MoE decode, batch 1 ------------------------------------------------------------------ */
+
+/* y = res + sigmoid(sgate) * shared(x') + sum_k wts[k] * expert_{idx[k]}(x'), x' = rmsnorm(x, nw, eps).
+ * act: scratch of (topk + 1) * i floats. x, res and y may be the same buffer.
+ * h == 2048, i == 512, topk == 8. drama.cu:470-599; ffi.rs:42-46 */
+int dr_moe_decode(const uint8_t* gu_q, const dr_half* gu_sm, const uint8_t* d_q, const dr_half* d_sm,
+                  const int8_t* sgu_q, const dr_half* sgu_s, const int8_t* sd_q, const dr_half* sd_s, const float* x,
+                  const int* idx, const float* wts, const float* sgate, const float* res, float* act, float* y, int h,
+                  int i, int topk, const float* nw, float eps, const char* pf, size_t pf_bytes, dr_stream st);
+
+/* ---- MoE prefill -------------------------------------------------------------------------- */
+
+int dr_moe_count(const int* idx, int n, int* counts, dr_stream st); /* drama.cu:745-753; ffi.rs:65 */
+/* drama.cu:755-778; ffi.rs:66-69 */
+int dr_moe_permute(const int* idx, int rows, int topk, const int* offsets, int* fill, int* slot_of, const dr_bf16* x,
+                   dr_bf16* xp, int h, dr_stream st);
+/* Rows of xp sorted by expert (offsets/counts). act: scratch, 16 bits per (slot, j), contents
+ * unspecified. y[slot, :] = down_e(silu(gate_e . x) * (up_e . x)). h == 2048, i == 512.
+ * drama.cu:799-968; ffi.rs:61-64 */
+int dr_moe_prefill(const uint8_t* gu_q, const dr_half* gu_sm, const uint8_t* d_q, const dr_half* d_sm,
+                   const dr_bf16* xp, const int* offsets, const int* counts, dr_bf16* act, float* y, int e, int h, int i,
+                   dr_stream st);
+/* drama.cu:780-797; ffi.rs:70-73 */
+int dr_moe_combine(float* x, const float* y, const int* slot_of, const float* wts, const float* sgate,
+                   const float* shared, int rows, int topk, int h, dr_stream st);
+
+/* ---- elementwise helpers of the prefill path ------------------------------------------------ */
+int dr_dequant_q8(const int8_t* w, const dr_half* s, dr_bf16* out, int n, int k, dr_stream st); /* drama.cu:1114-1134; ffi.rs:74 */
+int dr_f32_to_bf16(const float* x, dr_bf16* y, size_t n, dr_stream st);                         /* drama.cu:1158-1166; ffi.rs:75 */
+int dr_swiglu_rows(const float* h, dr_bf16* y, int rows, int i, dr_stream st);                  /* drama.cu:1168-1180; ffi.rs:76 */
+int dr_rmsnorm(const float* x, const float* w, float* y, dr_bf16* yb, int rows, int d, float eps,
+               dr_stream st);                                                                   /* drama.cu:1182-1202; ffi.rs:77 */
+
+/* ---- additions of this library; no counterpart in the reference ----------------------------- */
+int dr_stream_destroy(dr_stream s);
+int dr_cublas_destroy(void* h);
+int drb_init(void);                    /* per-device setup; also run by the pre-capture hooks above */
+int drb_device_error(unsigned* out);   /* reads and clears the bounded-wait error word; synchronises */
+int drb_grid_blocks(void);             /* blocks of the persistent kernels on the current device */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DRAMAKERNELS_H */

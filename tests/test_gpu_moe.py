@@ -1,0 +1,197 @@
+"""Router, MoE decode and MoE prefill through the C ABI against the oracle and the golden vectors."""
+
+import os
+
+import numpy as np
+import pytest
+
+from drama_rs_b200 import ffi, synth
+from drama_rs_b200.engine import MoeDecoder, MoePrefill
+from drama_rs_b200.gpu import DevBuf, Stream, launched
+from drama_rs_b200.model import MoeLayer
+from oracle import moe_oracle as orc
+from tests.helpers import NULL, assert_parity, device_error_word
+
+pytestmark = pytest.mark.gpu
+
+SHAPE = synth.MoeShape()
+
+
+@pytest.fixture(scope="module")
+def st():
+    return Stream()
+
+
+@pytest.fixture(scope="module")
+def layers(st):
+    """Seeded config-0 layers, generated once and kept on the device for the module."""
+    cache = {}
+
+    def get(seed, experts=256):
+        key = (seed, experts)
+        if key not in cache:
+            host = synth.make_layer(seed, synth.MoeShape(experts=experts))
+            cache[key] = (host, MoeLayer.upload(host, st))
+        return cache[key]
+
+    return get
+
+
+def test_moe_topk_rows_and_ties(st):
+    l = ffi.lib()
+    rng = np.random.Generator(np.random.PCG64(3))
+    for e, topk in ((256, 8), (16, 4), (200, 32), (8, 8)):
+        rows = 33
+        logits = rng.standard_normal((rows, e + 1)).astype(np.float32)
+        logits[1, :e] = 0.0  # all tied: lowest indices win, in order
+        logits[2, [3, 9 % e, 5]] = 4.0  # three-way tie at the top
+        d = DevBuf.from_array(logits, st)
+        didx, dw, dsg = DevBuf(rows * topk * 4), DevBuf(rows * topk * 4), DevBuf(rows * 4)
+        launched(l.dr_moe_topk(d.at(0), rows, e, topk, e + 1, didx.at(0), dw.at(0), dsg.at(0), st.raw), "moe_topk")
+        idx = didx.download(np.int32, rows * topk, st).reshape(rows, topk)
+        wts = dw.download(np.float32, rows * topk, st).reshape(rows, topk)
+        sg = dsg.download(np.float32, rows, st)
+        ridx, rwts, rsg = orc.route(logits, e, topk)
+        assert np.array_equal(idx, ridx), (e, topk)
+        assert idx[1].tolist() == list(range(topk))
+        assert np.abs(wts - rwts).max() <= 2e-6
+        assert np.array_equal(sg, rsg)
+    assert l.dr_moe_topk(d.at(0), 1, 300, 8, 301, didx.at(0), dw.at(0), dsg.at(0), st.raw) == -1
+
+
+@pytest.mark.parametrize("seed,experts,topk", [(0, 256, 8), (1, 256, 8), (3, 16, 8), (3, 16, 3)])
+def test_router_topk(st, layers, golden_dir, seed, experts, topk):
+    l = ffi.lib()
+    host, dev = layers(seed, experts)
+    x = synth.make_x(seed, 1, 2048)[0]
+    dx = DevBuf.from_array(x, st)
+    dlog, didx, dw, dsg = DevBuf((experts + 1) * 4), DevBuf(topk * 4), DevBuf(topk * 4), DevBuf(4)
+    counter = DevBuf.zeros(16, st)
+    for rep in range(3):  # the counter must come back to zero so that the call can be repeated
+        launched(
+            l.dr_router_topk(dev.router.at(0), dx.at(0), dev.post_norm.at(0), 1e-6, dlog.at(0), experts, topk, 2048,
+                             didx.at(0), dw.at(0), dsg.at(0), counter.at(0), NULL, NULL, NULL, NULL, 0, 0, 0, 0, st.raw),
+            "router_topk")
+        st.sync()
+        assert counter.download(np.uint32, 4, st).tolist() == [0, 0, 0, 0]
+    logits = dlog.download(np.float32, experts + 1, st)
+    idx, wts, sg = didx.download(np.int32, topk, st), dw.download(np.float32, topk, st), dsg.download(np.float32, 1, st)
+    xh = orc.rmsnorm(x[None], host["post_norm"], 1e-6, np.float64)
+    ref_logits = orc.router_logits(host, xh, np.float64)
+    ridx, rwts, rsg = orc.route(ref_logits, experts, topk, np.float64)
+    assert np.abs(logits - ref_logits[0]).max() <= 2e-5
+    assert np.array_equal(idx, ridx[0])
+    assert np.abs(wts - rwts[0]).max() <= 2e-5
+    assert abs(float(sg[0]) - float(rsg[0])) <= 2e-5
+    if experts == 256 and topk == 8 and seed in (0, 1):
+        g = np.load(os.path.join(golden_dir, f"moe_decode_seed{seed}.npz"))
+        assert np.array_equal(idx, g["idx"][0])  # the reference's own PyTorch routing
+    assert device_error_word() == 0
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_moe_decode_layer_golden(st, layers, golden_dir, seed):
+    """One config-0 layer, x == res == y, eager and as a replayed graph."""
+    g = np.load(os.path.join(golden_dir, f"moe_decode_seed{seed}.npz"))
+    host, dev = layers(seed)
+    x = synth.make_x(seed, 1, 2048)[0]
+    ref = x.astype(np.float64) + g["out_hf64"][0]
+    dec = MoeDecoder([dev], st=st)
+    dec.set_x(x)
+    y = dec.step_eager()
+    idx, wts, sg = dec.routing()
+    assert np.array_equal(idx, g["idx"][0])
+    assert np.abs(wts - g["wts"][0]).max() <= 2e-5
+    a, r = assert_parity(y, ref, f"decode seed {seed} eager")
+    # the reference's own fp32 result is not closer to fp64 than this by more than its own noise
+    floor = np.abs(g["out_hf"][0].astype(np.float64) - g["out_hf64"][0]).max()
+    print(f"seed {seed}: max-abs {a:.3e} rel-L2 {r:.3e}; reference fp32 noise floor {floor:.3e}")
+    dec.capture()
+    for _ in range(3):
+        dec.set_x(x)
+        y2 = dec.step()
+        assert np.array_equal(y2, y), "graph replay differs from the eager launch"
+    assert device_error_word() == 0
+
+
+def test_moe_decode_routed_part_alone(st, layers):
+    """With the shared expert gated off and no residual the routed int4 experts are all that is left."""
+    l = ffi.lib()
+    host, dev = layers(1)
+    x = synth.make_x(11, 1, 2048)[0]
+    xh = orc.rmsnorm(x[None], host["post_norm"], 1e-6, np.float64)
+    idx = np.array([5, 250, 17, 0, 255, 128, 64, 33], dtype=np.int32)
+    wts = np.array([0.3, 0.2, 0.15, 0.1, 0.1, 0.05, 0.05, 0.05], dtype=np.float32)
+    ref = np.zeros(2048)
+    for k in range(8):
+        ref += wts[k] * orc.expert_forward(host, int(idx[k]), xh, np.float64)[0]
+    dx, didx, dw = DevBuf.from_array(x, st), DevBuf.from_array(idx, st), DevBuf.from_array(wts, st)
+    dsg = DevBuf.from_array(np.array([-1e4], np.float32), st)  # sigmoid -> 0
+    dres, dact, dy = DevBuf.zeros(2048 * 4, st), DevBuf(9 * 512 * 4), DevBuf(2048 * 4)
+    gq, gs = dev.gate_up.expert(0)
+    dq, ds = dev.down.expert(0)
+    sgq, sgs = dev.shared_gate_up.rows(0)
+    sdq, sds = dev.shared_down.rows(0)
+    launched(
+        l.dr_moe_decode(gq, gs, dq, ds, sgq, sgs, sdq, sds, dx.at(0), didx.at(0), dw.at(0), dsg.at(0), dres.at(0), dact.at(0),
+                        dy.at(0), 2048, 512, 8, dev.post_norm.at(0), 1e-6, NULL, 0, st.raw), "moe_decode")
+    y = dy.download(np.float32, 2048, st)
+    a, r = assert_parity(y, ref, "routed experts alone", max_abs=1e-4, rel_l2=1e-5)
+    assert l.dr_moe_decode(gq, gs, dq, ds, sgq, sgs, sdq, sds, dx.at(0), didx.at(0), dw.at(0), dsg.at(0), dres.at(0),
+                           dact.at(0), dy.at(0), 2048, 256, 8, dev.post_norm.at(0), 1e-6, NULL, 0, st.raw) == -1
+
+
+def test_moe_decode_stack_of_layers(st, layers):
+    """Three layers carried x -> x + moe(rmsnorm(x)) in one graph, against the fp64 oracle."""
+    pairs = [layers(s) for s in (0, 1, 0)]
+    x = synth.make_x(21, 1, 2048)[0]
+    ref = x.astype(np.float64)[None]
+    for host, _ in pairs:
+        ref = orc.moe_layer(host, ref, 8, 1e-6, np.float64)[0]
+    dec = MoeDecoder([d for _, d in pairs], st=st)
+    dec.capture()
+    dec.set_x(x)
+    y = dec.step()
+    scale = np.abs(ref).max()
+    a, r = assert_parity(y, ref[0], "3-layer stack", max_abs=max(1e-2, 4e-6 * scale))
+    assert device_error_word() == 0
+
+
+def test_moe_prefill_golden_rows40(st, layers, golden_dir):
+    g = np.load(os.path.join(golden_dir, "moe_rows40_seed2.npz"))
+    host, dev = layers(2)
+    x = synth.make_x(2, 40, 2048)
+    pre = MoePrefill(dev, 64, st=st)
+    y = pre.run(x)
+    idx = pre.idx.download(np.int32, 40 * 8, st).reshape(40, 8)
+    assert np.array_equal(idx, g["idx"])
+    ref = x.astype(np.float64) + g["out_hf64"]
+    # The prefill path feeds bf16 activations to the experts (the ABI carries bf16 rows), so the comparison
+    # with the fp32-activation reference is in relative L2; max-abs scales with the output magnitude.
+    a, r = assert_parity(y, ref, "prefill 40 rows", max_abs=np.inf, rel_l2=3e-3)
+    # Against the oracle fed the same bf16-rounded normalised rows the agreement is tight.
+    xh = orc.round_bf16(orc.rmsnorm(x, host["post_norm"], 1e-6))
+    out = orc.moe_block(host, xh.astype(np.float64), 8, np.float64)[0]
+    assert_parity(y - x, out, "prefill 40 rows vs bf16-input oracle", max_abs=np.inf, rel_l2=REL_PREFILL)
+    assert device_error_word() == 0
+
+
+REL_PREFILL = 2.5e-3  # the shared expert runs through bf16 weights and a bf16 intermediate, as in the reference
+
+
+def test_moe_prefill_zipf_300(st, layers):
+    host, dev = layers(2)
+    x = synth.make_x(33, 300, 2048)
+    bias = synth.zipf_router_bias(33, 256, 1.1, 1.0)
+    pre = MoePrefill(dev, 300, st=st)
+    y = pre.run(x, logit_bias=bias)
+    xh = orc.round_bf16(orc.rmsnorm(x, host["post_norm"], 1e-6))
+    out, idx, wts, sgate, logits = orc.moe_block(host, xh.astype(np.float64), 8, np.float64, logit_bias=bias)
+    got_idx = pre.idx.download(np.int32, 300 * 8, st).reshape(300, 8)
+    margin = orc.route_margin(logits, 256, 8)
+    safe = margin > 1e-6
+    assert np.array_equal(got_idx[safe], idx[safe]) and safe.mean() > 0.99
+    counts = pre.counts.download(np.int32, 256, st)
+    assert counts.sum() == 2400 and np.array_equal(counts, orc.moe_count(got_idx, 256))
+    assert_parity((y - x)[safe], out[safe], "prefill zipf 300", max_abs=np.inf, rel_l2=REL_PREFILL)
+    assert device_error_word() == 0
