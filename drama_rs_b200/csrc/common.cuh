@@ -20,6 +20,31 @@
 // The library is one translation unit, so the definition lives here.
 __device__ unsigned int g_drb_error = 0;
 
+// Optional timing probes for development builds (-DDRB_TRACE): block 0 records the global timer at
+// numbered points of a kernel into g_drb_trace. Compiled out of the product build.
+#ifdef DRB_TRACE
+__device__ unsigned long long g_drb_trace[64];
+#define DRB_TRACE_POINT(i, tid)                                                   \
+  do {                                                                            \
+    if (blockIdx.x == 0 && threadIdx.x == (tid)) {                                \
+      unsigned long long t_;                                                      \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                      \
+      g_drb_trace[(i)] = t_;                                                      \
+    }                                                                             \
+  } while (0)
+#define DRB_TRACE_ANY(i, tid)                                                     \
+  do {                                                                            \
+    if (threadIdx.x == (tid)) {                                                   \
+      unsigned long long t_;                                                      \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                      \
+      g_drb_trace[(i)] = t_;                                                      \
+    }                                                                             \
+  } while (0)
+#else
+#define DRB_TRACE_POINT(i, tid) ((void)0)
+#define DRB_TRACE_ANY(i, tid) ((void)0)
+#endif
+
 enum DrbError : unsigned int {
   DRB_OK = 0,
   DRB_ERR_FULL_WAIT = 1,   // a consumer gave up waiting for a bulk copy to land
@@ -47,6 +72,11 @@ DRB_DEV float silu_f(float x) { return x / (1.f + expf(-x)); }
 DRB_DEV float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 
 DRB_DEV uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Activation vectors are staged in shared memory as float4s at a swizzled index: thread t writes
+// float4 t (coalesced global read), and a lane later reads the 4..8 consecutive float4s of its own
+// k-slice. The XOR keeps both patterns free of bank conflicts for slices of 4, 8 or 16 floats... per lane.
+DRB_DEV int swz4(int g) { return g ^ ((g >> 3) & 7); }
 
 // ------------------------------------------------------------------------------------------
 // programmatic dependent launch
@@ -242,6 +272,193 @@ DRB_DEV unsigned long long dot8_bf16(const uint4& v, const unsigned long long* x
   acc = fma2(pack2(__uint_as_float(v.z << 16), __uint_as_float(v.z & 0xffff0000u)), xp[2], acc);
   acc = fma2(pack2(__uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u)), xp[3], acc);
   return acc;
+}
+
+// ------------------------------------------------------------------------------------------
+// Integer dot products (dp4a). A lane's slice of the activation vector is re-expressed once per
+// kernel as block fixed point: x_k = delta * n_k with |n_k| <= 2^20 and delta = max|x| * 2^-20 over
+// the slice, n_k split into three signed limbs n = l0 + 128 l1 + 16384 l2 (l0, l1 in [-64, 63]).
+// A weight word then costs one dp4a per limb, four multiply-adds each, accumulated exactly in
+// int32; the three sums are recombined in integer and converted to fp32 once per 16-byte chunk.
+// Quantisation error of an activation is at most delta / 2 = 2^-21 of the slice's largest value
+// (fp32 itself carries 2^-24 of each value), and nothing is rounded during accumulation.
+
+DRB_DEV int dp4a_us(uint32_t a_u8x4, uint32_t b_s8x4, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_u8x4), "r"(b_s8x4), "r"(c));
+  return d;
+}
+DRB_DEV int dp4a_ss(uint32_t a_s8x4, uint32_t b_s8x4, int c) {
+  int d;
+  asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_s8x4), "r"(b_s8x4), "r"(c));
+  return d;
+}
+
+// Splits n (|n| <= 2^20 + a little) into its three limbs.
+DRB_DEV void limbs3(int n, int& l0, int& l1, int& l2) {
+  l0 = ((n + 64) & 127) - 64;
+  const int n1 = (n - l0) >> 7;
+  l1 = ((n1 + 64) & 127) - 64;
+  l2 = (n1 - l1) >> 7;
+}
+
+// N consecutive activations held by one lane, as limbs packed four to a word.
+//   NATURAL order: word i of limb j holds k = 4i .. 4i+3                     (int8 weight words)
+//   EVEN/ODD order (EO): word i holds k = 8(i/2) + {0,2,4,6} for even i and {1,3,5,7} for odd i,
+//   which is how the low and the high nibbles of an int4 weight word line up.
+template <int N, bool EO>
+struct QAct {
+  uint32_t l[3][N / 4];
+  float delta;
+  DRB_DEV void quantize(const float* x) {
+    float m = 0.f;
+#pragma unroll
+    for (int k = 0; k < N; ++k) m = fmaxf(m, fabsf(x[k]));
+    delta = m > 0.f ? m * (1.f / 1048576.f) : 1.f;
+    const float inv = 1.f / delta;
+#pragma unroll
+    for (int j = 0; j < 3; ++j)
+#pragma unroll
+      for (int i = 0; i < N / 4; ++i) l[j][i] = 0u;
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+      int l0, l1, l2;
+      limbs3(__float2int_rn(x[k] * inv), l0, l1, l2);
+      const int word = EO ? 2 * (k / 8) + (k & 1) : k / 4;
+      const int byte = EO ? (k & 7) >> 1 : k & 3;
+      l[0][word] |= (uint32_t)(l0 & 0xff) << (8 * byte);
+      l[1][word] |= (uint32_t)(l1 & 0xff) << (8 * byte);
+      l[2][word] |= (uint32_t)(l2 & 0xff) << (8 * byte);
+    }
+  }
+};
+
+// Cooperative quantisation: instead of every lane converting its own slice (hundreds of
+// instructions, repeated by every warp that owns the same slice), each thread converts the float4
+// it loaded, the threads of one block of 16 or 32 values agree on max|x| with shuffles, and the
+// packed limb words go to shared memory, from where the owning lanes pick them up with a few
+// 128-bit loads. Must be called by whole warps (it shuffles); threads with nothing to convert pass
+// valid = false. g4 is the float4's index in the vector: consecutive lanes hold consecutive g4.
+//
+// Even/odd packing, 32 values per block, 112 bytes per block: 3 limbs x 8 words, delta, sum(x), pad
+// (the 112-byte stride keeps the lanes' 128-bit reads on distinct banks).
+constexpr int QB32_BYTES = 112;
+DRB_DEV void quant_store_eo(unsigned char* blocks, int g4, float4 v, bool valid) {
+  float m = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+  float sum = (v.x + v.y) + (v.z + v.w);
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) {
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  }
+  if (!valid) return;
+  const float delta = m > 0.f ? m * (1.f / 1048576.f) : 1.f;
+  const float inv = 1.f / delta;
+  int l[4][3];
+  limbs3(__float2int_rn(v.x * inv), l[0][0], l[0][1], l[0][2]);
+  limbs3(__float2int_rn(v.y * inv), l[1][0], l[1][1], l[1][2]);
+  limbs3(__float2int_rn(v.z * inv), l[2][0], l[2][1], l[2][2]);
+  limbs3(__float2int_rn(v.w * inv), l[3][0], l[3][1], l[3][2]);
+  unsigned char* blk = blocks + (size_t)(g4 >> 3) * QB32_BYTES;
+  const int sub = g4 & 1, w = 2 * ((g4 & 7) >> 1);
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    *reinterpret_cast<uint16_t*>(blk + (j * 8 + w) * 4 + 2 * sub) = (uint16_t)((l[0][j] & 0xff) | ((l[2][j] & 0xff) << 8));
+    *reinterpret_cast<uint16_t*>(blk + (j * 8 + w + 1) * 4 + 2 * sub) = (uint16_t)((l[1][j] & 0xff) | ((l[3][j] & 0xff) << 8));
+  }
+  if ((g4 & 7) == 0) {
+    *reinterpret_cast<float*>(blk + 96) = delta;
+    *reinterpret_cast<float*>(blk + 100) = sum;
+  }
+}
+
+// Natural packing, 16 values per block, 64 bytes per block: 3 limbs x 4 words, delta, pad.
+constexpr int QB16_BYTES = 64;
+DRB_DEV void quant_store_nat(unsigned char* blocks, int g4, float4 v, bool valid) {
+  float m = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+  if (!valid) return;
+  const float delta = m > 0.f ? m * (1.f / 1048576.f) : 1.f;
+  const float inv = 1.f / delta;
+  int l[4][3];
+  limbs3(__float2int_rn(v.x * inv), l[0][0], l[0][1], l[0][2]);
+  limbs3(__float2int_rn(v.y * inv), l[1][0], l[1][1], l[1][2]);
+  limbs3(__float2int_rn(v.z * inv), l[2][0], l[2][1], l[2][2]);
+  limbs3(__float2int_rn(v.w * inv), l[3][0], l[3][1], l[3][2]);
+  unsigned char* blk = blocks + (size_t)(g4 >> 2) * QB16_BYTES;
+#pragma unroll
+  for (int j = 0; j < 3; ++j)
+    *reinterpret_cast<uint32_t*>(blk + (j * 4 + (g4 & 3)) * 4) =
+        (uint32_t)(l[0][j] & 0xff) | ((uint32_t)(l[1][j] & 0xff) << 8) | ((uint32_t)(l[2][j] & 0xff) << 16) | ((uint32_t)(l[3][j] & 0xff) << 24);
+  if ((g4 & 3) == 0) *reinterpret_cast<float*>(blk + 48) = delta;
+}
+
+DRB_DEV void qact_load(QAct<32, true>& a, float& sum, const unsigned char* blk) {
+#pragma unroll
+  for (int i = 0; i < 6; ++i) {
+    const uint4 v = reinterpret_cast<const uint4*>(blk)[i];
+    a.l[i / 2][(i & 1) * 4 + 0] = v.x, a.l[i / 2][(i & 1) * 4 + 1] = v.y, a.l[i / 2][(i & 1) * 4 + 2] = v.z, a.l[i / 2][(i & 1) * 4 + 3] = v.w;
+  }
+  a.delta = *reinterpret_cast<const float*>(blk + 96);
+  sum = *reinterpret_cast<const float*>(blk + 100);
+}
+
+DRB_DEV void qact_load(QAct<16, false>& a, const unsigned char* blk) {
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    const uint4 v = reinterpret_cast<const uint4*>(blk)[j];
+    a.l[j][0] = v.x, a.l[j][1] = v.y, a.l[j][2] = v.z, a.l[j][3] = v.w;
+  }
+  a.delta = *reinterpret_cast<const float*>(blk + 48);
+}
+
+DRB_DEV float recombine(int a0, int a1, int a2) { return (float)(a0 + (a1 << 7) + (a2 << 14)); }
+
+// sum_k q_k n_k over one 16-byte chunk of int4 weights (32 nibbles, k ascending) against words
+// [w0, w0 + 8) of an even/odd-ordered slice. Multiply by delta (and the group scale) afterwards.
+template <int N>
+DRB_DEV float dot32_q4_i(const uint4& v, const QAct<N, true>& a, int w0) {
+  int a0 = 0, a1 = 0, a2 = 0;
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t lo = w[i] & 0x0F0F0F0Fu, hi = (w[i] >> 4) & 0x0F0F0F0Fu;
+    a0 = dp4a_us(lo, a.l[0][w0 + 2 * i], a0), a0 = dp4a_us(hi, a.l[0][w0 + 2 * i + 1], a0);
+    a1 = dp4a_us(lo, a.l[1][w0 + 2 * i], a1), a1 = dp4a_us(hi, a.l[1][w0 + 2 * i + 1], a1);
+    a2 = dp4a_us(lo, a.l[2][w0 + 2 * i], a2), a2 = dp4a_us(hi, a.l[2][w0 + 2 * i + 1], a2);
+  }
+  return recombine(a0, a1, a2);
+}
+
+// sum_k w_k n_k over one 16-byte chunk of int8 weights against words [w0, w0 + 4) of a natural-ordered slice.
+template <int N>
+DRB_DEV float dot16_q8_i(const uint4& v, const QAct<N, false>& a, int w0) {
+  int a0 = 0, a1 = 0, a2 = 0;
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    a0 = dp4a_ss(w[i], a.l[0][w0 + i], a0);
+    a1 = dp4a_ss(w[i], a.l[1][w0 + i], a1);
+    a2 = dp4a_ss(w[i], a.l[2][w0 + i], a2);
+  }
+  return recombine(a0, a1, a2);
+}
+
+// The same for an even/odd-ordered slice: two weight words are first regrouped into their even and odd bytes.
+// Covers two 16-byte chunks (32 int8, k ascending) against words [w0, w0 + 8).
+template <int N>
+DRB_DEV float dot32_q8_eo(const uint4& v0, const uint4& v1, const QAct<N, true>& a, int w0) {
+  int a0 = 0, a1 = 0, a2 = 0;
+  const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t ev = prmt(w[2 * i], w[2 * i + 1], 0x6420u), od = prmt(w[2 * i], w[2 * i + 1], 0x7531u);
+    a0 = dp4a_ss(ev, a.l[0][w0 + 2 * i], a0), a0 = dp4a_ss(od, a.l[0][w0 + 2 * i + 1], a0);
+    a1 = dp4a_ss(ev, a.l[1][w0 + 2 * i], a1), a1 = dp4a_ss(od, a.l[1][w0 + 2 * i + 1], a1);
+    a2 = dp4a_ss(ev, a.l[2][w0 + 2 * i], a2), a2 = dp4a_ss(od, a.l[2][w0 + 2 * i + 1], a2);
+  }
+  return recombine(a0, a1, a2);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -44,14 +44,18 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
   constexpr int RG = CW / NSEG;                              // rows in flight per pass
   constexpr int RB = RG * RPW;                               // outputs per stage
   constexpr int ROW_BYTES = K * ESZ;
-  constexpr int STAGE_BYTES = RB * U * ROW_BYTES;
+  constexpr int SROW = MODE == BF16_PLAIN ? 0 : (K / 128) * 2;  // bytes of group scales per weight row
+  constexpr bool S_IN_STAGE = SROW >= 16;                     // bulk copies need 16-byte granules
+  constexpr int STAGE_BYTES = RB * U * (ROW_BYTES + (S_IN_STAGE ? SROW : 0));
   constexpr int STAGES = RING_BYTES / STAGE_BYTES < MAX_STAGES ? RING_BYTES / STAGE_BYTES : MAX_STAGES;
+  constexpr int NT = CW * 32;
   static_assert(STAGES >= 2, "ring too small");
   static_assert(NCH >= 1, "segment too small");
 
   extern __shared__ __align__(128) unsigned char dyn[];
   Smem& sm = *reinterpret_cast<Smem*>(dyn);
-  unsigned char* ring = dyn + 1024;
+  float4* xs4 = reinterpret_cast<float4*>(dyn + 1024);
+  unsigned char* ring = dyn + 1024 + K * 4;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned G = gridDim.x, b = blockIdx.x;
@@ -78,9 +82,15 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
         const int r0 = u0 + c * RB;
         const int nr = min(RB, u1 - r0);
         unsigned char* dst = ring + (size_t)s * STAGE_BYTES;
-        mbar_expect_tx(&sm.full[s], (unsigned)(nr * U * ROW_BYTES));
+        mbar_expect_tx(&sm.full[s], (unsigned)(nr * U * (ROW_BYTES + (S_IN_STAGE ? SROW : 0))));
         bulk_g2s(dst, W + (size_t)r0 * ROW_BYTES, (unsigned)(nr * ROW_BYTES), &sm.full[s]);
         if (U == 2) bulk_g2s(dst + RB * ROW_BYTES, W + ((size_t)N + r0) * ROW_BYTES, (unsigned)(nr * ROW_BYTES), &sm.full[s]);
+        if (S_IN_STAGE) {
+          const unsigned char* sp = reinterpret_cast<const unsigned char*>(S);
+          unsigned char* sd = dst + U * RB * ROW_BYTES;
+          bulk_g2s(sd, sp + (size_t)r0 * SROW, (unsigned)(nr * SROW), &sm.full[s]);
+          if (U == 2) bulk_g2s(sd + RB * SROW, sp + ((size_t)N + r0) * SROW, (unsigned)(nr * SROW), &sm.full[s]);
+        }
       }
       prefetch_share(pf, pf_bytes, b, G);
     }
@@ -94,35 +104,46 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
   if (nw) {
     float ss = 0.f;
     const float4* x4 = reinterpret_cast<const float4*>(x);
-    for (int i = threadIdx.x; i < K / 4; i += CW * 32) {
+    for (int i = threadIdx.x; i < K / 4; i += NT) {
       const float4 v = x4[i];
       ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
     ss = warp_sum(ss);
     if (lane == 0) sm.red[32 + warp] = ss;
-    consumer_sync(CW * 32);
-    if (threadIdx.x == 0) {
-      float t = 0.f;
-      for (int w = 0; w < CW; ++w) t += sm.red[32 + w];
-      sm.inv_rms = rsqrtf(t / K + eps);
-    }
-    consumer_sync(CW * 32);
-    inv = sm.inv_rms;
+    consumer_sync(NT);
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < CW; ++w) t += sm.red[32 + w];
+    inv = rsqrtf(t / K + eps);
   }
-  // This lane's activations: chunk c = lane + 32*i of the segment covers k = seg*KSEG + EPC*c ...
-  unsigned long long xp[NCH * EPC / 2];
+  // Stage the (normalised) activations once per block: coalesced read, then either a swizzled float4 store
+  // (bf16 weights keep fp32 activations) or conversion to limb blocks of 16 values (int8 weights, dp4a).
+  // Chunk c = lane + 32*i of the segment covers k = seg*KSEG + EPC*c ...; whole warps enter or skip the loop.
+  unsigned char* qb = reinterpret_cast<unsigned char*>(xs4);
+  for (int i = threadIdx.x; i < K / 4; i += NT) {
+    float4 v = reinterpret_cast<const float4*>(x)[i];
+    if (nw) {
+      const float4 w = reinterpret_cast<const float4*>(nw)[i];
+      v = make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w);
+    }
+    if (MODE == BF16_PLAIN) xs4[swz4(i)] = v;
+    else quant_store_nat(qb, i, v, true);
+  }
+  consumer_sync(NT);
+  unsigned long long xp[MODE == BF16_PLAIN ? NCH * EPC / 2 : 1];
+  QAct<16, false> xq[MODE == BF16_PLAIN ? 1 : NCH];
 #pragma unroll
   for (int i = 0; i < NCH; ++i) {
-    const int k0 = seg * KSEG + EPC * (lane + 32 * i);
+    if (MODE == BF16_PLAIN) {
+      const int g0 = (seg * KSEG + EPC * (lane + 32 * i)) / 4;
 #pragma unroll
-    for (int e = 0; e < EPC / 4; ++e) {
-      float4 v = *reinterpret_cast<const float4*>(x + k0 + 4 * e);
-      if (nw) {
-        const float4 w = *reinterpret_cast<const float4*>(nw + k0 + 4 * e);
-        v = make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w);
+      for (int e = 0; e < EPC / 4; ++e) {
+        const float4 v = xs4[swz4(g0 + e)];
+        xp[i * (EPC / 2) + 2 * e] = pack2(v.x, v.y);
+        xp[i * (EPC / 2) + 2 * e + 1] = pack2(v.z, v.w);
       }
-      xp[i * (EPC / 2) + 2 * e] = pack2(v.x, v.y);
-      xp[i * (EPC / 2) + 2 * e + 1] = pack2(v.z, v.w);
+    } else {
+      qact_load(xq[i], qb + (size_t)(seg * (KSEG / 16) + lane + 32 * i) * QB16_BYTES);
     }
   }
 
@@ -142,11 +163,23 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
 #pragma unroll
           for (int i = 0; i < NCH; ++i) {
             const size_t row = (size_t)(u ? N : 0) + r0 + lr;
-            sc[p][u][i] = lr < nr ? __half2float(__ldg(S + row * (K / 128) + (seg * KSEG + 16 * (lane + 32 * i)) / 128)) : 0.f;
+            sc[p][u][i] = (!S_IN_STAGE && lr < nr) ? __half2float(__ldg(S + row * (K / 128) + (seg * KSEG + 16 * (lane + 32 * i)) / 128)) : 0.f;
           }
       }
     }
     mbar_wait(&sm.full[s], (c / STAGES) & 1, DRB_ERR_FULL_WAIT);
+    if (MODE != BF16_PLAIN && S_IN_STAGE) {
+      const __half* ss = reinterpret_cast<const __half*>(st + U * RB * ROW_BYTES);
+#pragma unroll
+      for (int p = 0; p < RPW; ++p) {
+        const int lr = p * RG + rg;
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+          for (int i = 0; i < NCH; ++i)
+            sc[p][u][i] = lr < nr ? __half2float(ss[(u * RB + lr) * (K / 128) + (seg * KSEG + 16 * (lane + 32 * i)) / 128]) : 0.f;
+      }
+    }
 #pragma unroll
     for (int p = 0; p < RPW; ++p) {
       const int lr = p * RG + rg;
@@ -170,7 +203,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
           } else {
 #pragma unroll
             for (int i = 0; i < NCH; ++i)
-              d[u] += sc[p][u][i] * dot16_q8(*reinterpret_cast<const uint4*>(rowp + 16 * (lane + 32 * i)), xp + i * 8);
+              d[u] += sc[p][u][i] * xq[i].delta * dot16_q8_i(*reinterpret_cast<const uint4*>(rowp + 16 * (lane + 32 * i)), xq[i], 0);
           }
         }
         d[u] = warp_sum(d[u]);
@@ -207,11 +240,13 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
 
 template <int KSEG, int NSEG, int RPW, int CW, int MODE>
 constexpr size_t smem_bytes() {
+  constexpr int K = KSEG * NSEG;
   constexpr int ESZ = MODE == BF16_PLAIN ? 2 : 1;
   constexpr int U = MODE == Q8_SWIGLU ? 2 : 1;
-  constexpr int STAGE = (CW / NSEG) * RPW * U * KSEG * NSEG * ESZ;
+  constexpr int SROW = MODE == BF16_PLAIN ? 0 : (K / 128) * 2;
+  constexpr int STAGE = (CW / NSEG) * RPW * U * (K * ESZ + (SROW >= 16 ? SROW : 0));
   constexpr int STAGES = RING_BYTES / STAGE < MAX_STAGES ? RING_BYTES / STAGE : MAX_STAGES;
-  return 1024 + (size_t)STAGES * STAGE;
+  return 1024 + (size_t)K * 4 + (size_t)STAGES * STAGE;
 }
 
 template <int KSEG, int NSEG, int RPW, int CW, int MODE>
@@ -229,8 +264,10 @@ int launch(const void* W, const __half* S, const float* x, const float* res, flo
 
 template <int KSEG, int NSEG, int RPW, int CW, int MODE>
 cudaError_t configure() {
-  return cudaFuncSetAttribute(k_gemv<KSEG, NSEG, RPW, CW, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              (int)smem_bytes<KSEG, NSEG, RPW, CW, MODE>());
+  cudaError_t e = cudaFuncSetAttribute(k_gemv<KSEG, NSEG, RPW, CW, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem_bytes<KSEG, NSEG, RPW, CW, MODE>());
+  if (e != cudaSuccess) return e;
+  return drb_carveout(k_gemv<KSEG, NSEG, RPW, CW, MODE>);
 }
 
 static cudaError_t configure_all() {

@@ -232,6 +232,19 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+static cudaError_t configure_all() {
+  cudaError_t e;
+  if ((e = drb_carveout(k_count)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_permute)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_combine)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_pf_gate_up)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_pf_down)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_dequant_q8)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_f32_to_bf16)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_swiglu_rows)) != cudaSuccess) return e;
+  return drb_carveout(k_rmsnorm);
+}
+
 }  // namespace pf
 
 // Reference: kernels/drama.cu:750-753; src/ffi.rs:65. counts must be zeroed by the caller.

@@ -23,7 +23,7 @@ DRB_DEV bool before(float pa, int ia, float pb, int ib) { return pa > pb || (pa 
 
 struct TopkSmem {
   float red[32];
-  float cp[8 * MAX_TOPK];
+  unsigned ck[8 * MAX_TOPK];
   int ci[8 * MAX_TOPK];
   float top[MAX_TOPK];
   int ncand[8];
@@ -50,47 +50,51 @@ DRB_DEV float block_max_256(float v, float* red) {
 }
 
 // Softmax + top-k of one row of logits by a 256-thread block. Thread e holds logit e (or -inf).
+//
+// Selection in two levels. Every warp extracts the best min(topk, 32) of its 32 probabilities by
+// repeated warp arg-max (the lowest lane among equal values wins, and lane order is index order).
+// Warp 0 then merges the eight sorted lists: lane w holds the head of warp w's list, and among
+// equal heads the lowest lane again holds the lowest expert index.
 DRB_DEV void softmax_topk(float v, int E, int topk, int* __restrict__ idx, float* __restrict__ wts, TopkSmem& sm) {
   const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
   const float m = block_max_256(v, sm.red);
   const float ex = e < E ? expf(v - m) : 0.f;
   const float z = block_sum_256(ex, sm.red);
   const float p = e < E ? ex / z : -1.f;
-  // Rank inside the warp.
-  int r = 0;
-#pragma unroll
-  for (int o = 1; o < 32; ++o) {
-    const int src = (lane + o) & 31;
-    const float po = __shfl_sync(0xffffffffu, p, src);
-    r += before(po, (warp << 5) + src, p, e) ? 1 : 0;
-  }
-  const bool keep = r < topk && e < E;
-  if (keep) {
-    sm.cp[warp * MAX_TOPK + r] = p;
-    sm.ci[warp * MAX_TOPK + r] = e;
-  }
-  const unsigned kept = __ballot_sync(0xffffffffu, keep);
-  if (lane == 0) sm.ncand[warp] = __popc(kept);
-  __syncthreads();
-  // Rank of every survivor among all survivors.
-  if (keep) {
-    int g = r;  // the entries of its own warp that rank before it
-    for (int w = 0; w < 8; ++w) {
-      if (w == warp) continue;
-      const int n = sm.ncand[w];
-      for (int j = 0; j < n; ++j) g += before(sm.cp[w * MAX_TOPK + j], sm.ci[w * MAX_TOPK + j], p, e) ? 1 : 0;
+  // Probabilities are >= 0, so their bit patterns order like unsigned integers and one redux
+  // instruction finds a warp's maximum; spent or invalid entries are 0 and an all-zero round marks the end.
+  const int kk = topk < 32 ? topk : 32;
+  unsigned mine = e < E ? __float_as_uint(p) + 1u : 0u;  // + 1: a valid probability of exactly 0 still beats "spent"
+  for (int r = 0; r < kk; ++r) {
+    const unsigned best = __reduce_max_sync(0xffffffffu, mine);
+    const int src = __ffs(__ballot_sync(0xffffffffu, mine == best)) - 1;
+    if (lane == r) {
+      sm.ck[warp * MAX_TOPK + r] = best;
+      sm.ci[warp * MAX_TOPK + r] = (warp << 5) + src;
     }
-    if (g < topk) {
-      idx[g] = e;
-      sm.top[g] = p;
-    }
+    if (lane == src) mine = 0u;
   }
   __syncthreads();
-  if (threadIdx.x < topk) {
-    float total = 0.f;
-    for (int k = 0; k < topk; ++k) total += sm.top[k];  // rank order, as the reference accumulates
-    wts[threadIdx.x] = sm.top[threadIdx.x] / total;
+  if (warp != 0) return;
+  int head = 0;
+  unsigned hk = lane < 8 ? sm.ck[lane * MAX_TOPK] : 0u;
+  float my_top = 0.f;
+  for (int r = 0; r < topk; ++r) {
+    const unsigned best = __reduce_max_sync(0xffffffffu, hk);
+    const int src = __ffs(__ballot_sync(0xffffffffu, hk == best)) - 1;
+    const int win = __shfl_sync(0xffffffffu, lane < 8 ? sm.ci[lane * MAX_TOPK + head] : 0, src);
+    if (lane == r) {
+      my_top = __uint_as_float(best - 1u);
+      idx[r] = win;
+    }
+    if (lane == src) {
+      ++head;
+      hk = head < kk ? sm.ck[lane * MAX_TOPK + head] : 0u;
+    }
   }
+  float total = 0.f;
+  for (int r = 0; r < topk; ++r) total += __shfl_sync(0xffffffffu, my_top, r);  // rank order, as the reference accumulates
+  if (lane < topk) wts[lane] = my_top / total;
 }
 
 // grid = rows of logits; logits has E + 1 valid columns per row at the given stride.
@@ -129,6 +133,7 @@ __global__ void __launch_bounds__(THREADS)
                   float* __restrict__ sgate, unsigned* counter, const char* gu_q, const char* gu_sm, const char* d_q,
                   const char* d_sm, size_t gu_q_b, size_t gu_sm_b, size_t d_q_b, size_t d_sm_b) {
   __shared__ Smem sm;
+  DRB_TRACE_POINT(0, 0);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row0 = blockIdx.x * ROWS_PER_BLOCK;
   const int nrows = min(ROWS_PER_BLOCK, E + 1 - row0);
@@ -141,6 +146,7 @@ __global__ void __launch_bounds__(THREADS)
   __syncthreads();
   pdl_launch_dependents();  // the gate/up kernel may start fetching the shared expert's rows right away
   pdl_wait();               // x is the previous kernel's output
+  DRB_TRACE_POINT(1, 0);
 
   // RMSNorm scale, recomputed by every block (8 KB of x from L2).
   const float4* x4 = reinterpret_cast<const float4*>(x);
@@ -169,7 +175,9 @@ __global__ void __launch_bounds__(THREADS)
     }
     xp[0] = pack2(a.x, a.y), xp[1] = pack2(a.z, a.w), xp[2] = pack2(b.x, b.y), xp[3] = pack2(b.z, b.w);
   }
+  DRB_TRACE_POINT(2, 0);
   mbar_wait(&sm.full, 0, DRB_ERR_FULL_WAIT);
+  DRB_TRACE_POINT(3, 0);
   // Each thread owns one 16-byte chunk (8 weights) of every row of the block.
 #pragma unroll
   for (int r = 0; r < ROWS_PER_BLOCK; ++r) {
@@ -193,8 +201,10 @@ __global__ void __launch_bounds__(THREADS)
   __syncthreads();
   if (threadIdx.x == 0) sm.last = atomicAdd(counter, 1u) == gridDim.x - 1;
   __syncthreads();
+  DRB_TRACE_POINT(4, 0);
   if (!sm.last) return;
   __threadfence();
+  DRB_TRACE_ANY(5, 0);
   const int e = threadIdx.x;
   const float v = e < E ? __ldcg(logits + e) : -INFINITY;
   softmax_topk(v, E, topk, idx, wts, sm.tk);
@@ -202,17 +212,24 @@ __global__ void __launch_bounds__(THREADS)
     sgate[0] = __ldcg(logits + E);
     *counter = 0u;
   }
+  DRB_TRACE_ANY(6, 0);
   // Optional: pull exactly the chosen experts into L2 (one bulk prefetch per region and expert).
-  if (gu_q) {
-    __syncthreads();
-    if ((int)threadIdx.x < topk * 4) {
-      const int k = threadIdx.x >> 2, which = threadIdx.x & 3;
+  if (gu_q && threadIdx.x < 32) {
+    __syncwarp();
+    for (int i = threadIdx.x; i < topk * 4; i += 32) {
+      const int k = i >> 2, which = i & 3;
       const size_t ex = (size_t)idx[k];
       const char* base = which == 0 ? gu_q : which == 1 ? gu_sm : which == 2 ? d_q : d_sm;
       const size_t nb = which == 0 ? gu_q_b : which == 1 ? gu_sm_b : which == 2 ? d_q_b : d_sm_b;
       if (base) prefetch_share(base + ex * nb, nb, 0, 1);
     }
   }
+}
+
+static cudaError_t configure_all() {
+  cudaError_t e = drb_carveout(k_router_topk);
+  if (e != cudaSuccess) return e;
+  return drb_carveout(k_moe_topk);
 }
 
 }  // namespace router

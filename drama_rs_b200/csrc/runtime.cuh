@@ -14,7 +14,17 @@
 
 #include "common.cuh"
 
+// Every kernel of the library asks for the same shared-memory carveout (the maximum). Kernels that
+// prefer different L1/shared splits cannot share a multiprocessor, and switching the split between
+// consecutive launches drains it first: microseconds per launch on a path whose kernels run for two.
+template <typename K>
+static cudaError_t drb_carveout(K kernel) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+}
+
 namespace gemv { static cudaError_t configure_all(); }
+namespace router { static cudaError_t configure_all(); }
+namespace pf { static cudaError_t configure_all(); }
 namespace moe { static cudaError_t configure_all(); }
 namespace stack { static cudaError_t configure_all(); }
 namespace pfmma { static cudaError_t configure_all(); }
@@ -41,6 +51,8 @@ static cudaError_t setup(int d) {
   const char* p = getenv("DRB_PDL");
   dv.pdl = !(p && p[0] == '0');
   if ((e = gemv::configure_all()) != cudaSuccess) return e;
+  if ((e = router::configure_all()) != cudaSuccess) return e;
+  if ((e = pf::configure_all()) != cudaSuccess) return e;
   if ((e = moe::configure_all()) != cudaSuccess) return e;
   if ((e = stack::configure_all()) != cudaSuccess) return e;
   if ((e = pfmma::configure_all()) != cudaSuccess) return e;
@@ -166,3 +178,10 @@ DRB_API int drb_grid_blocks(void) {
   cudaGetDevice(&d);
   return rt::g_dev[d].sms;
 }
+
+#ifdef DRB_TRACE
+// Development builds only: copies the timing probes out (nanoseconds of the global timer).
+DRB_API int drb_trace_read(unsigned long long* out, int n) {
+  return (int)cudaMemcpyFromSymbol(out, g_drb_trace, sizeof(unsigned long long) * (n < 64 ? n : 64));
+}
+#endif

@@ -49,7 +49,8 @@ def test_gemv_q8_shapes(st, n, k):
     y = run_q8(st, q, s, x)
     ref = orc.gemv_q8(q, s, x, dtype=np.float64)
     scale = np.abs(ref).max()
-    assert np.abs(y - ref).max() <= 2e-6 * scale + 1e-6, (n, k)
+    # activations enter as 21-bit block fixed point: a few 1e-6 of the output scale
+    assert np.abs(y - ref).max() <= 1e-5 * scale + 5e-6, (n, k)
     assert device_error_word() == 0
 
 

@@ -164,19 +164,25 @@ def test_moe_prefill_golden_rows40(st, layers, golden_dir):
     pre = MoePrefill(dev, 64, st=st)
     y = pre.run(x)
     idx = pre.idx.download(np.int32, 40 * 8, st).reshape(40, 8)
-    assert np.array_equal(idx, g["idx"])
-    ref = x.astype(np.float64) + g["out_hf64"]
-    # The prefill path feeds bf16 activations to the experts (the ABI carries bf16 rows), so the comparison
-    # with the fp32-activation reference is in relative L2; max-abs scales with the output magnitude.
-    a, r = assert_parity(y, ref, "prefill 40 rows", max_abs=np.inf, rel_l2=3e-3)
-    # Against the oracle fed the same bf16-rounded normalised rows the agreement is tight.
+    # The prefill ABI carries the normalised rows in bf16 (src/engine.rs:499, 554), so routing is decided on
+    # bf16-rounded activations: compare with the oracle fed the same rows, and with the reference's fp32-input
+    # routing wherever the two oracles agree.
     xh = orc.round_bf16(orc.rmsnorm(x, host["post_norm"], 1e-6))
-    out = orc.moe_block(host, xh.astype(np.float64), 8, np.float64)[0]
+    out, oidx, _, _, logits = orc.moe_block(host, xh.astype(np.float64), 8, np.float64)
+    safe = orc.route_margin(logits, 256, 8) > 1e-6
+    assert safe.all() and np.array_equal(idx, oidx)
+    same = (oidx == g["idx"]).all(axis=1)
+    assert same.mean() >= 0.9 and np.array_equal(idx[same], g["idx"][same])
+    ref = x.astype(np.float64) + g["out_hf64"]
+    a, r = assert_parity(y[same], ref[same], "prefill 40 rows vs the reference (fp32 inputs)", max_abs=np.inf, rel_l2=REL_PREFILL)
     assert_parity(y - x, out, "prefill 40 rows vs bf16-input oracle", max_abs=np.inf, rel_l2=REL_PREFILL)
     assert device_error_word() == 0
 
 
-REL_PREFILL = 2.5e-3  # the shared expert runs through bf16 weights and a bf16 intermediate, as in the reference
+# Relative L2 of the prefill output. The shared expert runs through cuBLAS on weights dequantised to bf16 and
+# a bf16 intermediate, exactly as the reference's prefill does (src/engine.rs:351-355, 560-562); that rounding,
+# not the routed int4 path, sets this figure.
+REL_PREFILL = 4e-3
 
 
 def test_moe_prefill_zipf_300(st, layers):
