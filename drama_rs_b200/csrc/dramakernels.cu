@@ -5,6 +5,7 @@
 #include "gemv.cuh"
 #include "router.cuh"
 #include "moe_decode.cuh"
+#include "moe_decode_static.cuh"
 #include "moe_prefill.cuh"
 
 namespace stack { static cudaError_t configure_all() { return cudaSuccess; } }

@@ -127,6 +127,18 @@ int dr_swiglu_rows(const float* h, dr_bf16* y, int rows, int i, dr_stream st);  
 int dr_rmsnorm(const float* x, const float* w, float* y, dr_bf16* yb, int rows, int d, float eps,
                dr_stream st);                                                                   /* drama.cu:1182-1202; ffi.rs:77 */
 
+/* dr_moe_decode for callers that have no scratch to pass and may not allocate any (memory budget fixed at
+ * start-up, allocator owned by another component, a capture running on another thread). It has no
+ * counterpart in the reference. The (topk + 1) * i floats live in a fixed 18 KB device array inside the
+ * library, so: shapes beyond h = 2048, i = 512, topk = 8 return -1; calls that overlap on the GPU race on
+ * that array (same-stream calls are fine); the first call per device does a one-time set-up without
+ * allocating and should be made outside stream capture. */
+int dr_moe_decode_static(const uint8_t* gu_q, const dr_half* gu_sm, const uint8_t* d_q, const dr_half* d_sm,
+                         const int8_t* sgu_q, const dr_half* sgu_s, const int8_t* sd_q, const dr_half* sd_s,
+                         const float* x, const int* idx, const float* wts, const float* sgate, const float* res,
+                         float* y, int h, int i, int topk, const float* nw, float eps, const char* pf, size_t pf_bytes,
+                         dr_stream st);
+
 /* ---- additions of this library; no counterpart in the reference ----------------------------- */
 int dr_stream_destroy(dr_stream s);
 int dr_cublas_destroy(void* h);
