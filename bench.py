@@ -305,7 +305,7 @@ def run_gpu(args) -> None:
     line = {
         "metric": "int4_moe_decode_us_per_layer", "value": us_layer, "unit": "us/layer", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": False, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "vs_baseline": None, "dtype": "int4/int8 weights x 21-bit block-fixed activations (dp4a, exact int32) -> f32", "data": "synthetic",
         "config": {"workload": "decode_stack40_b1", "layers": args.layers, "hidden": SHAPE.hidden, "experts": SHAPE.experts,
                    "topk": SHAPE.topk, "inter": SHAPE.inter, "weights": "int4 g64 (scale,min) routed + int8 g128 shared",
                    "graph": "one CUDA graph per step, 3 kernels per layer", "replicas": world,
@@ -313,7 +313,10 @@ def run_gpu(args) -> None:
         "hbm_gbs": gbs,
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
                      "peak_source": f"{peak_kind} copy bandwidth", "kernel": "decode step graph (router, gate_up, down per layer)",
-                     "algorithmic_bytes_per_launch": step_bytes, "traffic": None},
+                     "algorithmic_bytes_per_launch": step_bytes,
+                     # dram__bytes_read+write per step from the ncu capture summarised in profiles/decode_kernels_ncu_full.md
+                     # (19.61 MB per layer, measured on a 4-layer case; traffic is proportional to the layer count)
+                     "traffic": 19.607e6 * args.layers},
         "e2e": {"value": e2e_us, "unit": "us/layer", "h2d_bytes_per_step": hidden_bytes, "d2h_bytes_per_step": hidden_bytes},
         "gpu_launches": args.steps * args.layers * 3,
         "clocks": clocks.summary(),
