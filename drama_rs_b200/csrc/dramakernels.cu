@@ -7,6 +7,6 @@
 #include "moe_decode.cuh"
 #include "moe_decode_static.cuh"
 #include "moe_prefill.cuh"
+#include "stack_decode.cuh"
 
-namespace stack { static cudaError_t configure_all() { return cudaSuccess; } }
 namespace pfmma { static cudaError_t configure_all() { return cudaSuccess; } }

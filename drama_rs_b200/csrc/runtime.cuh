@@ -34,7 +34,7 @@ namespace rt {
 constexpr int MAX_DEVICES = 32;
 constexpr int GRID_SYNC_WORDS = 1024;
 static DrbDevice g_dev[MAX_DEVICES];
-static const DrbDevice g_unready = {0, false, false, nullptr};
+static const DrbDevice g_unready = {};
 static std::mutex g_mu;
 static cudaError_t g_setup_error = cudaSuccess;
 
@@ -50,6 +50,8 @@ static cudaError_t setup(int d) {
   dv.sms = sms;
   const char* p = getenv("DRB_PDL");
   dv.pdl = !(p && p[0] == '0');
+  const char* rv = getenv("DRB_ROUTER");
+  dv.router_cluster = !(rv && rv[0] == 'g');
   if ((e = gemv::configure_all()) != cudaSuccess) return e;
   if ((e = router::configure_all()) != cudaSuccess) return e;
   if ((e = pf::configure_all()) != cudaSuccess) return e;

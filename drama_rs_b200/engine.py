@@ -23,7 +23,9 @@ from .gpu import DevBuf, Graph, Stream, check, launched
 from .model import MoeLayer
 
 NULL = C.c_void_p(0)
-ROUTER_PREFETCH = False  # src/engine.rs:18: the router's own expert warm-up is compiled in but off
+# src/engine.rs:18 has this switch off. Measured here as well: the warm-up runs in the router's single tail
+# block, and 14 MB of prefetches through one multiprocessor take ~55 us, so it stays off.
+ROUTER_PREFETCH = False
 GEMV_PREFETCH = True  # src/engine.rs:19
 
 
@@ -202,3 +204,47 @@ class MoePrefill:
             l.dr_moe_combine(self.x.at(0), self.yp.at(0), self.slot_of.at(0), self.wts.at(0), self.sgate.at(0),
                              self.sh_out.at(0), n, topk, h, st), "moe_combine")
         return self.x.download(np.float32, n * h, self.st).reshape(n, h)
+
+
+class MoeStackDecoder:
+    """The same stack as MoeDecoder through drb_moe_stack_decode: one persistent kernel per step."""
+
+    def __init__(self, layers: list[MoeLayer], topk: int = 8, eps: float = 1e-6, st: Stream | None = None) -> None:
+        self.l = ffi.lib()
+        self.st = st or Stream()
+        self.layers, self.topk, self.eps = layers, topk, eps
+        self.hidden, self.inter, self.experts = layers[0].hidden, layers[0].inter, layers[0].experts
+        table = np.zeros((len(layers), 10), dtype=np.uint64)
+        for i, ly in enumerate(layers):
+            table[i] = [ly.router.ptr, ly.post_norm.ptr, ly.gate_up.q.ptr, ly.gate_up.sm.ptr, ly.down.q.ptr, ly.down.sm.ptr,
+                        ly.shared_gate_up.q.ptr, ly.shared_gate_up.s.ptr, ly.shared_down.q.ptr, ly.shared_down.s.ptr]
+        self.table = DevBuf.from_array(table, self.st)
+        self.x = DevBuf(self.hidden * 4)
+        self.ws = DevBuf.zeros(self.l.drb_moe_stack_workspace_bytes(), self.st)
+        self.idx_trace = DevBuf(len(layers) * topk * 4)
+        self.wts_trace = DevBuf(len(layers) * topk * 4)
+        self.graph: Graph | None = None
+
+    def launch(self) -> None:
+        launched(
+            self.l.drb_moe_stack_decode(self.table.at(0), len(self.layers), self.x.at(0), self.ws.at(0), self.experts, self.topk,
+                                        self.hidden, self.inter, self.eps, self.idx_trace.at(0), self.wts_trace.at(0), self.st.raw),
+            "moe_stack_decode")
+
+    def capture(self) -> None:
+        self.graph = Graph(self.st, self.launch)
+
+    def set_x(self, x: np.ndarray) -> None:
+        self.x.upload(x.astype(np.float32), self.st)
+
+    def step(self) -> np.ndarray:
+        if self.graph is not None:
+            self.graph.launch(self.st)
+        else:
+            self.launch()
+        return self.x.download(np.float32, self.hidden, self.st)
+
+    def routing(self) -> tuple[np.ndarray, np.ndarray]:
+        n = len(self.layers) * self.topk
+        return (self.idx_trace.download(np.int32, n, self.st).reshape(-1, self.topk),
+                self.wts_trace.download(np.float32, n, self.st).reshape(-1, self.topk))

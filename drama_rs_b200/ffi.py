@@ -56,6 +56,8 @@ SIGNATURES: dict[str, tuple] = {
     "dr_f32_to_bf16": (I32, [P, P, SZ, P]),
     "dr_swiglu_rows": (I32, [P, P, I32, I32, P]),
     "dr_rmsnorm": (I32, [P, P, P, P, I32, I32, F32, P]),
+    "drb_moe_stack_workspace_bytes": (I32, []),
+    "drb_moe_stack_decode": (I32, [P, I32, P, P, I32, I32, I32, I32, F32, P, P, P]),
     "drb_init": (I32, []),
     "drb_device_error": (I32, [C.POINTER(U32)]),
     "drb_grid_blocks": (I32, []),

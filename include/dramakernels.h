@@ -140,6 +140,18 @@ int dr_moe_decode_static(const uint8_t* gu_q, const dr_half* gu_sm, const uint8_
                          dr_stream st);
 
 /* ---- additions of this library; no counterpart in the reference ----------------------------- */
+/* One layer's weights for drb_moe_stack_decode: device pointers in the layouts above. */
+typedef struct {
+  const void *router, *post_norm, *gu_q, *gu_sm, *d_q, *d_sm, *sgu_q, *sgu_s, *sd_q, *sd_s;
+} drb_moe_layer;
+/* x <- x + moe_l(rmsnorm(x, post_norm_l)) for l = 0 .. n_layers-1, in place, as ONE persistent cooperative
+ * kernel (the benchmark's 40-layer decode step without per-layer launches). layers: device array.
+ * workspace: drb_moe_stack_workspace_bytes() bytes of device memory. idx_trace / wts_trace: optional
+ * [n_layers, topk] device arrays receiving each layer's routing. h == 2048, i == 512, topk == 8, e <= 256,
+ * >= 148 multiprocessors; -1 otherwise. The per-layer dr_router_topk + dr_moe_decode compute the same. */
+int drb_moe_stack_workspace_bytes(void);
+int drb_moe_stack_decode(const drb_moe_layer* layers, int n_layers, float* x, void* workspace, int e, int topk, int h,
+                         int i, float eps, int* idx_trace, float* wts_trace, dr_stream st);
 int dr_stream_destroy(dr_stream s);
 int dr_cublas_destroy(void* h);
 int drb_init(void);                    /* per-device setup; also run by the pre-capture hooks above */

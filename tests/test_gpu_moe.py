@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from drama_rs_b200 import ffi, synth
-from drama_rs_b200.engine import MoeDecoder, MoePrefill
+from drama_rs_b200.engine import MoeDecoder, MoePrefill, MoeStackDecoder
 from drama_rs_b200.gpu import DevBuf, Stream, launched
 from drama_rs_b200.model import MoeLayer
 from oracle import moe_oracle as orc
@@ -154,6 +154,43 @@ def test_moe_decode_stack_of_layers(st, layers):
     y = dec.step()
     scale = np.abs(ref).max()
     a, r = assert_parity(y, ref[0], "3-layer stack", max_abs=max(1e-2, 4e-6 * scale))
+    assert device_error_word() == 0
+
+
+def test_moe_stack_persistent_kernel(st, layers, golden_dir):
+    """drb_moe_stack_decode: four layers in one persistent kernel, eager and from a graph, against the fp64
+    oracle (routing of every layer bit-exact) and against the per-layer entry points."""
+    pairs = [layers(s) for s in (0, 1, 0, 1)]
+    x = synth.make_x(21, 1, 2048)[0]
+    ref = x.astype(np.float64)[None]
+    ref_idx = []
+    for host, _ in pairs:
+        ref, ridx, _, _, _ = orc.moe_layer(host, ref, 8, 1e-6, np.float64)
+        ref_idx.append(ridx[0])
+    sd = MoeStackDecoder([d for _, d in pairs], st=st)
+    sd.set_x(x)
+    y = sd.step()
+    assert device_error_word() == 0
+    idx, wts = sd.routing()
+    assert np.array_equal(idx, np.stack(ref_idx))
+    scale = np.abs(ref).max()
+    assert_parity(y, ref[0], "4-layer persistent stack", max_abs=max(1e-2, 4e-6 * scale))
+    dec = MoeDecoder([d for _, d in pairs], st=st)
+    dec.set_x(x)
+    y_layers = dec.step_eager()
+    assert np.abs(y - y_layers).max() <= 4e-6 * scale
+    sd.capture()
+    for _ in range(3):
+        sd.set_x(x)
+        assert np.array_equal(sd.step(), y), "graph replay of the persistent kernel differs from the eager launch"
+    # one layer against the golden vectors of the reference's own code
+    g = np.load(os.path.join(golden_dir, "moe_decode_seed0.npz"))
+    one = MoeStackDecoder([pairs[0][1]], st=st)
+    x0 = synth.make_x(0, 1, 2048)[0]
+    one.set_x(x0)
+    y0 = one.step()
+    assert np.array_equal(one.routing()[0][0], g["idx"][0])
+    assert_parity(y0, x0.astype(np.float64) + g["out_hf64"][0], "persistent kernel, golden layer")
     assert device_error_word() == 0
 
 
