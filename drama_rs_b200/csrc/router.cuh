@@ -24,7 +24,7 @@ DRB_DEV bool before(float pa, int ia, float pb, int ib) { return pa > pb || (pa 
 struct TopkSmem {
   float red[8];
   unsigned ured[8];
-  unsigned long long comp[8 * MAX_TOPK];
+  __align__(16) unsigned long long comp[8 * MAX_TOPK];
   float top[MAX_TOPK];
 };
 
@@ -67,8 +67,11 @@ DRB_DEV void topk_sync() {
 
 // BAR_ID = 0: the block has exactly 256 threads. Otherwise threads 0..255 of a larger block call it and
 // synchronise on named barrier BAR_ID.
-template <int BAR_ID = 0>
-DRB_DEV void softmax_topk(float v, int E, int topk, int* __restrict__ idx, float* __restrict__ wts, TopkSmem& sm) {
+// TK > 0 fixes topk at compile time (the loops over candidates unroll and their shared-memory reads
+// overlap instead of forming a 64-long dependent chain); TK = 0 takes it from the argument.
+template <int BAR_ID = 0, int TK = 0>
+DRB_DEV void softmax_topk_impl(float v, int E, int topk, int* __restrict__ idx, float* __restrict__ wts, TopkSmem& sm) {
+  if (TK > 0) topk = TK;
   const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
   // max: one redux per warp on order-preserving integer keys, then eight values per thread
   const unsigned vb = __float_as_uint(v);
@@ -80,6 +83,7 @@ DRB_DEV void softmax_topk(float v, int E, int topk, int* __restrict__ idx, float
 #pragma unroll
   for (int w = 1; w < 8; ++w) mo = max(mo, sm.ured[w]);
   const float m = __uint_as_float((mo & 0x80000000u) ? (mo & 0x7fffffffu) : ~mo);
+  DRB_TRACE_ANY(40, 0);
   const float ex = e < E ? expf(v - m) : 0.f;
   const float ws = warp_sum(ex);
   if (lane == 0) sm.red[warp] = ws;
@@ -87,6 +91,7 @@ DRB_DEV void softmax_topk(float v, int E, int topk, int* __restrict__ idx, float
   // the butterfly over the eight warp totals, written out: ((0+4)+(2+6)) + ((1+5)+(3+7))
   const float z = ((sm.red[0] + sm.red[4]) + (sm.red[2] + sm.red[6])) + ((sm.red[1] + sm.red[5]) + (sm.red[3] + sm.red[7]));
   const float p = e < E ? ex / z : -1.f;
+  DRB_TRACE_ANY(41, 0);
   const unsigned key = e < E ? __float_as_uint(p) + 1u : 0u;
   int r = 0;
 #pragma unroll
@@ -96,24 +101,51 @@ DRB_DEV void softmax_topk(float v, int E, int topk, int* __restrict__ idx, float
     r += (ko > key || (ko == key && src < lane)) ? 1 : 0;
   }
   const int kk = topk < 32 ? topk : 32;
+  DRB_TRACE_ANY(42, 0);
   if (r < kk) sm.comp[warp * MAX_TOPK + r] = ((unsigned long long)key << 32) | (unsigned)(~e);
   topk_sync<BAR_ID>();
   if (r < kk && key != 0u) {
     const unsigned long long mine = ((unsigned long long)key << 32) | (unsigned)(~e);
     int g = 0;
-    for (int w = 0; w < 8; ++w)
-      for (int j = 0; j < kk; ++j) g += sm.comp[w * MAX_TOPK + j] > mine ? 1 : 0;
+    if (TK > 0) {
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+#pragma unroll
+        for (int j = 0; j < TK; j += 2) {
+          const ulonglong2 c = *reinterpret_cast<const ulonglong2*>(&sm.comp[w * MAX_TOPK + j]);
+          g += (c.x > mine ? 1 : 0) + ((j + 1 < TK && c.y > mine) ? 1 : 0);
+        }
+      }
+    } else {
+      for (int w = 0; w < 8; ++w)
+        for (int j = 0; j < kk; ++j) g += sm.comp[w * MAX_TOPK + j] > mine ? 1 : 0;
+    }
     if (g < topk) {
       idx[g] = e;
       sm.top[g] = p;
     }
   }
+  DRB_TRACE_ANY(43, 0);
   topk_sync<BAR_ID>();
   if (e < topk) {
     float total = 0.f;
-    for (int k = 0; k < topk; ++k) total += sm.top[k];  // rank order, as the reference accumulates
+    if (TK > 0) {
+      float t[TK > 0 ? TK : 1];
+#pragma unroll
+      for (int k = 0; k < TK; ++k) t[k] = sm.top[k];
+#pragma unroll
+      for (int k = 0; k < TK; ++k) total += t[k];  // rank order, as the reference accumulates
+    } else {
+      for (int k = 0; k < topk; ++k) total += sm.top[k];
+    }
     wts[e] = sm.top[e] / total;
   }
+}
+
+template <int BAR_ID = 0>
+DRB_DEV void softmax_topk(float v, int E, int topk, int* __restrict__ idx, float* __restrict__ wts, TopkSmem& sm) {
+  if (topk == 8) softmax_topk_impl<BAR_ID, 8>(v, E, topk, idx, wts, sm);
+  else softmax_topk_impl<BAR_ID, 0>(v, E, topk, idx, wts, sm);
 }
 
 // grid = rows of logits; logits has E + 1 valid columns per row at the given stride.
