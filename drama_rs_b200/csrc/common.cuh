@@ -491,6 +491,7 @@ struct DrbDevice {
   int sms;              // blocks of a persistent grid (multiprocessors, or the DRB_SMS override)
   bool pdl;             // programmatic dependent launch enabled (DRB_PDL=0 turns it off)
   bool ready;           // attributes set
+  bool prefill_mma;     // dr_moe_prefill on tcgen05 (DRB_PREFILL=simt selects the CUDA-core kernels)
   bool router_cluster;  // decode router as one 8-block cluster (DRB_ROUTER=grid selects the multi-block variant)
   unsigned* grid_sync;  // zeroed words used by grid-wide barriers
 };

@@ -6,7 +6,7 @@
 #include "router.cuh"
 #include "moe_decode.cuh"
 #include "moe_decode_static.cuh"
+#include "moe_prefill_mma.cuh"
 #include "moe_prefill.cuh"
 #include "stack_decode.cuh"
 
-namespace pfmma { static cudaError_t configure_all() { return cudaSuccess; } }

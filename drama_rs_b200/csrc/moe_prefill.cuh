@@ -279,6 +279,16 @@ extern "C" int dr_moe_prefill(const uint8_t* gu_q, const __half2* gu_sm, const u
                               int E, int H, int I, cudaStream_t st) {
   if (H != pf::H || I != pf::I) return -1;
   if (E <= 0) return 0;
+  const DrbDevice& dev = drb_device(st);
+  if (!dev.ready) return -2;
+  if (dev.prefill_mma) {
+    // tensor-core path: two persistent grouped GEMMs (moe_prefill_mma.cuh)
+    drb_launch(pfmma::k_grouped<0>, dim3(dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, gu_q, gu_sm,
+               (const void*)xp, (void*)act, offsets, counts, E);
+    drb_launch(pfmma::k_grouped<1>, dim3(dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, d_q, d_sm,
+               (const void*)act, (void*)y, offsets, counts, E);
+    return 0;
+  }
   pf::k_pf_gate_up<<<dim3(E, I / 16), 256, 0, st>>>(gu_q, gu_sm, xp, offsets, counts, reinterpret_cast<__half*>(act));
   pf::k_pf_down<<<dim3(E, H / 32), 256, 0, st>>>(d_q, d_sm, reinterpret_cast<const __half*>(act), offsets, counts, y);
   return 0;

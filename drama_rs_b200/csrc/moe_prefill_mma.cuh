@@ -1,0 +1,283 @@
+// Expert-grouped prefill on the 5th-generation tensor cores: dr_moe_prefill as two grouped GEMMs
+// whose int4 weights are dequantised straight into tcgen05 operand tiles.
+//
+//   gate/up:  for expert e with its cnt tokens  D[128, cnt] = W_tile[128, 2048] . X_e[cnt, 2048]^T
+//             (the tile interleaves 64 gate rows with their 64 up rows), epilogue silu(g) * u -> act
+//   down:     D[128, cnt] = Wd_tile[128, 512] . act_e[cnt, 512]^T -> y
+//
+// "Swap-AB": the weight rows are the MMA's M = 128 dimension and the tokens its N dimension
+// (16 .. 256, rounded up to 16), because most experts see a handful of tokens: with Zipf routing of
+// 300 rows the median group is 4 tokens. Accumulators live in tensor memory (256 columns of fp32).
+//
+// One persistent block per multiprocessor walks the (expert, 128-row tile) items. Per 64-wide
+// K chunk (= one int4 scale group) its 256 threads
+//   * dequantise 128 x 64 nibbles to fp16 (w = q*scale + min, single rounding) and store them in the
+//     K-major 128-byte-swizzled layout the MMA reads (A operand),
+//   * convert the tokens' 64 activations to fp16 in the same element order (B operand),
+// and one thread issues four tcgen05.mma.kind::f16 (K = 16 each). Three chunk stages let the
+// dequantisation of chunk k+1 overlap the MMAs of chunk k; tcgen05.commit on an mbarrier frees a stage.
+// fp16 operands (not bf16): bf16-dequantised weights miss the 1e-3 output tolerance (1.65e-3), fp16
+// measures 1.8e-4.
+//
+// Every wait is bounded (common.cuh); tensor memory is allocated once per block and always freed.
+// Replaces kernels/drama.cu:799-968 of the reference (k_moe_pf_gate_up, k_moe_pf_down).
+#pragma once
+
+#include "common.cuh"
+
+namespace pfmma {
+
+constexpr int H = 2048, I = 512;
+constexpr int THREADS = 256;
+constexpr int TILE_M = 128;
+constexpr int KC = 64;                              // K chunk = one swizzle atom of fp16 = one int4 scale group
+constexpr int MAX_N = 256;                          // tokens per accumulator
+constexpr int A_BYTES = TILE_M * KC * 2;            // 16 KB
+constexpr int B_BYTES = MAX_N * KC * 2;             // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;      // 48 KB
+constexpr int STAGES = 3;
+constexpr int CTL_BYTES = 1024;
+constexpr size_t SMEM_BYTES = CTL_BYTES + 1024 /* alignment slack */ + (size_t)STAGES * STAGE_BYTES;
+constexpr int TMEM_COLS = 256;
+
+struct Ctl {
+  uint64_t empty[STAGES];  // a stage's MMAs have completed
+  uint64_t done;           // all MMAs of the current accumulator have completed
+  uint32_t tmem_base;
+};
+
+// ---- tcgen05 wrappers ------------------------------------------------------------------------
+
+DRB_DEV void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {  // one full warp
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+DRB_DEV void tmem_dealloc(uint32_t base, uint32_t cols) {  // one full warp
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+}
+DRB_DEV void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+DRB_DEV void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+DRB_DEV void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+DRB_DEV uint64_t smem_desc(const void* p) {
+  const uint64_t addr = (uint64_t)(smem_u32(p) >> 4) & 0x3FFFull;
+  return addr | (1ull << 16) /* leading offset: unused with swizzle */ | (64ull << 32) /* 1024 B >> 4 */ |
+         (1ull << 46) /* descriptor version */ | (2ull << 61) /* SWIZZLE_128B */;
+}
+
+// Instruction descriptor for kind::f16: fp16 x fp16 -> fp32, both operands K-major, M = 128, N = n.
+DRB_DEV uint32_t instr_desc(int n) {
+  return (1u << 4) /* D = f32 */ | (0u << 7) /* A = f16 */ | (0u << 10) /* B = f16 */ | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+}
+
+DRB_DEV void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+      : "memory");
+}
+
+// Arrives on `bar` once every MMA issued so far by this thread has completed.
+DRB_DEV void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// 16 consecutive fp32 columns of this warp's 32 lanes.
+DRB_DEV void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+        "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Byte offset of 16-byte chunk c (0..7) of row r inside a K-major 128-byte-swizzled tile.
+DRB_DEV uint32_t swz_off(int r, int c) { return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4)); }
+
+// Eight nibbles of one word -> eight fp16 weights q*s + m, in element order (0,4,1,5,2,6,3,7).
+// 0x6400 | q is the half 1024 + q; subtracting 1024 is exact, the fused multiply-add rounds once.
+DRB_DEV uint4 dequant8(uint32_t w, __half2 s2, __half2 m2) {
+  const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
+  uint32_t t[4];
+  t[0] = lop3_and_or(w, 0x000F000Fu, 0x64006400u);
+  t[1] = lop3_and_or(w >> 4, 0x000F000Fu, 0x64006400u);
+  t[2] = lop3_and_or(w >> 8, 0x000F000Fu, 0x64006400u);
+  t[3] = lop3_and_or(w >> 12, 0x000F000Fu, 0x64006400u);
+  uint4 o;
+  uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 q = __hsub2(*reinterpret_cast<__half2*>(&t[i]), k1024);
+    const __half2 r = __hfma2(q, s2, m2);
+    op[i] = *reinterpret_cast<const uint32_t*>(&r);
+  }
+  return o;
+}
+
+// Eight bf16 activations (k ascending) -> fp16 in the same (0,4,1,5,2,6,3,7) order.
+DRB_DEV uint4 bf16x8_to_f16_perm(const uint4& v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};  // (0,1) (2,3) (4,5) (6,7)
+  float f[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) f[2 * i] = __uint_as_float(w[i] << 16), f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  uint4 o;
+  uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 h = __floats2half2_rn(f[i], f[i + 4]);
+    op[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return o;
+}
+
+// Eight fp16 (k ascending) -> the (0,4,1,5,2,6,3,7) order.
+DRB_DEV uint4 f16x8_perm(const uint4& v) {
+  uint4 o;
+  o.x = prmt(v.x, v.z, 0x5410u);  // (0, 4)
+  o.y = prmt(v.x, v.z, 0x7632u);  // (1, 5)
+  o.z = prmt(v.y, v.w, 0x5410u);  // (2, 6)
+  o.w = prmt(v.y, v.w, 0x7632u);  // (3, 7)
+  return o;
+}
+
+
+// GEMM = 0: gate/up (+ SwiGLU, fp16 out);  GEMM = 1: down (fp32 out).
+//   Q  [E, R, K/2] nibbles, SM [E, R, K/64] (scale, min);  R = 2I, K = H for gate/up;  R = H, K = I for down.
+//   src: gate/up: xp bf16 [slots, H];  down: act fp16 [slots, I]
+//   dst: gate/up: act fp16 [slots, I]; down: y f32 [slots, H]
+template <int GEMM>
+__global__ void __launch_bounds__(THREADS, 1)
+    k_grouped(const uint8_t* __restrict__ Q, const __half2* __restrict__ SM, const void* __restrict__ src, void* __restrict__ dst,
+              const int* __restrict__ offsets, const int* __restrict__ counts, int E) {
+  constexpr int K = GEMM == 0 ? H : I;
+  constexpr int R = GEMM == 0 ? 2 * I : H;
+  constexpr int MT = R / TILE_M;  // tiles per expert: 8 / 16
+  constexpr int NKC = K / KC;     // 32 / 8
+  extern __shared__ unsigned char dyn_raw[];
+  unsigned char* dyn = reinterpret_cast<unsigned char*>(((uintptr_t)dyn_raw + 1023) & ~(uintptr_t)1023);
+  Ctl& ctl = *reinterpret_cast<Ctl*>(dyn);
+  unsigned char* stages = dyn + CTL_BYTES;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(&ctl.empty[s], 1);
+    mbar_init(&ctl.done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) tmem_alloc(&ctl.tmem_base, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl.tmem_base;
+
+  bool dead = false;      // a wait ran out once: stop waiting (the error word is set; results are void)
+  unsigned chunk_no = 0;  // chunks issued so far by this block: selects stage and mbarrier phase
+  unsigned acc_no = 0;    // accumulators finished so far: phase of `done`
+  // This thread's share of the A tile: tile row t / 2, 32 of the chunk's 64 nibbles.
+  const int arow = threadIdx.x >> 1, ahalf = threadIdx.x & 1;
+
+  for (int item = blockIdx.x; item < E * MT; item += gridDim.x) {
+    const int e = item / MT, mt = item % MT;
+    const int cnt = counts[e];
+    if (cnt == 0) continue;
+    const int off = offsets[e];
+    // weight row of tile row r: gate/up interleaves gate j (even r) with up j (odd r)
+    const int wrow = GEMM == 0 ? (arow & 1) * I + mt * (TILE_M / 2) + (arow >> 1) : mt * TILE_M + arow;
+    const uint8_t* qrow = Q + ((size_t)e * R + wrow) * (K / 2) + ahalf * 16;
+    const __half2* smrow = SM + ((size_t)e * R + wrow) * (K / 64);
+
+    for (int n0 = 0; n0 < cnt; n0 += MAX_N) {
+      const int nt = min(MAX_N, cnt - n0);
+      const int N = (nt + 15) & ~15;
+      const uint32_t idesc = instr_desc(N);
+      uint4 qn = __ldg(reinterpret_cast<const uint4*>(qrow));
+      __half2 smn = __ldg(smrow);
+      for (int kc = 0; kc < NKC; ++kc, ++chunk_no) {
+        const int s = chunk_no % STAGES;
+        unsigned char* As = stages + (size_t)s * STAGE_BYTES;
+        unsigned char* Bs = As + A_BYTES;
+        const uint4 qv = qn;
+        const __half2 smv = smn;
+        if (kc + 1 < NKC) {  // next chunk's weights are in flight while this one is converted
+          qn = __ldg(reinterpret_cast<const uint4*>(qrow + (kc + 1) * (KC / 2)));
+          smn = __ldg(smrow + kc + 1);
+        }
+        // the MMAs that read this stage STAGES chunks ago must have completed
+        if (chunk_no >= STAGES && !dead) dead = !mbar_wait(&ctl.empty[s], ((chunk_no / STAGES) - 1) & 1, DRB_ERR_TMEM);
+        // ---- A: 32 nibbles -> 32 fp16 = four 16-byte chunks of the tile row
+        {
+          const __half2 s2 = __half2half2(__low2half(smv)), m2 = __half2half2(__high2half(smv));
+          const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(As + swz_off(arow, 4 * ahalf + j)) = dequant8(w[j], s2, m2);
+        }
+        // ---- B: nt tokens x 64 activations, eight 16-byte chunks per token
+        for (int i = threadIdx.x; i < nt * 8; i += THREADS) {
+          const int n = i >> 3, c = i & 7;
+          uint4 v;
+          if (GEMM == 0) {
+            v = bf16x8_to_f16_perm(__ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(src) + (size_t)(off + n0 + n) * H + kc * KC) + c));
+          } else {
+            v = f16x8_perm(*(reinterpret_cast<const uint4*>(static_cast<const __half*>(src) + (size_t)(off + n0 + n) * I + kc * KC) + c));
+          }
+          *reinterpret_cast<uint4*>(Bs + swz_off(n, c)) = v;
+        }
+        fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          tc_fence_after();
+          const uint64_t ad = smem_desc(As), bd = smem_desc(Bs);
+#pragma unroll
+          for (int k16 = 0; k16 < KC / 16; ++k16) mma_f16(tmem, ad + 2 * k16, bd + 2 * k16, idesc, kc > 0 || k16 > 0);
+          mma_commit(&ctl.empty[s]);
+          if (kc == NKC - 1) mma_commit(&ctl.done);
+        }
+      }
+      // ---- epilogue: accumulator [128 tile rows (lanes), N tokens (columns)]
+      if (!dead) dead = !mbar_wait(&ctl.done, acc_no & 1, DRB_ERR_TMEM);
+      ++acc_no;
+      tc_fence_after();
+      const int q4 = warp & 3;             // this warp reads tensor-memory lanes 32 q4 .. 32 q4 + 31
+      const int r = q4 * 32 + lane;        // tile row
+      for (int c0 = (warp >> 2) * 16; c0 < N; c0 += 32) {  // warps 0-3 and 4-7 alternate 16-column groups
+        uint32_t v[16];
+        tmem_ld16(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0, v);
+        if (GEMM == 0) {
+          __half* act = static_cast<__half*>(dst);
+          const int j = mt * (TILE_M / 2) + (r >> 1);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float mine = __uint_as_float(v[i]);
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 1);  // even lane: gate, odd lane: up
+            if ((lane & 1) == 0 && c0 + i < nt) act[(size_t)(off + n0 + c0 + i) * I + j] = __float2half_rn(silu_f(mine) * other);
+          }
+        } else {
+          float* y = static_cast<float*>(dst);
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (c0 + i < nt) y[(size_t)(off + n0 + c0 + i) * H + mt * TILE_M + r] = __uint_as_float(v[i]);
+        }
+      }
+      tc_fence_before();
+      __syncthreads();  // everyone has read the accumulator before the next MMA overwrites it
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+static cudaError_t configure_all() {
+  cudaError_t e;
+  if ((e = cudaFuncSetAttribute(k_grouped<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(k_grouped<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_grouped<0>)) != cudaSuccess) return e;
+  return drb_carveout(k_grouped<1>);
+}
+
+}  // namespace pfmma

@@ -50,6 +50,8 @@ static cudaError_t setup(int d) {
   dv.sms = sms;
   const char* p = getenv("DRB_PDL");
   dv.pdl = !(p && p[0] == '0');
+  const char* pv = getenv("DRB_PREFILL");
+  dv.prefill_mma = !(pv && pv[0] == 's');
   const char* rv = getenv("DRB_ROUTER");
   dv.router_cluster = !(rv && rv[0] == 'g');
   if ((e = gemv::configure_all()) != cudaSuccess) return e;

@@ -194,6 +194,37 @@ def test_moe_stack_persistent_kernel(st, layers, golden_dir):
     assert device_error_word() == 0
 
 
+def test_moe_prefill_grouped_kernel_direct(st, layers):
+    """dr_moe_prefill alone on hand-made groups: one expert with more tokens than one accumulator holds (300),
+    empty experts, groups of 1, 16 and 17 tokens. Each output row against the fp64 expert on the same bf16 row."""
+    l = ffi.lib()
+    host, dev = layers(3, 16)
+    counts = np.array([300, 0, 1, 17, 16, 5, 0, 33, 2, 0, 7, 64, 3, 1, 0, 9], dtype=np.int32)
+    offsets = (np.cumsum(counts) - counts).astype(np.int32)
+    n = int(counts.sum())
+    rng = np.random.Generator(np.random.PCG64(77))
+    xb = synth.f32_to_bf16_bits(rng.standard_normal((n, 2048), dtype=np.float32))
+    dxp, dcnt, doff = DevBuf.from_array(xb, st), DevBuf.from_array(counts, st), DevBuf.from_array(offsets, st)
+    dact, dy = DevBuf(n * 512 * 2), DevBuf(n * 2048 * 4)
+    dy.fill(0xFF, st)
+    gq, gs = dev.gate_up.expert(0)
+    dq, ds = dev.down.expert(0)
+    launched(l.dr_moe_prefill(gq, gs, dq, ds, dxp.at(0), doff.at(0), dcnt.at(0), dact.at(0), dy.at(0), 16, 2048, 512, st.raw), "moe_prefill")
+    y = dy.download(np.float32, n * 2048, st).reshape(n, 2048)
+    assert device_error_word() == 0
+    x = synth.bf16_bits_to_f32(xb).astype(np.float64)
+    worst = 0.0
+    for e in range(16):
+        if counts[e] == 0:
+            continue
+        rows = slice(offsets[e], offsets[e] + counts[e])
+        ref = orc.expert_forward(host, e, x[rows], np.float64)
+        rel = np.linalg.norm(y[rows] - ref, axis=1) / np.linalg.norm(ref, axis=1)
+        worst = max(worst, float(rel.max()))
+    # fp16 weights and fp16 intermediate: a few 1e-4 per row
+    assert worst <= 8e-4, worst
+
+
 def test_moe_prefill_golden_rows40(st, layers, golden_dir):
     g = np.load(os.path.join(golden_dir, "moe_rows40_seed2.npz"))
     host, dev = layers(2)
