@@ -202,6 +202,103 @@ def device_layers(torch, n_layers: int, seed: int, st):
     return out
 
 
+
+def time_on_stream(torch, st, ext_stream, fn, iters: int, warm: int = 3) -> float:
+    """Microseconds per call of fn(i), CUDA events on the library's stream."""
+    for i in range(warm):
+        fn(i)
+    st.sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(ext_stream)
+    for i in range(iters):
+        fn(i)
+    e1.record(ext_stream)
+    st.sync()
+    return e0.elapsed_time(e1) / iters * 1e3
+
+
+def prefill_extra(torch, layers, st, ext_stream) -> dict:
+    """Benchmark configuration 3 on this GPU: 300 rows through one MoE layer, Zipf(1.1) expert popularity,
+    the reference's call sequence (src/engine.rs:544-604) with the expert-grouped tcgen05 GEMMs inside.
+    Four layers are rotated so the expert weights come from HBM."""
+    from drama_rs_b200.engine import MoePrefill
+    from drama_rs_b200.gpu import launched
+
+    rows = 300
+    x = synth.make_x(33, rows, SHAPE.hidden)
+    bias = synth.zipf_router_bias(33, SHAPE.experts, 1.1)
+    pres = [MoePrefill(ly, rows, st=st) for ly in layers[:4]]
+    for p in pres:
+        p.run(x, logit_bias=bias)
+    counts = pres[0].counts.download(np.int32, SHAPE.experts, st)
+    hit = int((counts > 0).sum())
+
+    def full(i):
+        p = pres[i % len(pres)]
+        p.x.upload(x, st)  # 2.4 MB of host rows in: the block is in place, so every call needs fresh input
+        p.run_device(rows)
+
+    def grouped(i):
+        p = pres[i % len(pres)]
+        gq, gs = p.layer.gate_up.expert(0)
+        dq, ds = p.layer.down.expert(0)
+        launched(p.l.dr_moe_prefill(gq, gs, dq, ds, p.xp.at(0), p.offsets.at(0), p.counts.at(0), p.ap.at(0), p.yp.at(0),
+                                    SHAPE.experts, SHAPE.hidden, SHAPE.inter, st.raw), "moe_prefill")
+
+    us_full = time_on_stream(torch, st, ext_stream, full, 20)
+    us_grouped = time_on_stream(torch, st, ext_stream, grouped, 40)
+    wbytes = hit * SHAPE.expert_bytes
+    flops = 2.0 * rows * SHAPE.topk * 3 * SHAPE.hidden * SHAPE.inter
+    peaks_json = {}
+    try:
+        peaks_json = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    tf_peak = float(peaks_json.get("bf16_tflops", 1590.0))
+    hbm_peak = peaks()[0]
+    return {
+        "workload": "prefill_300rows_zipf1.1_one_layer", "rows": rows, "experts_hit": hit, "max_group": int(counts.max()),
+        "rows_per_s": rows / us_full * 1e6, "us_layer_host_rows_in": us_full,
+        "grouped_gemm_us": us_grouped, "grouped_gemm_rows_per_s": rows / us_grouped * 1e6,
+        "grouped_gemm_tflops": flops / us_grouped / 1e6, "tensor_pipe_frac_of_measured_bf16_peak": flops / us_grouped / 1e6 / tf_peak,
+        "grouped_gemm_hbm_gbs": wbytes / us_grouped / 1e3, "hbm_frac_of_measured": wbytes / us_grouped / 1e3 / hbm_peak,
+        "binding_bound": "hbm (33 FLOP/B against a ridge of ~213)",
+    }
+
+
+def gemv_extra(torch, st, ext_stream) -> list:
+    """Benchmark configuration 1: int8 GEMV sweep, batch 1; >= 8 copies of each matrix rotated per launch so
+    the reads come from HBM, not L2 (the method of the reference's bench/gemv_bench.cu:49-55)."""
+    from drama_rs_b200 import ffi
+    from drama_rs_b200.gpu import launched
+
+    lib = ffi.lib()
+    hbm_peak = peaks()[0]
+    out = []
+    g = torch.Generator(device="cuda")
+    g.manual_seed(7)
+    for n, k in ((4096, 2048), (2048, 4096), (8192, 2048), (151936, 2048)):
+        copies = max(8, int(1.5e9 // (n * k)) if n * k < 2e8 else 8)
+        w = torch.randint(-127, 128, (copies, n, k), dtype=torch.int8, device="cuda", generator=g)
+        s = (torch.randn((copies, n, 1), device="cuda", generator=g) * 0.005).abs().clamp_min(1e-4).half().expand(copies, n, k // 128).contiguous()
+        x = torch.randn(k, device="cuda", generator=g).bfloat16().float()
+        y = torch.empty(n, dtype=torch.float32, device="cuda")
+        torch.cuda.synchronize()
+        wb, sb = n * k, n * (k // 128) * 2
+
+        def call(i, w=w, s=s, x=x, y=y, n=n, k=k, wb=wb, sb=sb, copies=copies):
+            c = i % copies
+            launched(lib.dr_gemv_q8(C.c_void_p(w.data_ptr() + c * wb), C.c_void_p(s.data_ptr() + c * sb), C.c_void_p(x.data_ptr()),
+                                    None, C.c_void_p(y.data_ptr()), n, k, None, 0.0, None, 0, st.raw), "gemv_q8", debug=False)
+
+        us = time_on_stream(torch, st, ext_stream, call, 64, warm=8)
+        gbs = (wb + sb) / us / 1e3
+        out.append({"n": n, "k": k, "us": us, "gbs": gbs, "frac_of_measured_hbm": gbs / hbm_peak, "copies_rotated": copies})
+        del w, s
+        torch.cuda.empty_cache()
+    return out
+
+
 def run_gpu(args) -> None:
     import torch
 
@@ -322,6 +419,9 @@ def run_gpu(args) -> None:
         "clocks": clocks.summary(),
         "device_error_word": int(word.value),
     }
+    if not args.no_extras:
+        line["prefill"] = prefill_extra(torch, layers, st, ext_stream)
+        line["gemv_q8_sweep"] = gemv_extra(torch, st, ext_stream)
     if not args.no_cpu:
         line["cpu_baseline"] = cpu_decode_baseline()
     print(json.dumps(line), flush=True)
@@ -335,6 +435,7 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the prefill and GEMV-sweep figures")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

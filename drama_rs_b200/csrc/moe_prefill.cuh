@@ -283,9 +283,9 @@ extern "C" int dr_moe_prefill(const uint8_t* gu_q, const __half2* gu_sm, const u
   if (!dev.ready) return -2;
   if (dev.prefill_mma) {
     // tensor-core path: two persistent grouped GEMMs (moe_prefill_mma.cuh)
-    drb_launch(pfmma::k_grouped<0>, dim3(dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, gu_q, gu_sm,
+    drb_launch(pfmma::k_grouped<0>, dim3(2 * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, gu_q, gu_sm,
                (const void*)xp, (void*)act, offsets, counts, E);
-    drb_launch(pfmma::k_grouped<1>, dim3(dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, d_q, d_sm,
+    drb_launch(pfmma::k_grouped<1>, dim3(2 * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, d_q, d_sm,
                (const void*)act, (void*)y, offsets, counts, E);
     return 0;
   }

@@ -31,14 +31,16 @@ constexpr int H = 2048, I = 512;
 constexpr int THREADS = 256;
 constexpr int TILE_M = 128;
 constexpr int KC = 64;                              // K chunk = one swizzle atom of fp16 = one int4 scale group
-constexpr int MAX_N = 256;                          // tokens per accumulator
+constexpr int MAX_N = 128;                          // tokens per accumulator (one work item)
+constexpr int NG = 4;                               // token groups enumerated per expert; the last one loops on
 constexpr int A_BYTES = TILE_M * KC * 2;            // 16 KB
-constexpr int B_BYTES = MAX_N * KC * 2;             // 32 KB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;      // 48 KB
+constexpr int B_BYTES = MAX_N * KC * 2;             // 16 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;      // 32 KB: two blocks fit a multiprocessor
 constexpr int STAGES = 3;
 constexpr int CTL_BYTES = 1024;
-constexpr size_t SMEM_BYTES = CTL_BYTES + 1024 /* alignment slack */ + (size_t)STAGES * STAGE_BYTES;
-constexpr int TMEM_COLS = 256;
+constexpr size_t SMEM_BYTES = CTL_BYTES + 1024 /* alignment slack */ + (size_t)STAGES * STAGE_BYTES;  // 98 KB
+constexpr int TMEM_COLS = 128;
+constexpr int BPT = MAX_N * 8 / THREADS;             // 16-byte B chunks per thread and K chunk: 4
 
 struct Ctl {
   uint64_t empty[STAGES];  // a stage's MMAs have completed
@@ -150,7 +152,7 @@ DRB_DEV uint4 f16x8_perm(const uint4& v) {
 //   src: gate/up: xp bf16 [slots, H];  down: act fp16 [slots, I]
 //   dst: gate/up: act fp16 [slots, I]; down: y f32 [slots, H]
 template <int GEMM>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 2)
     k_grouped(const uint8_t* __restrict__ Q, const __half2* __restrict__ SM, const void* __restrict__ src, void* __restrict__ dst,
               const int* __restrict__ offsets, const int* __restrict__ counts, int E) {
   constexpr int K = GEMM == 0 ? H : I;
@@ -181,31 +183,51 @@ __global__ void __launch_bounds__(THREADS, 1)
   // This thread's share of the A tile: tile row t / 2, 32 of the chunk's 64 nibbles.
   const int arow = threadIdx.x >> 1, ahalf = threadIdx.x & 1;
 
-  for (int item = blockIdx.x; item < E * MT; item += gridDim.x) {
-    const int e = item / MT, mt = item % MT;
+  for (int item = blockIdx.x; item < E * NG * MT; item += gridDim.x) {
+    const int mt = item % MT, g = (item / MT) % NG, e = item / (MT * NG);
     const int cnt = counts[e];
-    if (cnt == 0) continue;
+    if (g * MAX_N >= cnt) continue;
     const int off = offsets[e];
     // weight row of tile row r: gate/up interleaves gate j (even r) with up j (odd r)
     const int wrow = GEMM == 0 ? (arow & 1) * I + mt * (TILE_M / 2) + (arow >> 1) : mt * TILE_M + arow;
     const uint8_t* qrow = Q + ((size_t)e * R + wrow) * (K / 2) + ahalf * 16;
     const __half2* smrow = SM + ((size_t)e * R + wrow) * (K / 64);
 
-    for (int n0 = 0; n0 < cnt; n0 += MAX_N) {
+    // token group g; the last enumerated group also takes whatever lies beyond NG * MAX_N tokens
+    for (int n0 = g * MAX_N; n0 < cnt; n0 += MAX_N) {
+      if (n0 > g * MAX_N && g != NG - 1) break;
       const int nt = min(MAX_N, cnt - n0);
       const int N = (nt + 15) & ~15;
       const uint32_t idesc = instr_desc(N);
+      // B source of this thread's i-th 16-byte chunk of K chunk kc (token n = idx / 8, chunk c = idx % 8)
+      auto load_b = [&](int kc, int i) -> uint4 {
+        const int idx = threadIdx.x + i * THREADS;
+        const int n = idx >> 3, c = idx & 7;
+        if (n >= nt) return make_uint4(0u, 0u, 0u, 0u);
+        if (GEMM == 0) return __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(src) + (size_t)(off + n0 + n) * H + kc * KC) + c);
+        return __ldcg(reinterpret_cast<const uint4*>(static_cast<const __half*>(src) + (size_t)(off + n0 + n) * I + kc * KC) + c);
+      };
+      const int nb = (nt * 8 + THREADS - 1) / THREADS;  // chunks this block's threads each convert (1..BPT)
       uint4 qn = __ldg(reinterpret_cast<const uint4*>(qrow));
       __half2 smn = __ldg(smrow);
+      uint4 bn[BPT];
+#pragma unroll
+      for (int i = 0; i < BPT; ++i) bn[i] = i < nb ? load_b(0, i) : make_uint4(0u, 0u, 0u, 0u);
       for (int kc = 0; kc < NKC; ++kc, ++chunk_no) {
         const int s = chunk_no % STAGES;
         unsigned char* As = stages + (size_t)s * STAGE_BYTES;
         unsigned char* Bs = As + A_BYTES;
         const uint4 qv = qn;
         const __half2 smv = smn;
-        if (kc + 1 < NKC) {  // next chunk's weights are in flight while this one is converted
+        uint4 bv[BPT];
+#pragma unroll
+        for (int i = 0; i < BPT; ++i) bv[i] = bn[i];
+        if (kc + 1 < NKC) {  // the next chunk's weights and activations are in flight while this one is converted
           qn = __ldg(reinterpret_cast<const uint4*>(qrow + (kc + 1) * (KC / 2)));
           smn = __ldg(smrow + kc + 1);
+#pragma unroll
+          for (int i = 0; i < BPT; ++i)
+            if (i < nb) bn[i] = load_b(kc + 1, i);
         }
         // the MMAs that read this stage STAGES chunks ago must have completed
         if (chunk_no >= STAGES && !dead) dead = !mbar_wait(&ctl.empty[s], ((chunk_no / STAGES) - 1) & 1, DRB_ERR_TMEM);
@@ -217,15 +239,11 @@ __global__ void __launch_bounds__(THREADS, 1)
           for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(As + swz_off(arow, 4 * ahalf + j)) = dequant8(w[j], s2, m2);
         }
         // ---- B: nt tokens x 64 activations, eight 16-byte chunks per token
-        for (int i = threadIdx.x; i < nt * 8; i += THREADS) {
-          const int n = i >> 3, c = i & 7;
-          uint4 v;
-          if (GEMM == 0) {
-            v = bf16x8_to_f16_perm(__ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(src) + (size_t)(off + n0 + n) * H + kc * KC) + c));
-          } else {
-            v = f16x8_perm(*(reinterpret_cast<const uint4*>(static_cast<const __half*>(src) + (size_t)(off + n0 + n) * I + kc * KC) + c));
-          }
-          *reinterpret_cast<uint4*>(Bs + swz_off(n, c)) = v;
+#pragma unroll
+        for (int i = 0; i < BPT; ++i) {
+          const int idx = threadIdx.x + i * THREADS;
+          if (i < nb && (idx >> 3) < nt)
+            *reinterpret_cast<uint4*>(Bs + swz_off(idx >> 3, idx & 7)) = GEMM == 0 ? bf16x8_to_f16_perm(bv[i]) : f16x8_perm(bv[i]);
         }
         fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
         __syncthreads();

@@ -157,7 +157,7 @@ class MoePrefill:
         self.ap = DevBuf(n * topk * i * 2)
         self.yp = DevBuf(n * topk * h * 4)
         self.wbuf = DevBuf(2 * i * h * 2)
-        self.logit_bias: DevBuf | None = None  # tests: [E] f32 added to the router logits (not in the reference)
+        self.logit_bias: DevBuf | None = None  # [n, E + 1] f32 rows the router GEMM accumulates onto (not in the reference)
 
     def gemm_q8(self, a, w, c, m: int, beta: float) -> None:
         """C = A . dequant(W)^T + beta C for a q8 weight. src/engine.rs:351-355."""
@@ -166,20 +166,32 @@ class MoePrefill:
         check(self.l.dr_gemm(self.blas, a, self.wbuf.at(0), c, m, w.n, w.k, beta), "gemm")
 
     def run(self, x: np.ndarray, logit_bias: np.ndarray | None = None) -> np.ndarray:
-        """x [n, H] f32 -> x + moe(rmsnorm(x, post_norm)). src/engine.rs:499-500 and 544-604."""
-        l, st, layer = self.l, self.st.raw, self.layer
+        """x [n, H] f32 on the host -> x + moe(rmsnorm(x, post_norm)). src/engine.rs:499-500 and 544-604.
+        logit_bias ([E] f32, tests and the benchmark's Zipf routing only) is added to the router logits."""
         n, h = x.shape
-        e, topk, i = layer.experts, self.topk, layer.inter
+        e = self.layer.experts
         assert n <= self.max_rows
         self.x.upload(x.astype(np.float32), self.st)
-        launched(l.dr_rmsnorm(self.x.at(0), layer.post_norm.at(0), NULL, self.hn_b.at(0), n, h, self.eps, st), "rmsnorm")
-        check(l.dr_gemm(self.blas, self.hn_b.at(0), layer.router.at(0), self.rlog.at(0), n, e + 1, h, 0.0), "gemm")
         if logit_bias is not None:
-            # Test-only: popularity bias on the logits, applied on the host between the reference's two calls.
-            self.st.sync()
-            lg = self.rlog.download(np.float32, n * (e + 1), self.st).reshape(n, e + 1)
-            lg[:, :e] += logit_bias.astype(np.float32)
-            self.rlog.upload(lg, self.st)
+            rows = np.zeros((n, e + 1), dtype=np.float32)
+            rows[:, :e] = logit_bias.astype(np.float32)
+            self.logit_bias = DevBuf.from_array(rows, self.st)
+        else:
+            self.logit_bias = None
+        self.run_device(n)
+        return self.x.download(np.float32, n * h, self.st).reshape(n, h)
+
+    def run_device(self, n: int) -> None:
+        """The block on the n rows already in self.x (device), in place; call for call the reference's sequence.
+        With a logit bias the router GEMM accumulates onto the bias rows (beta = 1) instead of overwriting."""
+        l, st, layer = self.l, self.st.raw, self.layer
+        h, e, topk, i = layer.hidden, layer.experts, self.topk, layer.inter
+        launched(l.dr_rmsnorm(self.x.at(0), layer.post_norm.at(0), NULL, self.hn_b.at(0), n, h, self.eps, st), "rmsnorm")
+        beta = 0.0
+        if self.logit_bias is not None:
+            check(l.dr_d2d(self.rlog.at(0), self.logit_bias.at(0), n * (e + 1) * 4, st), "d2d")
+            beta = 1.0
+        check(l.dr_gemm(self.blas, self.hn_b.at(0), layer.router.at(0), self.rlog.at(0), n, e + 1, h, beta), "gemm")
         launched(l.dr_moe_topk(self.rlog.at(0), n, e, topk, e + 1, self.idx.at(0), self.wts.at(0), self.sgate.at(0), st), "moe_topk")
         # Shared expert.
         self.gemm_q8(self.hn_b.at(0), layer.shared_gate_up, self.shh.at(0), n, 0.0)
@@ -203,8 +215,6 @@ class MoePrefill:
         launched(
             l.dr_moe_combine(self.x.at(0), self.yp.at(0), self.slot_of.at(0), self.wts.at(0), self.sgate.at(0),
                              self.sh_out.at(0), n, topk, h, st), "moe_combine")
-        return self.x.download(np.float32, n * h, self.st).reshape(n, h)
-
 
 class MoeStackDecoder:
     """The same stack as MoeDecoder through drb_moe_stack_decode: one persistent kernel per step."""

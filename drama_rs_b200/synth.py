@@ -131,10 +131,11 @@ def make_q8(seed: int, n: int, k: int, std: float = 0.005) -> tuple[np.ndarray, 
     return _q8(rng, n, k, std)
 
 
-def zipf_router_bias(seed: int, experts: int, s: float = 1.1, strength: float = 1.0) -> np.ndarray:
+def zipf_router_bias(seed: int, experts: int, s: float = 1.1, strength: float = 0.4) -> np.ndarray:
     """Additive router-logit bias that makes expert popularity follow Zipf(s) over a random ranking.
 
-    Returned as an f32 [experts] vector b_e = -s * ln(rank_e) * strength.
+    Returned as an f32 [experts] vector b_e = -s * ln(rank_e) * strength. strength 0.4 is calibrated against the
+    synthetic router (logit spread ~0.9): 300 rows x top-8 then touch ~234 of 256 experts, median group 4.
     """
     rng = np.random.Generator(np.random.PCG64(seed ^ 0x21BF))
     rank = rng.permutation(experts).astype(np.float64) + 1.0

@@ -256,7 +256,7 @@ REL_PREFILL = 4e-3
 def test_moe_prefill_zipf_300(st, layers):
     host, dev = layers(2)
     x = synth.make_x(33, 300, 2048)
-    bias = synth.zipf_router_bias(33, 256, 1.1, 1.0)
+    bias = synth.zipf_router_bias(33, 256, 1.1)
     pre = MoePrefill(dev, 300, st=st)
     y = pre.run(x, logit_bias=bias)
     xh = orc.round_bf16(orc.rmsnorm(x, host["post_norm"], 1e-6))
