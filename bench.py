@@ -299,6 +299,42 @@ def gemv_extra(torch, st, ext_stream) -> list:
     return out
 
 
+def prefill_ep_extra(torch, dist, layer, st, ext_stream, rank: int, world: int) -> dict:
+    """Configuration 3 expert-parallel: the 300 rows are split over the ranks, every rank owns 256 / N experts of
+    the (identical) layer, rows travel to their experts and back with NCCL all-to-all (drama_rs_b200/ep.py).
+    Timed on the device with events on every rank; the caller takes the max over ranks."""
+    from drama_rs_b200 import ep
+
+    rows = 300
+    lo, hi = rows * rank // world, rows * (rank + 1) // world
+    x_all = synth.make_x(33, rows, SHAPE.hidden)
+    ops = ep.EpGpuOps(layer, rank, world, rows, st=st)
+    with torch.cuda.stream(ops.stream):
+        ops.logit_bias = torch.from_numpy(synth.zipf_router_bias(33, SHAPE.experts, 1.1)).cuda()
+        x = torch.from_numpy(x_all[lo:hi].copy()).cuda()
+        for _ in range(3):
+            y = ep.ep_moe_block(x.clone(), ops, SHAPE.experts, SHAPE.topk)
+        torch.cuda.synchronize()
+        dist.barrier()
+        iters = 20
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(ext_stream)
+        for _ in range(iters):
+            y = ep.ep_moe_block(x.clone(), ops, SHAPE.experts, SHAPE.topk)
+        e1.record(ext_stream)
+        torch.cuda.synchronize()
+        dist.barrier()
+    us = e0.elapsed_time(e1) / iters * 1e3
+    t = torch.tensor([us], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    # checksum of the result, summed over ranks: identical for every N when the routing and the sums are
+    cs = torch.tensor([float(y.double().sum())], dtype=torch.float64, device="cuda")
+    dist.all_reduce(cs)
+    return {"workload": "prefill_300rows_zipf1.1_one_layer_expert_parallel", "rows": rows, "experts_per_rank": SHAPE.experts // world,
+            "us_layer": float(t[0]), "rows_per_s": rows / float(t[0]) * 1e6, "output_sum": float(cs[0]),
+            "exchange": "NCCL all_to_all_single, bf16 rows out, f32 rows back"}
+
+
 def run_gpu(args) -> None:
     import torch
 
@@ -389,7 +425,13 @@ def run_gpu(args) -> None:
     ms, ms_e2e = float(t[0]), float(t[1])
     word = C.c_uint(0)
     lib.drb_device_error(C.byref(word))
+    ep_info = None
+    if world > 1 and not args.no_extras:
+        same = device_layers(torch, 1, 4321, st)[0]  # the same seed on every rank: identical weights
+        ep_info = prefill_ep_extra(torch, dist, same, st, ext_stream, rank, world)
     if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
         return
 
     step_ms = ms / args.steps
@@ -406,6 +448,7 @@ def run_gpu(args) -> None:
         "config": {"workload": "decode_stack40_b1", "layers": args.layers, "hidden": SHAPE.hidden, "experts": SHAPE.experts,
                    "topk": SHAPE.topk, "inter": SHAPE.inter, "weights": "int4 g64 (scale,min) routed + int8 g128 shared",
                    "graph": "one CUDA graph per step, 3 kernels per layer", "replicas": world,
+                   "multi_gpu": "batch-1 decode does not shard: N independent replicas, no collective; the expert-parallel path is reported under prefill_expert_parallel",
                    "cache": "inputs larger than L2: 736 MB of weights read per step, 18.1 GB resident"},
         "hbm_gbs": gbs,
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
@@ -419,12 +462,16 @@ def run_gpu(args) -> None:
         "clocks": clocks.summary(),
         "device_error_word": int(word.value),
     }
+    if ep_info is not None:
+        line["prefill_expert_parallel"] = ep_info
     if not args.no_extras:
         line["prefill"] = prefill_extra(torch, layers, st, ext_stream)
         line["gemv_q8_sweep"] = gemv_extra(torch, st, ext_stream)
     if not args.no_cpu:
         line["cpu_baseline"] = cpu_decode_baseline()
     print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def main() -> None:

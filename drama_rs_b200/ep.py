@@ -112,6 +112,7 @@ class EpGpuOps:
         check(self.l.dr_cublas_create(C.byref(self.blas), self.st.raw), "cublas_create")
         self.wbuf = torch.empty(2 * layer.inter * layer.hidden, dtype=torch.bfloat16, device="cuda")
         self.stream = torch.cuda.ExternalStream(self.st.raw.value)
+        self.logit_bias = None  # optional [E] f32 tensor added to the router logits (benchmark's Zipf routing)
 
     def _p(self, t: torch.Tensor):
         return self.C.c_void_p(t.data_ptr())
@@ -134,8 +135,12 @@ class EpGpuOps:
         NULL = self.C.c_void_p(0)
         hn_b = torch.empty((n, h), dtype=torch.bfloat16, device="cuda")
         launched(l.dr_rmsnorm(self._p(x), ly.post_norm.at(0), NULL, self._p(hn_b), n, h, self.eps, st), "rmsnorm")
-        rlog = torch.empty((n, e + 1), dtype=torch.float32, device="cuda")
-        check(l.dr_gemm(self.blas, self._p(hn_b), ly.router.at(0), self._p(rlog), n, e + 1, h, 0.0), "gemm")
+        rlog = torch.zeros((n, e + 1), dtype=torch.float32, device="cuda")
+        beta = 0.0
+        if self.logit_bias is not None:  # the GEMM accumulates onto the bias rows
+            rlog[:, :e] = self.logit_bias
+            beta = 1.0
+        check(l.dr_gemm(self.blas, self._p(hn_b), ly.router.at(0), self._p(rlog), n, e + 1, h, beta), "gemm")
         idx = torch.empty((n, topk), dtype=torch.int32, device="cuda")
         wts = torch.empty((n, topk), dtype=torch.float32, device="cuda")
         sgate = torch.empty(n, dtype=torch.float32, device="cuda")
