@@ -28,7 +28,9 @@
 namespace pfmma {
 
 constexpr int H = 2048, I = 512;
-constexpr int THREADS = 256;
+constexpr int PRODUCER_WARPS = 8;
+constexpr int PRODUCERS = PRODUCER_WARPS * 32;
+constexpr int THREADS = PRODUCERS + 32;             // + the MMA-issuing warp
 constexpr int TILE_M = 128;
 constexpr int KC = 64;                              // K chunk = one swizzle atom of fp16 = one int4 scale group
 constexpr int MAX_N = 128;                          // tokens per accumulator (one work item)
@@ -40,11 +42,13 @@ constexpr int STAGES = 3;
 constexpr int CTL_BYTES = 1024;
 constexpr size_t SMEM_BYTES = CTL_BYTES + 1024 /* alignment slack */ + (size_t)STAGES * STAGE_BYTES;  // 98 KB
 constexpr int TMEM_COLS = 128;
-constexpr int BPT = MAX_N * 8 / THREADS;             // 16-byte B chunks per thread and K chunk: 4
+constexpr int BPT = MAX_N * 8 / PRODUCERS;             // 16-byte B chunks per thread and K chunk: 4
 
 struct Ctl {
+  uint64_t full[STAGES];   // a stage has been filled (one arrival per producer warp)
   uint64_t empty[STAGES];  // a stage's MMAs have completed
   uint64_t done;           // all MMAs of the current accumulator have completed
+  uint64_t tfree;          // the accumulator has been read out (one arrival per epilogue warp)
   uint32_t tmem_base;
 };
 
@@ -151,6 +155,8 @@ DRB_DEV uint4 f16x8_perm(const uint4& v) {
 //   Q  [E, R, K/2] nibbles, SM [E, R, K/64] (scale, min);  R = 2I, K = H for gate/up;  R = H, K = I for down.
 //   src: gate/up: xp bf16 [slots, H];  down: act fp16 [slots, I]
 //   dst: gate/up: act fp16 [slots, I]; down: y f32 [slots, H]
+// Warps 0-7 convert operands into the stage ring and run the epilogue; warp 8 issues the MMAs. They meet only
+// on mbarriers: full[s] (8 warp arrivals), empty[s] and done (tcgen05.commit), tfree (accumulator drained).
 template <int GEMM>
 __global__ void __launch_bounds__(THREADS, 2)
     k_grouped(const uint8_t* __restrict__ Q, const __half2* __restrict__ SM, const void* __restrict__ src, void* __restrict__ dst,
@@ -159,6 +165,7 @@ __global__ void __launch_bounds__(THREADS, 2)
   constexpr int R = GEMM == 0 ? 2 * I : H;
   constexpr int MT = R / TILE_M;  // tiles per expert: 8 / 16
   constexpr int NKC = K / KC;     // 32 / 8
+  constexpr int ESZ = 2;          // both activation sources are 16-bit
   extern __shared__ unsigned char dyn_raw[];
   unsigned char* dyn = reinterpret_cast<unsigned char*>(((uintptr_t)dyn_raw + 1023) & ~(uintptr_t)1023);
   Ctl& ctl = *reinterpret_cast<Ctl*>(dyn);
@@ -167,127 +174,167 @@ __global__ void __launch_bounds__(THREADS, 2)
 
   pdl_wait();
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) mbar_init(&ctl.empty[s], 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&ctl.empty[s], 1);
+      mbar_init(&ctl.full[s], PRODUCER_WARPS);
+    }
     mbar_init(&ctl.done, 1);
+    mbar_init(&ctl.tfree, PRODUCER_WARPS);
     mbar_fence_init();
   }
-  if (warp == 0) tmem_alloc(&ctl.tmem_base, TMEM_COLS);
+  if (warp == PRODUCER_WARPS) tmem_alloc(&ctl.tmem_base, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = ctl.tmem_base;
 
   bool dead = false;      // a wait ran out once: stop waiting (the error word is set; results are void)
-  unsigned chunk_no = 0;  // chunks issued so far by this block: selects stage and mbarrier phase
-  unsigned acc_no = 0;    // accumulators finished so far: phase of `done`
-  // This thread's share of the A tile: tile row t / 2, 32 of the chunk's 64 nibbles.
-  const int arow = threadIdx.x >> 1, ahalf = threadIdx.x & 1;
+  unsigned chunk_no = 0;  // chunks so far: selects stage and mbarrier phase (same sequence in every warp)
+  unsigned acc_no = 0;    // accumulators so far: phase of `done` and `tfree`
 
-  for (int item = blockIdx.x; item < E * NG * MT; item += gridDim.x) {
-    const int mt = item % MT, g = (item / MT) % NG, e = item / (MT * NG);
-    const int cnt = counts[e];
-    if (g * MAX_N >= cnt) continue;
-    const int off = offsets[e];
-    // weight row of tile row r: gate/up interleaves gate j (even r) with up j (odd r)
-    const int wrow = GEMM == 0 ? (arow & 1) * I + mt * (TILE_M / 2) + (arow >> 1) : mt * TILE_M + arow;
-    const uint8_t* qrow = Q + ((size_t)e * R + wrow) * (K / 2) + ahalf * 16;
-    const __half2* smrow = SM + ((size_t)e * R + wrow) * (K / 64);
+  if (warp == PRODUCER_WARPS) {
+    // ================= MMA warp =================
+    for (int item = blockIdx.x; item < E * NG * MT; item += gridDim.x) {
+      const int g = (item / MT) % NG, e = item / (MT * NG);
+      const int cnt = counts[e];
+      if (g * MAX_N >= cnt) continue;
+      for (int n0 = g * MAX_N; n0 < cnt; n0 += MAX_N) {
+        if (n0 > g * MAX_N && g != NG - 1) break;
+        const int N = (min(MAX_N, cnt - n0) + 15) & ~15;
+        const uint32_t idesc = instr_desc(N);
+        // the previous accumulator must have been read out
+        if (acc_no > 0 && !dead) dead = !mbar_wait(&ctl.tfree, (acc_no - 1) & 1, DRB_ERR_TMEM);
+        tc_fence_after();
+        for (int kc = 0; kc < NKC; ++kc, ++chunk_no) {
+          const int s = chunk_no % STAGES;
+          if (!dead) dead = !mbar_wait(&ctl.full[s], (chunk_no / STAGES) & 1, DRB_ERR_TMEM);
+          tc_fence_after();
+          if (lane == 0) {
+            unsigned char* As = stages + (size_t)s * STAGE_BYTES;
+            const uint64_t ad = smem_desc(As), bd = smem_desc(As + A_BYTES);
+#pragma unroll
+            for (int k16 = 0; k16 < KC / 16; ++k16) mma_f16(tmem, ad + 2 * k16, bd + 2 * k16, idesc, kc > 0 || k16 > 0);
+            mma_commit(&ctl.empty[s]);
+            if (kc == NKC - 1) mma_commit(&ctl.done);
+          }
+          __syncwarp();
+        }
+        ++acc_no;
+      }
+    }
+  } else {
+    // ================= producer / epilogue warps =================
+    // This thread's share of the A tile: tile row t / 2, 32 of the chunk's 64 nibbles -> four 16-byte chunks.
+    const int arow = threadIdx.x >> 1, ahalf = threadIdx.x & 1;
+    uint32_t a_off[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) a_off[j] = swz_off(arow, 4 * ahalf + j);
+    // Its share of the B tile: 16-byte chunk c of token n for idx = t + i * 256.
+    uint32_t b_off[BPT];
+#pragma unroll
+    for (int i = 0; i < BPT; ++i) b_off[i] = A_BYTES + swz_off((threadIdx.x + i * PRODUCERS) >> 3, threadIdx.x & 7);
+    const int q4 = warp & 3;       // tensor-memory lane quarter this warp may read
+    const int r = q4 * 32 + lane;  // tile row in the epilogue
 
-    // token group g; the last enumerated group also takes whatever lies beyond NG * MAX_N tokens
-    for (int n0 = g * MAX_N; n0 < cnt; n0 += MAX_N) {
-      if (n0 > g * MAX_N && g != NG - 1) break;
-      const int nt = min(MAX_N, cnt - n0);
-      const int N = (nt + 15) & ~15;
-      const uint32_t idesc = instr_desc(N);
-      // B source of this thread's i-th 16-byte chunk of K chunk kc (token n = idx / 8, chunk c = idx % 8)
-      auto load_b = [&](int kc, int i) -> uint4 {
-        const int idx = threadIdx.x + i * THREADS;
-        const int n = idx >> 3, c = idx & 7;
-        if (n >= nt) return make_uint4(0u, 0u, 0u, 0u);
-        if (GEMM == 0) return __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(src) + (size_t)(off + n0 + n) * H + kc * KC) + c);
-        return __ldcg(reinterpret_cast<const uint4*>(static_cast<const __half*>(src) + (size_t)(off + n0 + n) * I + kc * KC) + c);
-      };
-      const int nb = (nt * 8 + THREADS - 1) / THREADS;  // chunks this block's threads each convert (1..BPT)
-      uint4 qn = __ldg(reinterpret_cast<const uint4*>(qrow));
-      __half2 smn = __ldg(smrow);
-      uint4 bn[BPT];
-#pragma unroll
-      for (int i = 0; i < BPT; ++i) bn[i] = i < nb ? load_b(0, i) : make_uint4(0u, 0u, 0u, 0u);
-      for (int kc = 0; kc < NKC; ++kc, ++chunk_no) {
-        const int s = chunk_no % STAGES;
-        unsigned char* As = stages + (size_t)s * STAGE_BYTES;
-        unsigned char* Bs = As + A_BYTES;
-        const uint4 qv = qn;
-        const __half2 smv = smn;
-        uint4 bv[BPT];
-#pragma unroll
-        for (int i = 0; i < BPT; ++i) bv[i] = bn[i];
-        if (kc + 1 < NKC) {  // the next chunk's weights and activations are in flight while this one is converted
-          qn = __ldg(reinterpret_cast<const uint4*>(qrow + (kc + 1) * (KC / 2)));
-          smn = __ldg(smrow + kc + 1);
-#pragma unroll
-          for (int i = 0; i < BPT; ++i)
-            if (i < nb) bn[i] = load_b(kc + 1, i);
-        }
-        // the MMAs that read this stage STAGES chunks ago must have completed
-        if (chunk_no >= STAGES && !dead) dead = !mbar_wait(&ctl.empty[s], ((chunk_no / STAGES) - 1) & 1, DRB_ERR_TMEM);
-        // ---- A: 32 nibbles -> 32 fp16 = four 16-byte chunks of the tile row
-        {
-          const __half2 s2 = __half2half2(__low2half(smv)), m2 = __half2half2(__high2half(smv));
-          const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(As + swz_off(arow, 4 * ahalf + j)) = dequant8(w[j], s2, m2);
-        }
-        // ---- B: nt tokens x 64 activations, eight 16-byte chunks per token
+    for (int item = blockIdx.x; item < E * NG * MT; item += gridDim.x) {
+      const int mt = item % MT, g = (item / MT) % NG, e = item / (MT * NG);
+      const int cnt = counts[e];
+      if (g * MAX_N >= cnt) continue;
+      const int off = offsets[e];
+      // weight row of tile row r: gate/up interleaves gate j (even r) with up j (odd r)
+      const int wrow = GEMM == 0 ? (arow & 1) * I + mt * (TILE_M / 2) + (arow >> 1) : mt * TILE_M + arow;
+      const uint8_t* qrow = Q + ((size_t)e * R + wrow) * (K / 2) + ahalf * 16;
+      const __half2* smrow = SM + ((size_t)e * R + wrow) * (K / 64);
+
+      // token group g; the last enumerated group also takes whatever lies beyond NG * MAX_N tokens
+      for (int n0 = g * MAX_N; n0 < cnt; n0 += MAX_N) {
+        if (n0 > g * MAX_N && g != NG - 1) break;
+        const int nt = min(MAX_N, cnt - n0);
+        const int N = (nt + 15) & ~15;
+        // activation rows of this thread's B chunks (nullptr beyond the group)
+        const unsigned char* bsrc[BPT];
 #pragma unroll
         for (int i = 0; i < BPT; ++i) {
-          const int idx = threadIdx.x + i * THREADS;
-          if (i < nb && (idx >> 3) < nt)
-            *reinterpret_cast<uint4*>(Bs + swz_off(idx >> 3, idx & 7)) = GEMM == 0 ? bf16x8_to_f16_perm(bv[i]) : f16x8_perm(bv[i]);
+          const int n = (threadIdx.x + i * PRODUCERS) >> 3;
+          bsrc[i] = n < nt ? static_cast<const unsigned char*>(src) + ((size_t)(off + n0 + n) * K) * ESZ + (threadIdx.x & 7) * 16 : nullptr;
         }
-        fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
-        __syncthreads();
-        if (threadIdx.x == 0) {
-          tc_fence_after();
-          const uint64_t ad = smem_desc(As), bd = smem_desc(Bs);
+        auto load_b = [&](int kc, int i) -> uint4 {
+          if (!bsrc[i]) return make_uint4(0u, 0u, 0u, 0u);
+          const uint4* p = reinterpret_cast<const uint4*>(bsrc[i] + (size_t)kc * KC * ESZ);
+          return GEMM == 0 ? __ldg(p) : __ldcg(p);
+        };
+        // weights two chunks ahead, activations one chunk ahead, all in registers
+        uint4 q0 = __ldg(reinterpret_cast<const uint4*>(qrow));
+        __half2 sm0 = __ldg(smrow);
+        uint4 q1 = NKC > 1 ? __ldg(reinterpret_cast<const uint4*>(qrow + KC / 2)) : q0;
+        __half2 sm1 = NKC > 1 ? __ldg(smrow + 1) : sm0;
+        uint4 bn[BPT];
 #pragma unroll
-          for (int k16 = 0; k16 < KC / 16; ++k16) mma_f16(tmem, ad + 2 * k16, bd + 2 * k16, idesc, kc > 0 || k16 > 0);
-          mma_commit(&ctl.empty[s]);
-          if (kc == NKC - 1) mma_commit(&ctl.done);
-        }
-      }
-      // ---- epilogue: accumulator [128 tile rows (lanes), N tokens (columns)]
-      if (!dead) dead = !mbar_wait(&ctl.done, acc_no & 1, DRB_ERR_TMEM);
-      ++acc_no;
-      tc_fence_after();
-      const int q4 = warp & 3;             // this warp reads tensor-memory lanes 32 q4 .. 32 q4 + 31
-      const int r = q4 * 32 + lane;        // tile row
-      for (int c0 = (warp >> 2) * 16; c0 < N; c0 += 32) {  // warps 0-3 and 4-7 alternate 16-column groups
-        uint32_t v[16];
-        tmem_ld16(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0, v);
-        if (GEMM == 0) {
-          __half* act = static_cast<__half*>(dst);
-          const int j = mt * (TILE_M / 2) + (r >> 1);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float mine = __uint_as_float(v[i]);
-            const float other = __shfl_xor_sync(0xffffffffu, mine, 1);  // even lane: gate, odd lane: up
-            if ((lane & 1) == 0 && c0 + i < nt) act[(size_t)(off + n0 + c0 + i) * I + j] = __float2half_rn(silu_f(mine) * other);
+        for (int i = 0; i < BPT; ++i) bn[i] = load_b(0, i);
+        for (int kc = 0; kc < NKC; ++kc, ++chunk_no) {
+          const int s = chunk_no % STAGES;
+          unsigned char* st = stages + (size_t)s * STAGE_BYTES;
+          const uint4 qv = q0;
+          const __half2 smv = sm0;
+          q0 = q1, sm0 = sm1;
+          if (kc + 2 < NKC) {
+            q1 = __ldg(reinterpret_cast<const uint4*>(qrow + (kc + 2) * (KC / 2)));
+            sm1 = __ldg(smrow + kc + 2);
           }
-        } else {
-          float* y = static_cast<float*>(dst);
+          uint4 bv[BPT];
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            if (c0 + i < nt) y[(size_t)(off + n0 + c0 + i) * H + mt * TILE_M + r] = __uint_as_float(v[i]);
+          for (int i = 0; i < BPT; ++i) bv[i] = bn[i];
+          if (kc + 1 < NKC) {
+#pragma unroll
+            for (int i = 0; i < BPT; ++i) bn[i] = load_b(kc + 1, i);
+          }
+          // the MMAs that read this stage STAGES chunks ago must have completed
+          if (chunk_no >= STAGES && !dead) dead = !mbar_wait(&ctl.empty[s], ((chunk_no / STAGES) - 1) & 1, DRB_ERR_TMEM);
+          {
+            const __half2 s2 = __half2half2(__low2half(smv)), m2 = __half2half2(__high2half(smv));
+            const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(st + a_off[j]) = dequant8(w[j], s2, m2);
+          }
+#pragma unroll
+          for (int i = 0; i < BPT; ++i)
+            if (bsrc[i]) *reinterpret_cast<uint4*>(st + b_off[i]) = GEMM == 0 ? bf16x8_to_f16_perm(bv[i]) : f16x8_perm(bv[i]);
+          fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctl.full[s]);
         }
+        // ---- epilogue: accumulator [128 tile rows (lanes), N tokens (columns)]
+        if (!dead) dead = !mbar_wait(&ctl.done, acc_no & 1, DRB_ERR_TMEM);
+        ++acc_no;
+        tc_fence_after();
+        for (int c0 = (warp >> 2) * 16; c0 < N; c0 += 32) {  // warps 0-3 and 4-7 alternate 16-column groups
+          uint32_t v[16];
+          tmem_ld16(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0, v);
+          if (GEMM == 0) {
+            __half* act = static_cast<__half*>(dst);
+            const int j = mt * (TILE_M / 2) + (r >> 1);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float mine = __uint_as_float(v[i]);
+              const float other = __shfl_xor_sync(0xffffffffu, mine, 1);  // even lane: gate, odd lane: up
+              if ((lane & 1) == 0 && c0 + i < nt) act[(size_t)(off + n0 + c0 + i) * I + j] = __float2half_rn(silu_f(mine) * other);
+            }
+          } else {
+            float* y = static_cast<float*>(dst);
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (c0 + i < nt) y[(size_t)(off + n0 + c0 + i) * H + mt * TILE_M + r] = __uint_as_float(v[i]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl.tfree);  // this warp has drained its part of the accumulator
       }
-      tc_fence_before();
-      __syncthreads();  // everyone has read the accumulator before the next MMA overwrites it
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+  if (warp == PRODUCER_WARPS) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 static cudaError_t configure_all() {
