@@ -335,6 +335,43 @@ def prefill_ep_extra(torch, dist, layer, st, ext_stream, rank: int, world: int) 
             "exchange": "NCCL all_to_all_single, bf16 rows out, f32 rows back"}
 
 
+def decode64_ep_extra(torch, dist, layers, st, ext_stream, rank: int, world: int) -> dict:
+    """Configuration 4: 64 independent streams, one row each, through the whole stack; experts sharded
+    256 / N per GPU; per layer one all-to-all out and one back (uniform routing, no bias)."""
+    from drama_rs_b200 import ep
+
+    rows = 64
+    lo, hi = rows * rank // world, rows * (rank + 1) // world
+    x_all = synth.make_x(64, rows, SHAPE.hidden)
+    opss = [ep.EpGpuOps(ly, rank, world, rows, st=st) for ly in layers]
+    with torch.cuda.stream(opss[0].stream):
+        x0 = torch.from_numpy(x_all[lo:hi].copy()).cuda()
+
+        def step():
+            x = x0.clone()
+            for ops in opss:
+                x = ep.ep_moe_block(x, ops, SHAPE.experts, SHAPE.topk)
+            return x
+
+        step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        iters = 3
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(ext_stream)
+        for _ in range(iters):
+            y = step()
+        e1.record(ext_stream)
+        torch.cuda.synchronize()
+        dist.barrier()
+    us = e0.elapsed_time(e1) / iters * 1e3
+    t = torch.tensor([us], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"workload": "decode_64streams_stack_expert_parallel", "streams": rows, "layers": len(layers),
+            "us_per_step": float(t[0]), "us_per_layer": float(t[0]) / len(layers),
+            "stream_layers_per_s": rows * len(layers) / float(t[0]) * 1e6, "finite": bool(torch.isfinite(y).all())}
+
+
 def run_gpu(args) -> None:
     import torch
 
@@ -353,7 +390,7 @@ def run_gpu(args) -> None:
     lib = ffi.lib()  # raises if the CUDA library is missing: there is no fallback
     st = Stream()
     ext_stream = torch.cuda.ExternalStream(st.raw.value)
-    layers = device_layers(torch, args.layers, 1234 + 1000 * rank, st)
+    layers = device_layers(torch, args.layers, 1234, st)  # the same seed on every rank: replicas for decode, shards for the expert-parallel legs
     dec = MoeDecoder(layers, st=st)
     x0 = synth.make_x(99, 1, SHAPE.hidden)[0]
     x0_dev = torch.from_numpy(x0).cuda()
@@ -425,10 +462,10 @@ def run_gpu(args) -> None:
     ms, ms_e2e = float(t[0]), float(t[1])
     word = C.c_uint(0)
     lib.drb_device_error(C.byref(word))
-    ep_info = None
+    ep_info = ep_info64 = None
     if world > 1 and not args.no_extras:
-        same = device_layers(torch, 1, 4321, st)[0]  # the same seed on every rank: identical weights
-        ep_info = prefill_ep_extra(torch, dist, same, st, ext_stream, rank, world)
+        ep_info = prefill_ep_extra(torch, dist, layers[0], st, ext_stream, rank, world)
+        ep_info64 = decode64_ep_extra(torch, dist, layers, st, ext_stream, rank, world)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -464,6 +501,7 @@ def run_gpu(args) -> None:
     }
     if ep_info is not None:
         line["prefill_expert_parallel"] = ep_info
+        line["decode_64streams_expert_parallel"] = ep_info64
     if not args.no_extras:
         line["prefill"] = prefill_extra(torch, layers, st, ext_stream)
         line["gemv_q8_sweep"] = gemv_extra(torch, st, ext_stream)

@@ -232,8 +232,38 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// offsets[e] = sum of counts[0..e): the exclusive scan the reference does on the host between two launches
+// (src/engine.rs:567-574). One block, any number of experts.
+__global__ void __launch_bounds__(256) k_offsets(const int* __restrict__ counts, int E, int* __restrict__ offsets) {
+  pdl_wait();
+  __shared__ int warp_tot[8];
+  __shared__ int carry;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int base = 0; base < E; base += 256) {
+    const int i = base + threadIdx.x;
+    const int c = i < E ? counts[i] : 0;
+    int incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    int before = carry;
+    for (int w = 0; w < warp; ++w) before += warp_tot[w];
+    if (i < E) offsets[i] = before + incl - c;
+    __syncthreads();
+    if (threadIdx.x == 255) carry = before + incl;
+    __syncthreads();
+  }
+}
+
 static cudaError_t configure_all() {
   cudaError_t e;
+  if ((e = drb_carveout(k_offsets)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_count)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_permute)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_combine)) != cudaSuccess) return e;
@@ -251,6 +281,14 @@ static cudaError_t configure_all() {
 extern "C" int dr_moe_count(const int* idx, int n, int* counts, cudaStream_t st) {
   if (n <= 0) return 0;
   pf::k_count<<<(n + 255) / 256, 256, 0, st>>>(idx, n, counts);
+  return 0;
+}
+
+// No counterpart in the reference, which downloads the counts and scans them on the host (src/engine.rs:567-574):
+// with this call the prefill sequence needs no host round trip and can be captured in a graph.
+extern "C" int drb_moe_offsets(const int* counts, int e, int* offsets, cudaStream_t st) {
+  if (e <= 0) return 0;
+  pf::k_offsets<<<1, 256, 0, st>>>(counts, e, offsets);
   return 0;
 }
 

@@ -157,6 +157,7 @@ class MoePrefill:
         self.ap = DevBuf(n * topk * i * 2)
         self.yp = DevBuf(n * topk * h * 4)
         self.wbuf = DevBuf(2 * i * h * 2)
+        self.device_scan = False  # True: offsets by drb_moe_offsets on the device instead of the reference's host scan
         self.logit_bias: DevBuf | None = None  # [n, E + 1] f32 rows the router GEMM accumulates onto (not in the reference)
 
     def gemm_q8(self, a, w, c, m: int, beta: float) -> None:
@@ -200,9 +201,12 @@ class MoePrefill:
         # Group (row, k) pairs by expert.
         self.counts.zero(self.st)
         launched(l.dr_moe_count(self.idx.at(0), n * topk, self.counts.at(0), st), "moe_count")
-        counts = self.counts.download(np.int32, e, self.st)
-        offsets = (np.cumsum(counts) - counts).astype(np.int32)
-        self.offsets.upload(offsets, self.st)
+        if self.device_scan:
+            launched(l.drb_moe_offsets(self.counts.at(0), e, self.offsets.at(0), st), "moe_offsets")
+        else:
+            counts = self.counts.download(np.int32, e, self.st)
+            offsets = (np.cumsum(counts) - counts).astype(np.int32)
+            self.offsets.upload(offsets, self.st)
         self.fill.zero(self.st)
         launched(
             l.dr_moe_permute(self.idx.at(0), n, topk, self.offsets.at(0), self.fill.at(0), self.slot_of.at(0),

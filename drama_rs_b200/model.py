@@ -87,3 +87,34 @@ class MoeLayer:
         for b in (self.router, self.post_norm, self.shared_gate_up.q, self.shared_gate_up.s, self.shared_down.q,
                   self.shared_down.s, self.gate_up.q, self.gate_up.sm, self.down.q, self.down.sm):
             b.free()
+
+
+LAYER_TENSORS = ("moe.router", "post_norm", "moe.shared_gate_up.q8", "moe.shared_gate_up.s", "moe.shared_down.q8",
+                 "moe.shared_down.s", "moe.gate_up.q4", "moe.gate_up.sm", "moe.down.q4", "moe.down.sm")
+
+
+def save_layer_safetensors(t: dict[str, np.ndarray], path: str) -> None:
+    """Writes the MoE tensors of one layer under the converter's names (tools/convert.py:299-346 writes one
+    `layerNN.safetensors` per layer with exactly these keys next to the mixer's)."""
+    import torch
+    from safetensors.torch import save_file
+
+    out = {}
+    for k in LAYER_TENSORS:
+        a = np.ascontiguousarray(t[k])
+        out[k] = torch.from_numpy(a.view(np.int16)).view(torch.bfloat16) if k == "moe.router" else torch.from_numpy(a)
+    save_file(out, path)
+
+
+def load_layer_safetensors(path: str) -> dict[str, np.ndarray]:
+    """Reads the MoE tensors of a drama-rs-v1 `layerNN.safetensors` (src/model.rs:217-227 reads the same keys);
+    other tensors in the file (mixer, norms) are ignored. bf16 comes back as uint16 bit patterns."""
+    import torch
+    from safetensors import safe_open
+
+    out = {}
+    with safe_open(path, framework="pt", device="cpu") as f:
+        for k in LAYER_TENSORS:
+            v = f.get_tensor(k)
+            out[k] = v.view(torch.int16).numpy().view(np.uint16) if v.dtype == torch.bfloat16 else v.numpy()
+    return out

@@ -152,6 +152,9 @@ typedef struct {
 int drb_moe_stack_workspace_bytes(void);
 int drb_moe_stack_decode(const drb_moe_layer* layers, int n_layers, float* x, void* workspace, int e, int topk, int h,
                          int i, float eps, int* idx_trace, float* wts_trace, dr_stream st);
+/* offsets[e] = counts[0] + ... + counts[e-1] on the device: replaces the reference's host-side scan between
+ * dr_moe_count and dr_moe_permute (src/engine.rs:567-574), so the prefill sequence needs no host round trip. */
+int drb_moe_offsets(const int* counts, int e, int* offsets, dr_stream st);
 int dr_stream_destroy(dr_stream s);
 int dr_cublas_destroy(void* h);
 int drb_init(void);                    /* per-device setup; also run by the pre-capture hooks above */

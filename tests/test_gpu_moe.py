@@ -253,6 +253,26 @@ def test_moe_prefill_golden_rows40(st, layers, golden_dir):
 REL_PREFILL = 4e-3
 
 
+def test_moe_prefill_device_scan_and_graph(st, layers):
+    """With the offsets computed on the device the whole prefill block is one captured graph; its result equals
+    the reference-style sequence with the host scan."""
+    from drama_rs_b200.gpu import Graph
+
+    host, dev = layers(2)
+    x = synth.make_x(5, 64, 2048)
+    pre = MoePrefill(dev, 64, st=st)
+    y_host_scan = pre.run(x)
+    pre.device_scan = True
+    y_dev_scan = pre.run(x)
+    assert np.array_equal(y_host_scan, y_dev_scan)
+    g = Graph(st, lambda: pre.run_device(64))
+    pre.x.upload(x, st)
+    g.launch(st)
+    y_graph = pre.x.download(np.float32, 64 * 2048, st).reshape(64, 2048)
+    assert np.array_equal(y_graph, y_host_scan)
+    assert device_error_word() == 0
+
+
 def test_moe_prefill_zipf_300(st, layers):
     host, dev = layers(2)
     x = synth.make_x(33, 300, 2048)
