@@ -44,5 +44,25 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+HOST = os.path.join(HERE, "host")
+HOST_BIN = os.path.join(HOST, "moe_decode_main")
+
+
+def build_host(force: bool = False) -> str:
+    """Compiles the C++ host driver (g++ only: it sees the kernels through the C ABI, no CUDA headers)."""
+    build(force=False)
+    srcs = [os.path.join(HOST, f) for f in os.listdir(HOST) if f.endswith((".cpp", ".hpp"))]
+    srcs.append(os.path.join(os.path.dirname(HERE), "include", "dramakernels.h"))
+    if not force and os.path.exists(HOST_BIN) and all(os.path.getmtime(s) <= os.path.getmtime(HOST_BIN) for s in srcs):
+        return HOST_BIN
+    cmd = [os.environ.get("CXX", "g++"), "-std=c++17", "-O2", "-Wall", "-Wextra", "-o", HOST_BIN,
+           os.path.join(HOST, "moe_decode_main.cpp"), "-L" + HERE, "-ldramakernels", "-Wl,-rpath,$ORIGIN/.."]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("g++ failed:\n" + r.stdout + r.stderr)
+    return HOST_BIN
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_host(force="--force" in sys.argv))
