@@ -246,6 +246,23 @@ def prefill_extra(torch, layers, st, ext_stream) -> dict:
                                     SHAPE.experts, SHAPE.hidden, SHAPE.inter, st.raw), "moe_prefill")
 
     us_full = time_on_stream(torch, st, ext_stream, full, 20)
+    # The same layer with the offsets scanned on the device, captured once: rows restored by a device copy inside
+    # the graph, no host round trip between the launches.
+    from drama_rs_b200.gpu import DevBuf, Graph, check
+
+    x_keep = DevBuf.from_array(x.astype(np.float32), st)
+    graphs = []
+    for p in pres:
+        p.device_scan = True
+
+        def record(p=p):
+            check(p.l.dr_d2d(p.x.at(0), x_keep.at(0), rows * SHAPE.hidden * 4, st.raw), "d2d")
+            p.run_device(rows)
+
+        graphs.append(Graph(st, record))
+    us_graph = time_on_stream(torch, st, ext_stream, lambda i: graphs[i % len(graphs)].launch(st), 40)
+    for p in pres:
+        p.device_scan = False
     us_grouped = time_on_stream(torch, st, ext_stream, grouped, 40)
     wbytes = hit * SHAPE.expert_bytes
     flops = 2.0 * rows * SHAPE.topk * 3 * SHAPE.hidden * SHAPE.inter
@@ -258,7 +275,8 @@ def prefill_extra(torch, layers, st, ext_stream) -> dict:
     hbm_peak = peaks()[0]
     return {
         "workload": "prefill_300rows_zipf1.1_one_layer", "rows": rows, "experts_hit": hit, "max_group": int(counts.max()),
-        "rows_per_s": rows / us_full * 1e6, "us_layer_host_rows_in": us_full,
+        "rows_per_s": rows / us_graph * 1e6, "us_layer_device_graph": us_graph,
+        "rows_per_s_reference_call_sequence": rows / us_full * 1e6, "us_layer_reference_call_sequence_host_rows_in": us_full,
         "grouped_gemm_us": us_grouped, "grouped_gemm_rows_per_s": rows / us_grouped * 1e6,
         "grouped_gemm_tflops": flops / us_grouped / 1e6, "tensor_pipe_frac_of_measured_bf16_peak": flops / us_grouped / 1e6 / tf_peak,
         "grouped_gemm_hbm_gbs": wbytes / us_grouped / 1e3, "hbm_frac_of_measured": wbytes / us_grouped / 1e3 / hbm_peak,
@@ -299,77 +317,93 @@ def gemv_extra(torch, st, ext_stream) -> list:
     return out
 
 
+def _ep_time(torch, dist, ext_stream, stream, step, restore, iters: int) -> tuple[float, bool]:
+    """Device time of step() in us (max over ranks). The step is captured in a CUDA graph (collectives included)
+    when capture works; restore() puts the input back and runs inside the timed region either way."""
+    restore()
+    step()
+    torch.cuda.synchronize()
+    graph = None
+    try:
+        g = torch.cuda.CUDAGraph()
+        restore()
+        with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+            step()
+        graph = g
+    except Exception as exc:  # noqa: BLE001 - the eager sequence is the same work
+        sys.stderr.write(f"bench: expert-parallel graph capture failed ({type(exc).__name__}: {exc}); timing eager launches\n")
+    run = graph.replay if graph is not None else step
+    for _ in range(3):
+        restore()
+        run()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(ext_stream)
+    for _ in range(iters):
+        restore()
+        run()
+    e1.record(ext_stream)
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / iters * 1e3], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0]), graph is not None
+
+
 def prefill_ep_extra(torch, dist, layer, st, ext_stream, rank: int, world: int) -> dict:
     """Configuration 3 expert-parallel: the 300 rows are split over the ranks, every rank owns 256 / N experts of
-    the (identical) layer, rows travel to their experts and back with NCCL all-to-all (drama_rs_b200/ep.py).
-    Timed on the device with events on every rank; the caller takes the max over ranks."""
+    the (identical) layer, rows travel to their experts and back with NCCL all-to-all at a fixed capacity
+    (drama_rs_b200/ep.py ep_moe_block_fixed: no size is read on the host, the layer replays from a CUDA graph).
+    Timed on the device with events on every rank; max over ranks."""
     from drama_rs_b200 import ep
 
     rows = 300
     lo, hi = rows * rank // world, rows * (rank + 1) // world
+    max_rows = -(-rows // world)
+    cap = max_rows * SHAPE.topk
     x_all = synth.make_x(33, rows, SHAPE.hidden)
-    ops = ep.EpGpuOps(layer, rank, world, rows, st=st)
+    ops = ep.EpGpuFixed(layer, rank, world, max_rows, cap, st=st)
     with torch.cuda.stream(ops.stream):
         ops.logit_bias = torch.from_numpy(synth.zipf_router_bias(33, SHAPE.experts, 1.1)).cuda()
-        x = torch.from_numpy(x_all[lo:hi].copy()).cuda()
-        for _ in range(3):
-            y = ep.ep_moe_block(x.clone(), ops, SHAPE.experts, SHAPE.topk)
-        torch.cuda.synchronize()
-        dist.barrier()
-        iters = 20
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(ext_stream)
-        for _ in range(iters):
-            y = ep.ep_moe_block(x.clone(), ops, SHAPE.experts, SHAPE.topk)
-        e1.record(ext_stream)
-        torch.cuda.synchronize()
-        dist.barrier()
-    us = e0.elapsed_time(e1) / iters * 1e3
-    t = torch.tensor([us], dtype=torch.float64, device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    # checksum of the result, summed over ranks: identical for every N when the routing and the sums are
-    cs = torch.tensor([float(y.double().sum())], dtype=torch.float64, device="cuda")
-    dist.all_reduce(cs)
+        x0 = torch.from_numpy(x_all[lo:hi].copy()).cuda()
+        x = x0.clone()
+        us, graphed = _ep_time(torch, dist, ext_stream, ops.stream, lambda: ep.ep_moe_block_fixed(x, ops, SHAPE.experts, SHAPE.topk, cap),
+                               lambda: x.copy_(x0), 20)
+        # checksum of the result, summed over ranks: identical for every N when the routing and the sums are
+        cs = torch.tensor([float(x.double().sum())], dtype=torch.float64, device="cuda")
+        dist.all_reduce(cs)
     return {"workload": "prefill_300rows_zipf1.1_one_layer_expert_parallel", "rows": rows, "experts_per_rank": SHAPE.experts // world,
-            "us_layer": float(t[0]), "rows_per_s": rows / float(t[0]) * 1e6, "output_sum": float(cs[0]),
-            "exchange": "NCCL all_to_all_single, bf16 rows out, f32 rows back"}
+            "us_layer": us, "rows_per_s": rows / us * 1e6, "output_sum": float(cs[0]), "cuda_graph": graphed,
+            "exchange": f"NCCL all_to_all_single at fixed capacity ({cap} row slots per peer): bf16 rows out, f32 rows back"}
 
 
 def decode64_ep_extra(torch, dist, layers, st, ext_stream, rank: int, world: int) -> dict:
     """Configuration 4: 64 independent streams, one row each, through the whole stack; experts sharded
-    256 / N per GPU; per layer one all-to-all out and one back (uniform routing, no bias)."""
+    256 / N per GPU; per layer one all-to-all out and one back (uniform routing, no bias); the whole 40-layer step
+    is one CUDA graph."""
     from drama_rs_b200 import ep
 
     rows = 64
     lo, hi = rows * rank // world, rows * (rank + 1) // world
+    max_rows = -(-rows // world)
+    cap = max_rows * SHAPE.topk
     x_all = synth.make_x(64, rows, SHAPE.hidden)
-    opss = [ep.EpGpuOps(ly, rank, world, rows, st=st) for ly in layers]
-    with torch.cuda.stream(opss[0].stream):
+    ops = ep.EpGpuFixed(layers[0], rank, world, max_rows, cap, st=st)
+    with torch.cuda.stream(ops.stream):
         x0 = torch.from_numpy(x_all[lo:hi].copy()).cuda()
+        x = x0.clone()
 
         def step():
-            x = x0.clone()
-            for ops in opss:
-                x = ep.ep_moe_block(x, ops, SHAPE.experts, SHAPE.topk)
-            return x
+            for ly in layers:
+                ops.layer = ly
+                ep.ep_moe_block_fixed(x, ops, SHAPE.experts, SHAPE.topk, cap)
 
-        step()
-        torch.cuda.synchronize()
-        dist.barrier()
-        iters = 3
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(ext_stream)
-        for _ in range(iters):
-            y = step()
-        e1.record(ext_stream)
-        torch.cuda.synchronize()
-        dist.barrier()
-    us = e0.elapsed_time(e1) / iters * 1e3
-    t = torch.tensor([us], dtype=torch.float64, device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us, graphed = _ep_time(torch, dist, ext_stream, ops.stream, step, lambda: x.copy_(x0), 5)
+        finite = bool(torch.isfinite(x).all())
     return {"workload": "decode_64streams_stack_expert_parallel", "streams": rows, "layers": len(layers),
-            "us_per_step": float(t[0]), "us_per_layer": float(t[0]) / len(layers),
-            "stream_layers_per_s": rows * len(layers) / float(t[0]) * 1e6, "finite": bool(torch.isfinite(y).all())}
+            "us_per_step": us, "us_per_layer": us / len(layers), "cuda_graph": graphed,
+            "stream_layers_per_s": rows * len(layers) / us * 1e6, "finite": finite}
 
 
 def run_gpu(args) -> None:

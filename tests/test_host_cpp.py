@@ -68,6 +68,7 @@ def test_cpp_decoder_matches_oracle(tmp_path):
     for t in layers:
         want = orc.moe_layer(t, want[None, :], SHAPE.topk, SHAPE.eps, np.float64)[0][0]
     eager, graph = np.fromfile(ea, np.float32), np.fromfile(gr, np.float32)
-    assert_parity(eager, want, "C++ host, eager")
+    # the hidden state grows layer over layer (no final norm): the absolute bar scales with it, as for the stack tests
+    assert_parity(eager, want, "C++ host, eager", max_abs=max(1e-2, 4e-6 * np.abs(want).max()))
     assert np.array_equal(eager.view(np.uint32), graph.view(np.uint32)), "graph replay differs from the eager step"
     assert '"device_error": 0' in r.stdout
