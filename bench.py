@@ -348,7 +348,11 @@ def _ep_time(torch, dist, ext_stream, stream, step, restore, iters: int) -> tupl
     dist.barrier()
     t = torch.tensor([e0.elapsed_time(e1) / iters * 1e3], dtype=torch.float64, device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t[0]), graph is not None
+    graphed = graph is not None
+    # a live graph that holds captured collectives keeps the communicator busy at shutdown: drop it here
+    del graph, run
+    torch.cuda.synchronize()
+    return float(t[0]), graphed
 
 
 def prefill_ep_extra(torch, dist, layer, st, ext_stream, rank: int, world: int) -> dict:

@@ -16,9 +16,25 @@ ROWS = 37
 SHAPE = synth.MoeShape(experts=16)
 
 
+def _watchdog(seconds: int = 120) -> None:
+    """A rank that stops making progress dumps every thread's stack and exits instead of waiting forever."""
+    import faulthandler
+    import sys
+
+    faulthandler.dump_traceback_later(seconds, exit=True, file=sys.stderr)
+
+
+def _stage(rank: int, what: str) -> None:
+    import sys
+
+    print(f"[rank {rank}] {what}", file=sys.stderr, flush=True)
+
+
 def fixed_worker(rank, world, port, out):
     """The fixed-capacity exchange: eager once, then the same layer captured in a CUDA graph and replayed."""
     import torch.distributed as dist
+
+    _watchdog()
 
     from drama_rs_b200 import ep
     from drama_rs_b200.gpu import Stream
@@ -38,18 +54,23 @@ def fixed_worker(rank, world, port, out):
     with torch.cuda.stream(ops.stream):
         x0 = torch.from_numpy(x_all[lo:hi].copy()).cuda()
         x = x0.clone()
+        _stage(rank, "eager layer")
         ep.ep_moe_block_fixed(x, ops, SHAPE.experts, SHAPE.topk, cap)
         torch.cuda.synchronize()
         eager = x.cpu().numpy()
         x.copy_(x0)
+        _stage(rank, "capture")
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=ops.stream, capture_error_mode="thread_local"):
             ep.ep_moe_block_fixed(x, ops, SHAPE.experts, SHAPE.topk, cap)
+        _stage(rank, "replay")
         for _ in range(2):  # the second replay starts from the same input again
             x.copy_(x0)
             g.replay()
         torch.cuda.synchronize()
         replay = x.cpu().numpy()
+        _stage(rank, "done")
+        del g
     np.save(os.path.join(out, f"eager{rank}.npy"), eager)
     np.save(os.path.join(out, f"replay{rank}.npy"), replay)
     dist.destroy_process_group()
@@ -83,6 +104,8 @@ def test_ep_fixed_capacity_eager_and_graph(tmp_path, world):
 
 def worker(rank, world, port, out):
     import torch.distributed as dist
+
+    _watchdog()
 
     from drama_rs_b200 import ep
     from drama_rs_b200.gpu import Stream
