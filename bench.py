@@ -429,7 +429,8 @@ def run_gpu(args) -> None:
     st = Stream()
     ext_stream = torch.cuda.ExternalStream(st.raw.value)
     layers = device_layers(torch, args.layers, 1234, st)  # the same seed on every rank: replicas for decode, shards for the expert-parallel legs
-    dec = MoeDecoder(layers, st=st)
+    chained = args.sequence == "chained"
+    dec = MoeDecoder(layers, st=st, chained=chained)
     x0 = synth.make_x(99, 1, SHAPE.hidden)[0]
     x0_dev = torch.from_numpy(x0).cuda()
     hidden_bytes = SHAPE.hidden * 4
@@ -469,6 +470,20 @@ def run_gpu(args) -> None:
                 graph.launch(st)
             st.sync()
     y_resident = dec.x.download(np.float32, SHAPE.hidden, st)
+
+    # The other call sequence on the same layers, for comparison (device-resident step only).
+    alt = MoeDecoder(layers, st=st, chained=not chained)
+
+    def record_alt():
+        check(lib.dr_d2d(alt.x.at(0), C.c_void_p(x0_dev.data_ptr()), hidden_bytes, st.raw), "d2d")
+        alt.record_step()
+
+    alt_graph = Graph(st, record_alt)
+    alt_us = time_on_stream(torch, st, ext_stream, lambda i: alt_graph.launch(st), args.steps) / args.layers
+    y_alt = alt.x.download(np.float32, SHAPE.hidden, st)
+    alt_info = {"sequence": "chained" if not chained else "reference", "us_per_layer": alt_us,
+                "max_abs_diff_to_headline_sequence": float(np.abs(y_alt - y_resident).max()),
+                "hidden_state_scale": float(np.abs(y_resident).max())}
 
     # End to end through the public call: pinned host x -> device, graph, device -> pinned host.
     hx = torch.from_numpy(x0).pin_memory()
@@ -523,6 +538,8 @@ def run_gpu(args) -> None:
         "config": {"workload": "decode_stack40_b1", "layers": args.layers, "hidden": SHAPE.hidden, "experts": SHAPE.experts,
                    "topk": SHAPE.topk, "inter": SHAPE.inter, "weights": "int4 g64 (scale,min) routed + int8 g128 shared",
                    "graph": "one CUDA graph per step, 3 kernels per layer", "replicas": world,
+                   "sequence": ("chained: dr_router_topk for layer 0, then drb_moe_decode_chained + drb_router_topk_chained per layer"
+                                if chained else "reference: dr_router_topk + dr_moe_decode per layer (src/engine.rs:959-1042)"),
                    "multi_gpu": "batch-1 decode does not shard: N independent replicas, no collective; the expert-parallel path is reported under prefill_expert_parallel",
                    "cache": "inputs larger than L2: 736 MB of weights read per step, 18.1 GB resident"},
         "hbm_gbs": gbs,
@@ -536,6 +553,7 @@ def run_gpu(args) -> None:
         "gpu_launches": args.steps * args.layers * 3,
         "clocks": clocks.summary(),
         "device_error_word": int(word.value),
+        "decode_other_sequence": alt_info,
     }
     if ep_info is not None:
         line["prefill_expert_parallel"] = ep_info
@@ -557,6 +575,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--sequence", default="reference", choices=["reference", "chained"],
+                    help="decode call sequence of the headline number: the reference engine's, or the chained entry points")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill and GEMV-sweep figures")
     args = ap.parse_args()

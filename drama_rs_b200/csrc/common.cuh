@@ -493,6 +493,7 @@ struct DrbDevice {
   bool ready;           // attributes set
   bool prefill_mma;     // dr_moe_prefill on tcgen05 (DRB_PREFILL=simt selects the CUDA-core kernels)
   bool router_cluster;  // decode router as one 8-block cluster (DRB_ROUTER=grid selects the multi-block variant)
+  bool down_warmup;     // gate/up warms the down projection's rows into L2 (off; DRB_DOWN_WARMUP=1 turns it on)
   unsigned* grid_sync;  // zeroed words used by grid-wide barriers
 };
 const DrbDevice& drb_device(cudaStream_t st);

@@ -105,7 +105,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
     float ss = 0.f;
     const float4* x4 = reinterpret_cast<const float4*>(x);
     for (int i = threadIdx.x; i < K / 4; i += NT) {
-      const float4 v = x4[i];
+      const float4 v = __ldcg(x4 + i);
       ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
     ss = warp_sum(ss);
@@ -121,7 +121,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
   // Chunk c = lane + 32*i of the segment covers k = seg*KSEG + EPC*c ...; whole warps enter or skip the loop.
   unsigned char* qb = reinterpret_cast<unsigned char*>(xs4);
   for (int i = threadIdx.x; i < K / 4; i += NT) {
-    float4 v = reinterpret_cast<const float4*>(x)[i];
+    float4 v = __ldcg(reinterpret_cast<const float4*>(x) + i);
     if (nw) {
       const float4 w = reinterpret_cast<const float4*>(nw)[i];
       v = make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w);
@@ -211,7 +211,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
       if (NSEG == 1) {
         if (lane == 0 && lr < nr) {
           const int row = r0 + lr;
-          y[row] = U == 2 ? silu_f(d[0]) * d[U - 1] : d[0] + (res ? res[row] : 0.f);
+          y[row] = U == 2 ? silu_f(d[0]) * d[U - 1] : d[0] + (res ? __ldcg(res + row) : 0.f);
         }
       } else {
         // K is split over NSEG warps: combine their partial sums in segment order.
@@ -228,7 +228,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
             t1 += sm.red[(rg * NSEG + q) * 2 + 1];
           }
           const int row = r0 + lr;
-          y[row] = U == 2 ? silu_f(t0) * t1 : t0 + (res ? res[row] : 0.f);
+          y[row] = U == 2 ? silu_f(t0) * t1 : t0 + (res ? __ldcg(res + row) : 0.f);
         }
         consumer_sync(CW * 32);
       }

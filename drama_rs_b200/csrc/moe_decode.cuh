@@ -1,18 +1,23 @@
 // Batch-1 MoE decode: dr_moe_decode = gate/up + SwiGLU over the 8 routed int4 experts and the int8
 // shared expert, then down projection + weighted combine + sigmoid-gated shared expert + residual.
 //
-// Both kernels launch at least one block per multiprocessor (148 / 128 blocks at least, so that a
-// block's share always fits its shared memory in one go). Every block owns a byte-balanced,
-// contiguous share of the weight rows and requests ALL of it at once with bulk asynchronous copies
-// (each lane of the producer warp issues the copies of one chunk), so the HBM queue is full from
-// the first microsecond. The down kernel is launched with a programmatic dependency: its blocks
-// start while gate/up still runs, read the routing, and pull their weight rows into shared memory
-// before they wait for the activations.
+// Gate/up: 144 blocks. Block b < 128 owns 32 consecutive units (a gate row and its up row each) of one routed
+// expert, blocks 128..143 own 32 units of the shared expert; every block requests ALL its rows at once with bulk
+// asynchronous copies (four parts, one mbarrier each), so the HBM queue is full from the first microsecond, and the
+// shared expert's rows, which do not depend on the routing, are requested before the dependency wait. The 32
+// activations a block produces are exactly one quantisation block of the down projection's input, so the block
+// converts them to block fixed point itself and the down kernel never sees floats.
+// Down: at least 128 blocks of at most 16 output rows; a block pulls its rows of the eight chosen experts and of the
+// shared expert into shared memory before it waits for the activations (programmatic dependent launch), copies the
+// 16 KB of quantised activations once, and its lanes keep the limb words of their k-slice in registers.
 //
-// Activations are read coalesced, normalised, and converted once per block to block fixed point
-// (three signed 7-bit limbs per value, see common.cuh); each lane keeps the limb words of its
-// k-slice in registers. Weight words then go through dp4a against them: integer-exact sums,
-// group scales applied in fp32, warp-shuffle reductions folded over all the rows a warp owns.
+// x is read coalesced, normalised, and converted once per block to block fixed point (three signed 7-bit limbs per
+// value, see common.cuh). Weight words then go through dp4a against the limbs: integer-exact sums, group scales
+// applied in fp32, warp-shuffle reductions folded over all the rows a warp owns.
+//
+// Every load of data that the preceding kernel wrote goes through ld.global.cg (or a bulk copy): a block launched
+// programmatically can be resident before its predecessor has written that data, and an L1-cached or non-coherent
+// load may then return what the multiprocessor saw earlier. Measured: with plain loads a 3-layer stack diverged.
 //
 // Replaces kernels/drama.cu:470-599 of the reference (k_moe_gate_up_q4, k_moe_down_q4,
 // dr_moe_decode), behind the same C signature (src/ffi.rs:42-46). Like the reference the launcher
@@ -33,116 +38,168 @@ DRB_DEV void named_sync() {
 // ------------------------------------------------------------------------------------------
 // gate/up
 
+// The SwiGLU activations cross from gate/up to down as block fixed point, not as floats: `act` (the caller's
+// scratch of (topk + 1) * I floats, which nothing else reads) holds, for every 32 consecutive inputs of a routed
+// expert's down projection, one 112-byte block (limbs in even/odd order, delta, sum; common.cuh), block
+// k * 16 + c for inputs [32 c, 32 c + 32) of expert slot k; then, from ACTQ_SHARED on, one 64-byte block (natural
+// order) for every 16 inputs of the shared expert. 16,384 of the 18,432 bytes are used. Every gate/up block
+// produces exactly the 32 values of one routed block (or two shared ones), so it quantises them once and the down
+// kernel's lanes load their limbs straight into registers.
+constexpr int ACTQ_SHARED = TOPK * (I / 32) * QB32_BYTES;  // 14,336
+
 namespace gu {
 
-constexpr int CW = 16;                                    // consumer warps, one unit (gate row + up row) at a time each
+constexpr int CW = 16;                                    // consumer warps
 constexpr int NT = CW * 32;                               // consumer threads
 constexpr int THREADS = NT + 32;                          // + one producer warp
-constexpr int MIN_GRID = 148;                             // a block then owns <= 28 routed and <= 4 shared units
-constexpr int UPW = 2;                                    // units per warp and pass: 32 units over 16 warps
-constexpr int RU = 4;                                     // routed units per chunk
-constexpr int SU = 2;                                     // shared-expert units per chunk
+constexpr int UNITS = 32;                                 // units (gate row + up row) per block: warp w takes w and w + 16
+constexpr int ROUTED_BLOCKS = TOPK * I / UNITS;           // 128
+constexpr int SHARED_BLOCKS = I / UNITS;                  // 16
+constexpr int GRID = ROUTED_BLOCKS + SHARED_BLOCKS;       // 144
+constexpr int QUARTERS = 4, QU = UNITS / QUARTERS;        // the block's rows arrive in four parts of 8 units
 constexpr int QROW = H / 2;                               // 1024 bytes of nibbles per routed row
 constexpr int SMROW = (H / 64) * 4;                       // 128 bytes of (scale, min) per routed row
 constexpr int SSROW = (H / 128) * 2;                      // 32 bytes of scales per shared-expert row
-constexpr int STAGE_BYTES = RU * 2 * (QROW + SMROW);      // 9216; a shared chunk needs SU*2*(H+32) = 8320
-constexpr int STAGES = 12;                                // >= 3 shared + 8 routed chunks (chunks are aligned)
+// stage: gate rows [32] | up rows [32] | gate scales [32] | up scales [32]
+constexpr int R_STAGE = 2 * UNITS * (QROW + SMROW);       // 73,728
+constexpr int S_STAGE = 2 * UNITS * (H + SSROW);          // 133,120
 constexpr int CTL_BYTES = 1024;
 constexpr int QX_BYTES = (H / 32) * QB32_BYTES;           // the normalised activations as limb blocks
-constexpr size_t SMEM_BYTES = CTL_BYTES + QX_BYTES + (size_t)STAGES * STAGE_BYTES;
-static_assert(SU * 2 * (H + SSROW) <= STAGE_BYTES, "shared-expert chunk does not fit a stage");
+constexpr size_t SMEM_BYTES = CTL_BYTES + QX_BYTES + (size_t)S_STAGE;
 static_assert(NT == H / 4, "one float4 of x per consumer thread");
 
 struct Ctl {
-  uint64_t full[STAGES];
+  uint64_t full[QUARTERS];
   float red[CW];
+  float actv[UNITS];
 };
 
-struct Plan {
-  int us0, us1, ur0, ur1;  // this block's shared units and routed units
-  int sc0, nsc, rc0, nrc;  // aligned chunk ranges
-  DRB_DEV Plan(unsigned b, unsigned G) {
-    us0 = (int)((long long)I * b / G), us1 = (int)((long long)I * (b + 1) / G);
-    ur0 = (int)((long long)TOPK * I * b / G), ur1 = (int)((long long)TOPK * I * (b + 1) / G);
-    sc0 = us0 / SU, nsc = us1 > us0 ? (us1 + SU - 1) / SU - sc0 : 0;
-    rc0 = ur0 / RU, nrc = ur1 > ur0 ? (ur1 + RU - 1) / RU - rc0 : 0;
+// One warp turns 32 values (lane = input index) into a 112-byte even/odd block at dst (global or shared).
+DRB_DEV void quant_block32_warp(float v, unsigned char* dst, int lane) {
+  const float m = warp_max(fabsf(v));
+  const float sum = warp_sum(v);
+  const float delta = m > 0.f ? m * (1.f / 1048576.f) : 1.f;
+  int l0, l1, l2;
+  limbs3(__float2int_rn(v * (1.f / delta)), l0, l1, l2);
+  const uint32_t pack = (uint32_t)(l0 & 0xff) | ((uint32_t)(l1 & 0xff) << 8) | ((uint32_t)(l2 & 0xff) << 16);
+  // word w (lanes 0..7) holds inputs 8 (w / 2) + (w & 1) + {0, 2, 4, 6}
+  const int base = 8 * ((lane >> 1) & 3) + (lane & 1);
+  const uint32_t t0 = __shfl_sync(0xffffffffu, pack, base), t1 = __shfl_sync(0xffffffffu, pack, base + 2);
+  const uint32_t t2 = __shfl_sync(0xffffffffu, pack, base + 4), t3 = __shfl_sync(0xffffffffu, pack, base + 6);
+  if (lane < 8) {
+    uint32_t* out = reinterpret_cast<uint32_t*>(dst);
+    out[lane] = prmt(prmt(t0, t1, 0x0040u), prmt(t2, t3, 0x0040u), 0x5410u);
+    out[8 + lane] = prmt(prmt(t0, t1, 0x0051u), prmt(t2, t3, 0x0051u), 0x5410u);
+    out[16 + lane] = prmt(prmt(t0, t1, 0x0062u), prmt(t2, t3, 0x0062u), 0x5410u);
   }
-  DRB_DEV int chunks() const { return nsc + nrc; }
-  DRB_DEV int units() const { return (us1 - us0) + (ur1 - ur0); }
-  // Units [ua, ub) of chunk t and the aligned base of the chunk. Chunks are aligned to multiples of
-  // RU (SU), so a routed chunk never straddles two experts.
-  DRB_DEV void chunk(int t, bool& shared, int& base, int& ua, int& ub) const {
-    shared = t < nsc;
-    if (shared) {
-      base = (sc0 + t) * SU, ua = max(base, us0), ub = min(base + SU, us1);
-    } else {
-      base = (rc0 + t - nsc) * RU, ua = max(base, ur0), ub = min(base + RU, ur1);
-    }
+  if (lane == 0) {
+    *reinterpret_cast<float*>(dst + 96) = delta;
+    *reinterpret_cast<float*>(dst + 100) = sum;
   }
-  // The o-th unit of the block: shared units first. Returns its chunk and its slot in the chunk.
-  DRB_DEV void unit(int o, bool& shared, int& u, int& t, int& slot) const {
-    shared = o < us1 - us0;
-    if (shared) {
-      u = us0 + o, t = u / SU - sc0, slot = u % SU;
-    } else {
-      u = ur0 + o - (us1 - us0), t = nsc + u / RU - rc0, slot = u % RU;
-    }
-  }
-};
+}
 
+// Each half-warp turns 16 values (lane & 15 = input index) into a 64-byte natural-order block at dst + 64 * half.
+DRB_DEV void quant_block16_halfwarps(float v, unsigned char* dst, int lane) {
+  float m = fabsf(v);
+#pragma unroll
+  for (int o = 1; o < 16; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  const float delta = m > 0.f ? m * (1.f / 1048576.f) : 1.f;
+  int l0, l1, l2;
+  limbs3(__float2int_rn(v * (1.f / delta)), l0, l1, l2);
+  const uint32_t pack = (uint32_t)(l0 & 0xff) | ((uint32_t)(l1 & 0xff) << 8) | ((uint32_t)(l2 & 0xff) << 16);
+  const int h = lane >> 4, q = lane & 3;  // word q (lanes 0..3 of the half) holds inputs 4 q .. 4 q + 3
+  const int base = 16 * h + 4 * q;
+  const uint32_t t0 = __shfl_sync(0xffffffffu, pack, base), t1 = __shfl_sync(0xffffffffu, pack, base + 1);
+  const uint32_t t2 = __shfl_sync(0xffffffffu, pack, base + 2), t3 = __shfl_sync(0xffffffffu, pack, base + 3);
+  unsigned char* blk = dst + h * QB16_BYTES;
+  if ((lane & 15) < 4) {
+    uint32_t* out = reinterpret_cast<uint32_t*>(blk);
+    out[q] = prmt(prmt(t0, t1, 0x0040u), prmt(t2, t3, 0x0040u), 0x5410u);
+    out[4 + q] = prmt(prmt(t0, t1, 0x0051u), prmt(t2, t3, 0x0051u), 0x5410u);
+    out[8 + q] = prmt(prmt(t0, t1, 0x0062u), prmt(t2, t3, 0x0062u), 0x5410u);
+  }
+  if ((lane & 15) == 0) *reinterpret_cast<float*>(blk + 48) = delta;
+}
+
+// Block b < 128: units [32 (b % 16), +32) of routed expert slot b / 16 (64 int4 rows, 72 KB). Block b >= 128: units
+// [32 (b - 128), +32) of the shared expert (64 int8 rows, 130 KB; they do not depend on the routing and are requested
+// before the dependency wait, so these larger blocks finish first). The rows arrive in four parts of 8 units with one
+// mbarrier each; warp w computes units w and w + 16, i.e. parts w / 8 and 2 + w / 8.
+// CH = true (chained sequence): with have_prev the routing and the hidden state are read from this block's replica in
+// the workspace instead of idx and x.
+template <bool CH>
 __global__ void __launch_bounds__(THREADS, 1)
     k_moe_gate_up(const uint8_t* __restrict__ Q, const __half2* __restrict__ SM, const int8_t* __restrict__ shq,
                   const __half* __restrict__ shs, const float* __restrict__ x, const int* __restrict__ idx,
-                  float* __restrict__ act, const float* __restrict__ nw, float eps) {
+                  unsigned char* __restrict__ actq, const float* __restrict__ nw, float eps, float* __restrict__ ws,
+                  int have_prev, const uint8_t* __restrict__ DQ, const __half2* __restrict__ DSM,
+                  const int8_t* __restrict__ dshq, const char* pf, size_t pf_bytes) {
+  if (CH && have_prev) {
+    idx = reinterpret_cast<const int*>(ws + chainws::OFF_ROUTE + (blockIdx.x % chainws::ROUTE_REPS) * chainws::ROUTE_STRIDE);
+    x = ws + chainws::OFF_YREP + (blockIdx.x % chainws::VEC_REPS) * chainws::HID;
+  }
   extern __shared__ __align__(128) unsigned char dyn[];
   Ctl& ctl = *reinterpret_cast<Ctl*>(dyn);
   unsigned char* qx = dyn + CTL_BYTES;
-  unsigned char* ring = dyn + CTL_BYTES + QX_BYTES;
+  unsigned char* st = dyn + CTL_BYTES + QX_BYTES;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const Plan plan(blockIdx.x, gridDim.x);
+  const int b = blockIdx.x;
+  const bool shared = b >= ROUTED_BLOCKS;
+  const int j0 = shared ? (b - ROUTED_BLOCKS) * UNITS : (b % (I / UNITS)) * UNITS;  // first unit
   DRB_TRACE_POINT(10, 0);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) mbar_init(&ctl.full[s], 1);
+    for (int q = 0; q < QUARTERS; ++q) mbar_init(&ctl.full[q], 1);
     mbar_fence_init();
   }
   __syncthreads();
 
   if (warp == CW) {
-    // ---------------- producer warp: lane t requests chunk t
-    if (lane < plan.chunks() && lane < STAGES) {
-      const int t = lane;
-      bool shared;
-      int base, ua, ub;
-      plan.chunk(t, shared, base, ua, ub);
-      unsigned char* dst = ring + (size_t)t * STAGE_BYTES;
-      const int n = ub - ua, slot = ua - base;
-      if (shared) {
-        // The shared expert's rows do not depend on the routing: requested before the dependency wait.
+    // ---------------- producer warp: lane 4 q + c requests copy c (gate rows, up rows, gate scales, up scales) of part q
+    if (lane == 31) prefetch_share(pf, pf_bytes, blockIdx.x, gridDim.x);  // constants of a later kernel (chained: the next router)
+    const int q = lane >> 2, c = lane & 3;
+    const bool issuing = q < QUARTERS;
+    if (shared) {
+      if (issuing && c == 0) mbar_expect_tx(&ctl.full[q], (unsigned)(2 * QU * (H + SSROW)));
+      __syncwarp();
+      if (issuing) {
+        const int u0 = j0 + q * QU, l0 = q * QU;
         const unsigned char* sp = reinterpret_cast<const unsigned char*>(shs);
-        mbar_expect_tx(&ctl.full[t], (unsigned)(n * 2 * (H + SSROW)));
-        bulk_g2s(dst + slot * H, shq + (size_t)ua * H, (unsigned)(n * H), &ctl.full[t]);
-        bulk_g2s(dst + (SU + slot) * H, shq + ((size_t)I + ua) * H, (unsigned)(n * H), &ctl.full[t]);
-        bulk_g2s(dst + 2 * SU * H + slot * SSROW, sp + (size_t)ua * SSROW, (unsigned)(n * SSROW), &ctl.full[t]);
-        bulk_g2s(dst + 2 * SU * H + (SU + slot) * SSROW, sp + ((size_t)I + ua) * SSROW, (unsigned)(n * SSROW), &ctl.full[t]);
-      } else {
-        pdl_wait();  // idx is the router's output
-        DRB_TRACE_POINT(11, CW * 32);
-        const int k = ua / I, j = ua % I;
-        const size_t ek = (size_t)idx[k];
-        const uint8_t* q = Q + ek * (2 * I) * QROW;
+        if (c == 0) bulk_g2s(st + (size_t)l0 * H, shq + (size_t)u0 * H, QU * H, &ctl.full[q]);
+        else if (c == 1) bulk_g2s(st + (size_t)(UNITS + l0) * H, shq + ((size_t)I + u0) * H, QU * H, &ctl.full[q]);
+        else if (c == 2) bulk_g2s(st + (size_t)2 * UNITS * H + l0 * SSROW, sp + (size_t)u0 * SSROW, QU * SSROW, &ctl.full[q]);
+        else bulk_g2s(st + (size_t)2 * UNITS * H + (UNITS + l0) * SSROW, sp + ((size_t)I + u0) * SSROW, QU * SSROW, &ctl.full[q]);
+      }
+      pdl_wait();
+    } else {
+      pdl_wait();  // idx is the router's output
+      DRB_TRACE_POINT(11, CW * 32);
+      if (issuing && c == 0) mbar_expect_tx(&ctl.full[q], (unsigned)(2 * QU * (QROW + SMROW)));
+      __syncwarp();
+      if (issuing) {
+        const size_t ek = (size_t)__ldcg(idx + b / (I / UNITS));
+        const uint8_t* qp = Q + ek * (2 * I) * QROW;
         const unsigned char* smp = reinterpret_cast<const unsigned char*>(SM) + ek * (2 * I) * SMROW;
-        mbar_expect_tx(&ctl.full[t], (unsigned)(n * 2 * (QROW + SMROW)));
-        bulk_g2s(dst + slot * QROW, q + (size_t)j * QROW, (unsigned)(n * QROW), &ctl.full[t]);
-        bulk_g2s(dst + (RU + slot) * QROW, q + ((size_t)I + j) * QROW, (unsigned)(n * QROW), &ctl.full[t]);
-        bulk_g2s(dst + 2 * RU * QROW + slot * SMROW, smp + (size_t)j * SMROW, (unsigned)(n * SMROW), &ctl.full[t]);
-        bulk_g2s(dst + 2 * RU * QROW + (RU + slot) * SMROW, smp + ((size_t)I + j) * SMROW, (unsigned)(n * SMROW), &ctl.full[t]);
+        const int u0 = j0 + q * QU, l0 = q * QU;
+        if (c == 0) bulk_g2s(st + (size_t)l0 * QROW, qp + (size_t)u0 * QROW, QU * QROW, &ctl.full[q]);
+        else if (c == 1) bulk_g2s(st + (size_t)(UNITS + l0) * QROW, qp + ((size_t)I + u0) * QROW, QU * QROW, &ctl.full[q]);
+        else if (c == 2) bulk_g2s(st + (size_t)2 * UNITS * QROW + l0 * SMROW, smp + (size_t)u0 * SMROW, QU * SMROW, &ctl.full[q]);
+        else bulk_g2s(st + (size_t)2 * UNITS * QROW + (UNITS + l0) * SMROW, smp + ((size_t)I + u0) * SMROW, QU * SMROW, &ctl.full[q]);
       }
     }
-    __syncwarp();
-    pdl_wait();
     DRB_TRACE_POINT(12, CW * 32);
     pdl_launch_dependents();  // never before the wait: the down kernel's prologue reads the router's idx
+    // The down kernel cannot start while this one holds the registers, so its weights are warmed into L2 from
+    // here: once this block's own rows have landed (the warm-up must not compete with them), each of the first
+    // 17 lanes asks for this block's 1/gridDim share of one region of the down projection.
+    if (DQ) {
+      if (lane < QUARTERS) mbar_wait(&ctl.full[lane], 0, DRB_ERR_FULL_WAIT);
+      __syncwarp();
+      constexpr size_t DQ_BYTES = (size_t)H * (I / 2), DSM_BYTES = (size_t)H * (I / 64) * 4, DSH_BYTES = (size_t)H * I;
+      if (lane < TOPK) prefetch_share(reinterpret_cast<const char*>(DQ) + (size_t)__ldcg(idx + lane) * DQ_BYTES, DQ_BYTES, blockIdx.x, gridDim.x);
+      else if (lane < 2 * TOPK) prefetch_share(reinterpret_cast<const char*>(DSM) + (size_t)__ldcg(idx + lane - TOPK) * DSM_BYTES, DSM_BYTES, blockIdx.x, gridDim.x);
+      else if (lane == 2 * TOPK) prefetch_share(reinterpret_cast<const char*>(dshq), DSH_BYTES, blockIdx.x, gridDim.x);
+    }
     return;
   }
 
@@ -152,7 +209,13 @@ __global__ void __launch_bounds__(THREADS, 1)
   pdl_wait();               // x is the previous kernel's output
   pdl_launch_dependents();
   DRB_TRACE_POINT(13, 0);
-  const float4 xv = reinterpret_cast<const float4*>(x)[threadIdx.x];
+  const float4 xv = __ldcg(reinterpret_cast<const float4*>(x) + threadIdx.x);
+#ifdef DRB_TRACE
+  {
+    asm volatile("" ::"f"(xv.x));
+    DRB_TRACE_POINT(18, 0);
+  }
+#endif
   float inv = 1.f;
   if (nw) {
     const float ss = warp_sum(xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w);
@@ -173,60 +236,50 @@ __global__ void __launch_bounds__(THREADS, 1)
   qact_load(x1, X1, qx + (size_t)(32 + lane) * QB32_BYTES);
   DRB_TRACE_POINT(14, 0);
 
-  // Per-lane partial sums of the (up to) UPW units of this warp: v[2i] = gate, v[2i + 1] = up of its i-th unit.
-  const int nunits = plan.units();
-  for (int o0 = warp; o0 < nunits; o0 += CW * UPW) {
-    float v[2 * UPW];
-    int uid[UPW];
+  // v[2i] = gate, v[2i + 1] = up partial sums of this warp's unit warp + 16 i
+  float v[4];
 #pragma unroll
-    for (int i = 0; i < UPW; ++i) {
-      const int o = o0 + i * CW;
-      v[2 * i] = v[2 * i + 1] = 0.f;
-      uid[i] = -1;
-      if (o >= nunits) continue;
-      bool shared;
-      int u, t, slot;
-      plan.unit(o, shared, u, t, slot);
-      uid[i] = shared ? TOPK * I + u : u;
-      const unsigned char* st = ring + (size_t)t * STAGE_BYTES;
-      mbar_wait(&ctl.full[t], 0, DRB_ERR_FULL_WAIT);
-      if (shared) {
-        const uint4* gr = reinterpret_cast<const uint4*>(st + (size_t)slot * H);
-        const uint4* ur = reinterpret_cast<const uint4*>(st + (size_t)(SU + slot) * H);
-        const __half* gs = reinterpret_cast<const __half*>(st + 2 * SU * H + (size_t)slot * SSROW);
-        const __half* us = reinterpret_cast<const __half*>(st + 2 * SU * H + (size_t)(SU + slot) * SSROW);
-        v[2 * i] = __half2float(gs[lane >> 2]) * x0.delta * dot32_q8_eo(gr[2 * lane], gr[2 * lane + 1], x0, 0) +
-                   __half2float(gs[8 + (lane >> 2)]) * x1.delta * dot32_q8_eo(gr[64 + 2 * lane], gr[64 + 2 * lane + 1], x1, 0);
-        v[2 * i + 1] = __half2float(us[lane >> 2]) * x0.delta * dot32_q8_eo(ur[2 * lane], ur[2 * lane + 1], x0, 0) +
-                       __half2float(us[8 + (lane >> 2)]) * x1.delta * dot32_q8_eo(ur[64 + 2 * lane], ur[64 + 2 * lane + 1], x1, 0);
-      } else {
-        const uint4* gr = reinterpret_cast<const uint4*>(st + (size_t)slot * QROW);
-        const uint4* ur = reinterpret_cast<const uint4*>(st + (size_t)(RU + slot) * QROW);
-        const __half2* gs = reinterpret_cast<const __half2*>(st + 2 * RU * QROW + (size_t)slot * SMROW);
-        const __half2* us = reinterpret_cast<const __half2*>(st + 2 * RU * QROW + (size_t)(RU + slot) * SMROW);
-        // w = s*q + m: sum_k w x = s * delta * sum(q n) + m * sum(x) per 64-group; chunk c belongs to group c / 2.
-        const float2 g0 = __half22float2(gs[lane >> 1]), g1 = __half22float2(gs[16 + (lane >> 1)]);
-        const float2 u0 = __half22float2(us[lane >> 1]), u1 = __half22float2(us[16 + (lane >> 1)]);
-        v[2 * i] = g0.x * x0.delta * dot32_q4_i(gr[lane], x0, 0) + g0.y * X0 + g1.x * x1.delta * dot32_q4_i(gr[32 + lane], x1, 0) + g1.y * X1;
-        v[2 * i + 1] = u0.x * x0.delta * dot32_q4_i(ur[lane], x0, 0) + u0.y * X0 + u1.x * x1.delta * dot32_q4_i(ur[32 + lane], x1, 0) + u1.y * X1;
-      }
+  for (int i = 0; i < 2; ++i) {
+    const int u = warp + CW * i;
+    mbar_wait(&ctl.full[u / QU], 0, DRB_ERR_FULL_WAIT);
+    if (shared) {
+      const uint4* gr = reinterpret_cast<const uint4*>(st + (size_t)u * H);
+      const uint4* ur = reinterpret_cast<const uint4*>(st + (size_t)(UNITS + u) * H);
+      const __half* gs = reinterpret_cast<const __half*>(st + (size_t)2 * UNITS * H + (size_t)u * SSROW);
+      const __half* us = reinterpret_cast<const __half*>(st + (size_t)2 * UNITS * H + (size_t)(UNITS + u) * SSROW);
+      v[2 * i] = __half2float(gs[lane >> 2]) * x0.delta * dot32_q8_eo(gr[2 * lane], gr[2 * lane + 1], x0, 0) +
+                 __half2float(gs[8 + (lane >> 2)]) * x1.delta * dot32_q8_eo(gr[64 + 2 * lane], gr[64 + 2 * lane + 1], x1, 0);
+      v[2 * i + 1] = __half2float(us[lane >> 2]) * x0.delta * dot32_q8_eo(ur[2 * lane], ur[2 * lane + 1], x0, 0) +
+                     __half2float(us[8 + (lane >> 2)]) * x1.delta * dot32_q8_eo(ur[64 + 2 * lane], ur[64 + 2 * lane + 1], x1, 0);
+    } else {
+      const uint4* gr = reinterpret_cast<const uint4*>(st + (size_t)u * QROW);
+      const uint4* ur = reinterpret_cast<const uint4*>(st + (size_t)(UNITS + u) * QROW);
+      const __half2* gs = reinterpret_cast<const __half2*>(st + (size_t)2 * UNITS * QROW + (size_t)u * SMROW);
+      const __half2* us = reinterpret_cast<const __half2*>(st + (size_t)2 * UNITS * QROW + (size_t)(UNITS + u) * SMROW);
+      // w = s*q + m: sum_k w x = s * delta * sum(q n) + m * sum(x) per 64-group; chunk c belongs to group c / 2.
+      const float2 g0 = __half22float2(gs[lane >> 1]), g1 = __half22float2(gs[16 + (lane >> 1)]);
+      const float2 u0 = __half22float2(us[lane >> 1]), u1 = __half22float2(us[16 + (lane >> 1)]);
+      v[2 * i] = g0.x * x0.delta * dot32_q4_i(gr[lane], x0, 0) + g0.y * X0 + g1.x * x1.delta * dot32_q4_i(gr[32 + lane], x1, 0) + g1.y * X1;
+      v[2 * i + 1] = u0.x * x0.delta * dot32_q4_i(ur[lane], x0, 0) + u0.y * X0 + u1.x * x1.delta * dot32_q4_i(ur[32 + lane], x1, 0) + u1.y * X1;
     }
-    // Fold the four per-lane sums into one reduction: after two exchange steps lane group
-    // (lane & 16, lane & 8) carries v[(lane >> 3) & 3]; three butterfly steps finish it.
-    static_assert(UPW == 2, "the fold below is written for four values");
-    const bool hi16 = lane & 16, hi8 = lane & 8;
-    const float r0 = (hi16 ? v[2] : v[0]) + __shfl_xor_sync(0xffffffffu, hi16 ? v[0] : v[2], 16);
-    const float r1 = (hi16 ? v[3] : v[1]) + __shfl_xor_sync(0xffffffffu, hi16 ? v[1] : v[3], 16);
-    float s = (hi8 ? r1 : r0) + __shfl_xor_sync(0xffffffffu, hi8 ? r0 : r1, 8);
-    s += __shfl_xor_sync(0xffffffffu, s, 4);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    // lanes 0..7: gate of unit 0, 8..15: up of unit 0, 16..23: gate of unit 1, 24..31: up of unit 1
-    const float upv = __shfl_xor_sync(0xffffffffu, s, 8);
-    if ((lane & 15) == 0) {
-      const int id = (lane & 16) ? uid[1] : uid[0];
-      if (id >= 0) act[id] = silu_f(s) * upv;
-    }
+  }
+  // Fold the four per-lane sums into one reduction: after two exchange steps lane group
+  // (lane & 16, lane & 8) carries v[(lane >> 3) & 3]; three butterfly steps finish it.
+  const bool hi16 = lane & 16, hi8 = lane & 8;
+  const float r0 = (hi16 ? v[2] : v[0]) + __shfl_xor_sync(0xffffffffu, hi16 ? v[0] : v[2], 16);
+  const float r1 = (hi16 ? v[3] : v[1]) + __shfl_xor_sync(0xffffffffu, hi16 ? v[1] : v[3], 16);
+  float s = (hi8 ? r1 : r0) + __shfl_xor_sync(0xffffffffu, hi8 ? r0 : r1, 8);
+  s += __shfl_xor_sync(0xffffffffu, s, 4);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  // lanes 0..7: gate of unit warp, 8..15: its up, 16..23: gate of unit warp + 16, 24..31: its up
+  const float upv = __shfl_xor_sync(0xffffffffu, s, 8);
+  if ((lane & 15) == 0) ctl.actv[warp + (lane & 16)] = silu_f(s) * upv;
+  named_sync<NT>();
+  if (warp == 0) {
+    const float a = ctl.actv[lane];
+    if (shared) quant_block16_halfwarps(a, actq + ACTQ_SHARED + (size_t)(b - ROUTED_BLOCKS) * 2 * QB16_BYTES, lane);
+    else quant_block32_warp(a, actq + (size_t)b * QB32_BYTES, lane);
   }
   DRB_TRACE_POINT(17, 0);
 }
@@ -248,38 +301,77 @@ constexpr int SMROW = (I / 64) * 4;             // 32 bytes of (scale, min)
 constexpr int EXPERT_BYTES = RT * (QROW + SMROW);
 constexpr int STAGE_BYTES = TOPK * EXPERT_BYTES + RT * I;  // + the shared expert's int8 rows: 45056
 constexpr int CTL_BYTES = 1024;
-constexpr int QA_BYTES = (TOPK * I / 32) * QB32_BYTES;     // routed activations as even/odd limb blocks
-constexpr int QS_BYTES = (I / 16) * QB16_BYTES;            // the shared expert's activations, natural order
-constexpr size_t SMEM_BYTES = CTL_BYTES + QA_BYTES + QS_BYTES + STAGE_BYTES;
+constexpr int ACTQ_BYTES = TOPK * (I / 32) * QB32_BYTES + (I / 16) * QB16_BYTES;  // 16,384: the gate/up kernel's output
+constexpr size_t SMEM_BYTES = CTL_BYTES + ACTQ_BYTES + STAGE_BYTES;
+static_assert(ACTQ_BYTES == 2 * NT * 16, "two 16-byte pieces of the activations per consumer thread");
 static_assert(RT == CW, "one shared-expert row per consumer warp");
 
 struct Ctl {
   uint64_t full;
   float part[TOPK + 1][RT];
+  float xs[RT];   // CHAIN: this block's new hidden values times the next layer's norm weight
+  float ysq[RT];  // CHAIN: their squares
+  float wk[TOPK]; // the routing weights and the shared expert's gate, fetched once per block
+  float sgate;
+  int last;       // CHAIN: this block was the last to add its shares
+  float tail[2];  // CHAIN: the shared gate's logit and the sum of squares, for the last block
+  int ridx[32];
+  float rwts[32];
+};
+static_assert(sizeof(Ctl) <= CTL_BYTES, "control block too large");
+
+// What a chained launch adds: the next layer's router matrix [e_next + 1, H] (bf16), its norm weight, and where
+// this block's partial logits go: partials[block][c], c < e_next + 1 the partial dot products of router row c with
+// (new hidden state * norm weight) over this block's rows, c = e_next + 1 the partial sum of squares.
+struct Chain {
+  const __nv_bfloat16* w;  // nullptr: last layer of the chain, nothing to prepare
+  const float* nw;
+  float* ws;               // the chain workspace (chain.cuh)
+  int e_next;
+  int have_prev;           // the routing is read from the workspace replicas instead of idx / wts / sgate
+  float eps;
+  int* idx_out;            // where the next layer's routing goes (the caller's idx / wts / sgate, and logits or nullptr)
+  float* wts_out;
+  float* sgate_out;
+  float* logits_out;
 };
 
+// CHAIN = true: the activations come from this block's replica in the workspace, the new hidden state is also
+// written to the workspace replicas, and (chain.w != nullptr) the block writes its share of the NEXT layer's router logits (the logits are linear in
+// the hidden state; the 1 / rms factor is applied by the kernel that sums the shares, router::k_router_tail).
+// The router rows are fetched before the dependency wait, so the next layer's routing costs no matrix read after
+// this kernel and no second pass over the hidden state.
+template <bool CHAIN>
 __global__ void __launch_bounds__(THREADS, 1)
     k_moe_down(const uint8_t* __restrict__ Q, const __half2* __restrict__ SM, const int8_t* __restrict__ shq,
-               const __half* __restrict__ shs, const float* __restrict__ act, const int* __restrict__ idx,
+               const __half* __restrict__ shs, const unsigned char* __restrict__ actq, const int* __restrict__ idx,
                const float* __restrict__ wts, const float* __restrict__ sgate, const float* res, float* y,
-               const char* pf, size_t pf_bytes) {
+               const char* pf, size_t pf_bytes, Chain chain) {
   extern __shared__ __align__(128) unsigned char dyn[];
   Ctl& ctl = *reinterpret_cast<Ctl*>(dyn);
   unsigned char* qa = dyn + CTL_BYTES;
-  unsigned char* qs = qa + QA_BYTES;
-  unsigned char* st = qs + QS_BYTES;
+  unsigned char* st = qa + ACTQ_BYTES;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned G = gridDim.x, b = blockIdx.x;
   const int n0 = (int)((long long)H * b / G), n1 = (int)((long long)H * (b + 1) / G);
   const int nr = n1 - n0;  // <= RT because the grid has at least MIN_GRID blocks
   DRB_TRACE_POINT(20, 0);
+  const bool chain_out = CHAIN && chain.w != nullptr;
+  if (CHAIN) {
+    if (chain.have_prev) {
+      const float* rep = chain.ws + chainws::OFF_ROUTE + (b % chainws::ROUTE_REPS) * chainws::ROUTE_STRIDE;
+      idx = reinterpret_cast<const int*>(rep), wts = rep + 8, sgate = rep + 16;
+    }
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(&ctl.full, 1);
     mbar_fence_init();
   }
   __syncthreads();
+#ifndef DRB_D_LATE
   pdl_launch_dependents();
+#endif
 
   if (warp == CW) {
     // ---------------- producer warp. This kernel is only ever launched behind k_moe_gate_up, which lets its
@@ -289,7 +381,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       if (lane == 0) mbar_expect_tx(&ctl.full, (unsigned)(nr * (TOPK * (QROW + SMROW) + I)));
       __syncwarp();
       if (lane < TOPK) {
-        const size_t row = (size_t)idx[lane] * H + n0;
+        const size_t row = (size_t)__ldcg(idx + lane) * H + n0;
         bulk_g2s(st + lane * EXPERT_BYTES, Q + row * QROW, (unsigned)(nr * QROW), &ctl.full);
         bulk_g2s(st + lane * EXPERT_BYTES + RT * QROW, reinterpret_cast<const unsigned char*>(SM) + row * SMROW,
                  (unsigned)(nr * SMROW), &ctl.full);
@@ -306,35 +398,55 @@ __global__ void __launch_bounds__(THREADS, 1)
   const int ke = warp & (TOPK - 1), rh = warp >> 3;
   // The shared expert's scales are constants: fetched before the dependency wait.
   const float ssc = warp < nr ? __half2float(__ldg(shs + (size_t)(n0 + warp) * (I / 128) + (lane >> 3))) : 0.f;
-  pdl_wait();  // act, and everything the caller wrote before
-  DRB_TRACE_POINT(22, 0);
-  // Quantise the 9 x 512 activations once per block: coalesced reads (all in flight at once).
-  constexpr int NR4 = TOPK * I / 4, NS4 = I / 4;  // float4s of the routed part and of the shared part
-  constexpr int AV = (NR4 + NS4 + NT - 1) / NT;
-  float4 av[AV];
+  float wn[RT];     // CHAIN: router row threadIdx.x of the next layer, columns n0 .. n0 + nr
+  float nwn = 0.f;  // CHAIN: the next layer's norm weight of row n0 + threadIdx.x
+  if (CHAIN) {
 #pragma unroll
-  for (int i = 0; i < AV; ++i) {
-    const int g = threadIdx.x + i * NT;
-    av[i] = g < NR4 + NS4 ? reinterpret_cast<const float4*>(act)[g] : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < RT; ++i) wn[i] = 0.f;
+    if (chain_out) {
+      // a chained launch has exactly H / RT blocks: the block's 16 columns of a router row are 32 aligned bytes
+      if ((int)threadIdx.x <= chain.e_next) {
+        const uint4* wr = reinterpret_cast<const uint4*>(chain.w + (size_t)threadIdx.x * H + n0);
+        const uint4 a = __ldg(wr), c = __ldg(wr + 1);
+        const uint32_t w8[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) wn[2 * i] = __uint_as_float(w8[i] << 16), wn[2 * i + 1] = __uint_as_float(w8[i] & 0xffff0000u);
+      }
+      if ((int)threadIdx.x < nr) nwn = __ldg(chain.nw + n0 + threadIdx.x);
+    }
+    if (threadIdx.x < RT) ctl.xs[threadIdx.x] = 0.f, ctl.ysq[threadIdx.x] = 0.f;
   }
-  const float sg = sigmoid_f(sgate[0]);
-  float wk[TOPK];
-#pragma unroll
-  for (int k = 0; k < TOPK; ++k) wk[k] = wts[k];
-#pragma unroll
-  for (int i = 0; i < AV; ++i) {
-    const int g = threadIdx.x + i * NT;  // a warp's 32 float4s fall on one side of NR4 (both multiples of 32)
-    if (g - lane < NR4) quant_store_eo(qa, g, av[i], true);
-    else quant_store_nat(qs, g - NR4, av[i], g < NR4 + NS4);
+  pdl_wait();  // the activations, and everything the caller wrote before
+#ifdef DRB_D_LATE
+  pdl_launch_dependents();
+#endif
+  DRB_TRACE_POINT(22, 0);
+  // The block copies the 16 KB of activations once (read at L2: they were written while this block may already
+  // have been resident, so nothing of them may come from this multiprocessor's L1), together with the routing
+  // weights; then half-warps take alternate rows, lane & 15 = 16-byte chunk cc of the row, k in [32 cc, 32 cc + 32):
+  // its activations are block ke * 16 + cc.
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(actq);
+    const uint4 p0 = __ldcg(src + threadIdx.x), p1 = __ldcg(src + NT + threadIdx.x);
+    float r = 0.f;
+    if (threadIdx.x < TOPK) r = __ldcg(wts + threadIdx.x);
+    else if (threadIdx.x == TOPK) r = __ldcg(sgate);
+    reinterpret_cast<uint4*>(qa)[threadIdx.x] = p0;
+    reinterpret_cast<uint4*>(qa)[NT + threadIdx.x] = p1;
+    if (threadIdx.x < TOPK) ctl.wk[threadIdx.x] = r;
+    else if (threadIdx.x == TOPK) ctl.sgate = r;
   }
   named_sync<NT>();
-  // Half-warps take alternate rows; lane & 15 = 16-byte chunk cc of the row, k in [32 cc, 32 cc + 32).
   const int cc = lane & 15, half = lane >> 4;
   QAct<32, true> aq;
   float A;
   qact_load(aq, A, qa + (size_t)(ke * (I / 32) + cc) * QB32_BYTES);
   QAct<16, false> sq;  // shared expert: the whole warp per row, lane = 16-byte chunk of 16 int8
-  qact_load(sq, qs + (size_t)lane * QB16_BYTES);
+  qact_load(sq, qa + ACTQ_SHARED + (size_t)lane * QB16_BYTES);
+  const float sg = sigmoid_f(ctl.sgate);
+  float wk[TOPK];
+#pragma unroll
+  for (int k = 0; k < TOPK; ++k) wk[k] = ctl.wk[k];
   DRB_TRACE_POINT(23, 0);
 
   mbar_wait(&ctl.full, 0, DRB_ERR_FULL_WAIT);
@@ -378,7 +490,77 @@ __global__ void __launch_bounds__(THREADS, 1)
     float acc = 0.f;
 #pragma unroll
     for (int k = 0; k < TOPK; ++k) acc += wk[k] * ctl.part[k][lr];
-    y[n0 + lr] = res[n0 + lr] + sg * ctl.part[TOPK][lr] + acc;
+    const float yn = __ldcg(res + n0 + lr) + sg * ctl.part[TOPK][lr] + acc;
+    y[n0 + lr] = yn;
+    if (CHAIN) {
+      ctl.xs[lr] = yn * nwn, ctl.ysq[lr] = yn * yn;
+#pragma unroll
+      for (int c = 0; c < chainws::VEC_REPS; ++c) chain.ws[chainws::OFF_YREP + c * chainws::HID + n0 + lr] = yn;
+    }
+  }
+  if (chain_out) {
+    named_sync<NT>();
+    unsigned long long* acc0 = reinterpret_cast<unsigned long long*>(chain.ws + chainws::OFF_ACC);
+    unsigned long long* accp = acc0 + (size_t)(b % chainws::ACC_REPS) * chainws::ACC_COLS;
+    unsigned* counter = reinterpret_cast<unsigned*>(chain.ws + chainws::OFF_COUNTER);
+    const int E = chain.e_next;
+    if ((int)threadIdx.x <= E) {
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < RT; ++i) acc = fmaf(wn[i], ctl.xs[i], acc);
+      atomicAdd(accp + threadIdx.x, (unsigned long long)__double2ll_rn((double)acc * chainws::FX_LOGIT));
+    } else if ((int)threadIdx.x == E + 1) {
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < RT; ++i) acc += ctl.ysq[i];
+      atomicAdd(accp + threadIdx.x, (unsigned long long)__double2ll_rn((double)acc * chainws::FX_SSQ));
+    }
+    DRB_TRACE_POINT(26, 0);
+    // The last block to arrive turns the totals into the next layer's routing.
+    __threadfence();
+    named_sync<NT>();
+    if (threadIdx.x == 0) ctl.last = atomicAdd(counter, 1u) == G - 1 ? 1 : 0;
+    named_sync<NT>();
+    if (!ctl.last || threadIdx.x >= 256) return;
+    __threadfence();
+    DRB_TRACE_ANY(51, 0);
+    const int e = threadIdx.x;
+    long long mine = 0, t = 0;
+#pragma unroll
+    for (int r = 0; r < chainws::ACC_REPS; ++r) mine += (long long)__ldcg(acc0 + r * chainws::ACC_COLS + e);
+#pragma unroll
+    for (int r = 0; r < chainws::ACC_REPS; ++r) acc0[r * chainws::ACC_COLS + e] = 0ull;
+    if (e < 2) {  // columns 256 and 257 exist only when E = 256; reading them is harmless otherwise
+#pragma unroll
+      for (int r = 0; r < chainws::ACC_REPS; ++r) t += (long long)__ldcg(acc0 + r * chainws::ACC_COLS + 256 + e);
+#pragma unroll
+      for (int r = 0; r < chainws::ACC_REPS; ++r) acc0[r * chainws::ACC_COLS + 256 + e] = 0ull;
+      if (256 + e == E) ctl.tail[0] = (float)((double)t * (1.0 / chainws::FX_LOGIT));
+      if (256 + e == E + 1) ctl.tail[1] = (float)((double)t * (1.0 / chainws::FX_SSQ));
+    }
+    if (e == E) ctl.tail[0] = (float)((double)mine * (1.0 / chainws::FX_LOGIT));
+    if (e == E + 1) ctl.tail[1] = (float)((double)mine * (1.0 / chainws::FX_SSQ));
+    if (e == 0) *counter = 0u;
+    asm volatile("bar.sync 2, 256;" ::: "memory");
+    const float inv = rsqrtf(ctl.tail[1] / (float)H + chain.eps);
+    const float v = e < E ? (float)((double)mine * (1.0 / chainws::FX_LOGIT)) * inv : -INFINITY;
+    const float sgn = ctl.tail[0] * inv;
+    if (chain.logits_out) {
+      if (e < E) chain.logits_out[e] = v;
+      if (e == 0) chain.logits_out[E] = sgn;
+    }
+    router::TopkSmem& tk = *reinterpret_cast<router::TopkSmem*>(st);  // the weight stage is free by now
+    router::softmax_topk<2>(v, E, TOPK, ctl.ridx, ctl.rwts, tk);
+    asm volatile("bar.sync 2, 256;" ::: "memory");
+    DRB_TRACE_ANY(53, 0);
+    if (e < TOPK) chain.idx_out[e] = ctl.ridx[e], chain.wts_out[e] = ctl.rwts[e];
+    if (e == 0) chain.sgate_out[0] = sgn;
+    {
+      float* rep = chain.ws + chainws::OFF_ROUTE + (size_t)(e >> 4) * chainws::ROUTE_STRIDE;
+      const int j = e & 15;
+      rep[j] = j < 8 ? __int_as_float(ctl.ridx[j]) : ctl.rwts[j - 8];
+      if (j == 0) rep[16] = sgn;
+    }
   }
   DRB_TRACE_POINT(25, 0);
 }
@@ -386,16 +568,21 @@ __global__ void __launch_bounds__(THREADS, 1)
 }  // namespace dn
 
 static cudaError_t configure_all() {
-  cudaError_t e = cudaFuncSetAttribute(gu::k_moe_gate_up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gu::SMEM_BYTES);
+  cudaError_t e = cudaFuncSetAttribute(gu::k_moe_gate_up<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gu::SMEM_BYTES);
   if (e != cudaSuccess) return e;
-  if ((e = cudaFuncSetAttribute(dn::k_moe_down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dn::SMEM_BYTES)) != cudaSuccess) return e;
-  if ((e = drb_carveout(gu::k_moe_gate_up)) != cudaSuccess) return e;
-  return drb_carveout(dn::k_moe_down);
+  if ((e = cudaFuncSetAttribute(gu::k_moe_gate_up<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gu::SMEM_BYTES)) != cudaSuccess) return e;
+  if ((e = drb_carveout(gu::k_moe_gate_up<true>)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(dn::k_moe_down<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dn::SMEM_BYTES)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(dn::k_moe_down<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dn::SMEM_BYTES)) != cudaSuccess) return e;
+  if ((e = drb_carveout(gu::k_moe_gate_up<false>)) != cudaSuccess) return e;
+  if ((e = drb_carveout(dn::k_moe_down<true>)) != cudaSuccess) return e;
+  return drb_carveout(dn::k_moe_down<false>);
 }
 
 }  // namespace moe
 
-// act must hold (topk + 1) * I floats. x, res and y may be one buffer (the reference's caller passes the
+// act must hold (topk + 1) * I floats; between the two kernels it carries the activations as block fixed point
+// (see ACTQ_SHARED above), not as floats. x, res and y may be one buffer (the reference's caller passes the
 // same pointer three times): every read of x happens in the first kernel, every write of y in the second.
 // Reference: kernels/drama.cu:588-599; src/ffi.rs:42-46.
 extern "C" int dr_moe_decode(const uint8_t* gu_q, const __half2* gu_sm, const uint8_t* d_q, const __half2* d_sm,
@@ -406,11 +593,50 @@ extern "C" int dr_moe_decode(const uint8_t* gu_q, const __half2* gu_sm, const ui
   if (H != moe::H || I != moe::I || topk != moe::TOPK) return -1;
   const DrbDevice& dev = drb_device(st);
   if (!dev.ready) return -2;
-  const int g_gu = dev.sms > moe::gu::MIN_GRID ? dev.sms : moe::gu::MIN_GRID;
+  const int g_gu = moe::gu::GRID;
   const int g_dn = dev.sms > moe::dn::MIN_GRID ? dev.sms : moe::dn::MIN_GRID;
-  drb_launch(moe::gu::k_moe_gate_up, dim3(g_gu), dim3(moe::gu::THREADS), moe::gu::SMEM_BYTES, st, dev.pdl, gu_q, gu_sm,
-             sgu_q, sgu_s, x, idx, act, nw, eps);
-  drb_launch(moe::dn::k_moe_down, dim3(g_dn), dim3(moe::dn::THREADS), moe::dn::SMEM_BYTES, st, dev.pdl, d_q, d_sm, sd_q,
-             sd_s, (const float*)act, idx, wts, sgate, res, y, pf, pf_bytes);
+  drb_launch(moe::gu::k_moe_gate_up<false>, dim3(g_gu), dim3(moe::gu::THREADS), moe::gu::SMEM_BYTES, st, dev.pdl, gu_q, gu_sm,
+             sgu_q, sgu_s, x, idx, reinterpret_cast<unsigned char*>(act), nw, eps, (float*)nullptr, 0, dev.down_warmup ? d_q : nullptr, d_sm, sd_q,
+             (const char*)nullptr, (size_t)0);
+  drb_launch(moe::dn::k_moe_down<false>, dim3(g_dn), dim3(moe::dn::THREADS), moe::dn::SMEM_BYTES, st, dev.pdl, d_q, d_sm, sd_q,
+             sd_s, reinterpret_cast<const unsigned char*>(act), idx, wts, sgate, res, y, pf, pf_bytes, moe::dn::Chain{});
   return 0;
 }
+
+// No counterpart in the reference. dr_moe_decode as one link of a chain over consecutive MoE layers:
+//   * next_router != NULL: the down kernel also computes the NEXT layer's routing. Every block adds its share of
+//     next_router . (y * next_nw) and of sum(y^2) to fixed-point accumulators in the workspace (integer atomics: the
+//     totals do not depend on the order of arrival); the last block to arrive applies rsqrt(mean(y^2) + eps), runs
+//     softmax + top-k and OVERWRITES idx / wts / sgate (and logits, if given) with the next layer's routing, exactly
+//     what dr_router_topk(next_router, y, next_nw, ...) would write. The router rows are fetched while the kernel
+//     waits for its activations, so the next layer needs no router launch at all.
+//     next_router == NULL ends the chain (plain outputs only).
+//   * have_prev != 0: this layer's routing was produced by the previous chained call on the same workspace and x is
+//     that call's y: both are then read from the workspace's replicas (one per group of blocks) instead of
+//     idx / wts / sgate / x, which must still be passed and hold the same values.
+// workspace: drb_moe_chain_workspace_bytes() bytes, owned by the caller, zeroed once, private to one stream.
+// 8 <= e_next <= 256. Same limits and return codes as dr_moe_decode.
+extern "C" int drb_moe_decode_chained(const uint8_t* gu_q, const __half2* gu_sm, const uint8_t* d_q, const __half2* d_sm,
+                                      const int8_t* sgu_q, const __half* sgu_s, const int8_t* sd_q, const __half* sd_s,
+                                      const float* x, int* idx, float* wts, float* sgate, const float* res, float* act,
+                                      float* y, int H, int I, int topk, const float* nw, float eps,
+                                      const __nv_bfloat16* next_router, const float* next_nw, int e_next, float* logits,
+                                      float* workspace, int have_prev, cudaStream_t st) {
+  if (H != moe::H || I != moe::I || topk != moe::TOPK || !workspace) return -1;
+  if (next_router && (e_next < 8 || e_next > 256 || !next_nw)) return -1;
+  const DrbDevice& dev = drb_device(st);
+  if (!dev.ready) return -2;
+  const int g_gu = moe::gu::GRID;
+  const int g_dn = moe::dn::MIN_GRID;  // 16 rows per block: the block's columns of a router row are 32 aligned bytes
+  drb_launch(moe::gu::k_moe_gate_up<true>, dim3(g_gu), dim3(moe::gu::THREADS), moe::gu::SMEM_BYTES, st, dev.pdl, gu_q, gu_sm,
+             sgu_q, sgu_s, x, (const int*)idx, reinterpret_cast<unsigned char*>(act), nw, eps, workspace, have_prev,
+             dev.down_warmup ? d_q : nullptr, d_sm, sd_q, reinterpret_cast<const char*>(next_router),
+             next_router ? (size_t)(e_next + 1) * moe::H * 2 : (size_t)0);
+  drb_launch(moe::dn::k_moe_down<true>, dim3(g_dn), dim3(moe::dn::THREADS), moe::dn::SMEM_BYTES, st, dev.pdl, d_q, d_sm, sd_q,
+             sd_s, reinterpret_cast<const unsigned char*>(act), (const int*)idx, (const float*)wts, (const float*)sgate, res, y,
+             (const char*)nullptr, (size_t)0,
+             moe::dn::Chain{next_router, next_nw, workspace, e_next, have_prev, eps, idx, wts, sgate, logits});
+  return 0;
+}
+
+extern "C" size_t drb_moe_chain_workspace_bytes(void) { return (size_t)chainws::TOTAL_FLOATS * sizeof(float); }

@@ -157,9 +157,9 @@ __global__ void __launch_bounds__(THREADS)
   pdl_wait();
   const int r = blockIdx.x;
   const float* l = logits + (size_t)r * stride;
-  const float v = (int)threadIdx.x < E ? l[threadIdx.x] : -INFINITY;
+  const float v = (int)threadIdx.x < E ? __ldcg(l + threadIdx.x) : -INFINITY;
   softmax_topk(v, E, topk, idx + (size_t)r * topk, wts + (size_t)r * topk, sm);
-  if (threadIdx.x == 0) sgate[r] = l[E];
+  if (threadIdx.x == 0) sgate[r] = __ldcg(l + E);
 }
 
 // Decode router. Block b owns rows [b*R, b*R + R) of the [E+1, 2048] bf16 matrix, fetched with one
@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(THREADS)
 
   // RMSNorm scale, recomputed by every block (8 KB of x from L2).
   const float4* x4 = reinterpret_cast<const float4*>(x);
-  const float4 xa = x4[threadIdx.x * 2], xb = x4[threadIdx.x * 2 + 1];  // k = 8*t .. 8*t+7
+  const float4 xa = __ldcg(x4 + threadIdx.x * 2), xb = __ldcg(x4 + threadIdx.x * 2 + 1);  // k = 8*t .. 8*t+7
   float inv = 1.f;
   if (nw) {
     float ss = xa.x * xa.x + xa.y * xa.y + xa.z * xa.z + xa.w * xa.w + xb.x * xb.x + xb.y * xb.y + xb.z * xb.z + xb.w * xb.w;
@@ -345,7 +345,7 @@ __global__ void __launch_bounds__(THREADS, 1)
   pdl_wait();  // x is the previous kernel's output
   DRB_TRACE_POINT(1, 0);
 
-  const float4 xa = reinterpret_cast<const float4*>(x)[threadIdx.x * 2], xb = reinterpret_cast<const float4*>(x)[threadIdx.x * 2 + 1];
+  const float4 xa = __ldcg(reinterpret_cast<const float4*>(x) + threadIdx.x * 2), xb = __ldcg(reinterpret_cast<const float4*>(x) + threadIdx.x * 2 + 1);
   float inv = 1.f;
   float4 wa = make_float4(1.f, 1.f, 1.f, 1.f), wb = wa;
   if (nw) {

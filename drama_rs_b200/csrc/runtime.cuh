@@ -54,6 +54,8 @@ static cudaError_t setup(int d) {
   dv.prefill_mma = !(pv && pv[0] == 's');
   const char* rv = getenv("DRB_ROUTER");
   dv.router_cluster = !(rv && rv[0] == 'g');
+  const char* dw = getenv("DRB_DOWN_WARMUP");
+  dv.down_warmup = dw && dw[0] == '1';  // measured 0.3 us per layer slower than leaving the rows to the down kernel
   if ((e = gemv::configure_all()) != cudaSuccess) return e;
   if ((e = router::configure_all()) != cudaSuccess) return e;
   if ((e = pf::configure_all()) != cudaSuccess) return e;

@@ -49,7 +49,71 @@ namespace stack {
 using moe::H;
 using moe::I;
 using moe::TOPK;
-namespace gu = moe::gu;
+
+// The persistent kernel keeps its own work split for the gate/up phase (byte-balanced shares of units, cut into
+// chunks that travel through a ring of stages) and quantises the activations per block in the down phase.
+namespace gu1 {
+constexpr int CW = 16;                                    // consumer warps, one unit (gate row + up row) at a time each
+constexpr int NT = CW * 32;                               // consumer threads
+constexpr int THREADS = NT + 32;                          // + one producer warp
+constexpr int MIN_GRID = 148;                             // a block then owns <= 28 routed and <= 4 shared units
+constexpr int UPW = 2;                                    // units per warp and pass: 32 units over 16 warps
+constexpr int RU = 4;                                     // routed units per chunk
+constexpr int SU = 2;                                     // shared-expert units per chunk
+constexpr int QROW = H / 2;                               // 1024 bytes of nibbles per routed row
+constexpr int SMROW = (H / 64) * 4;                       // 128 bytes of (scale, min) per routed row
+constexpr int SSROW = (H / 128) * 2;                      // 32 bytes of scales per shared-expert row
+constexpr int STAGE_BYTES = RU * 2 * (QROW + SMROW);      // 9216; a shared chunk needs SU*2*(H+32) = 8320
+constexpr int STAGES = 12;                                // >= 3 shared + 8 routed chunks (chunks are aligned)
+constexpr int CTL_BYTES = 1024;
+constexpr int QX_BYTES = (H / 32) * QB32_BYTES;           // the normalised activations as limb blocks
+constexpr size_t SMEM_BYTES = CTL_BYTES + QX_BYTES + (size_t)STAGES * STAGE_BYTES;
+static_assert(SU * 2 * (H + SSROW) <= STAGE_BYTES, "shared-expert chunk does not fit a stage");
+static_assert(NT == H / 4, "one float4 of x per consumer thread");
+
+struct Ctl {
+  uint64_t full[STAGES];
+  float red[CW];
+};
+
+struct Plan {
+  int us0, us1, ur0, ur1;  // this block's shared units and routed units
+  int sc0, nsc, rc0, nrc;  // aligned chunk ranges
+  DRB_DEV Plan(unsigned b, unsigned G) {
+    us0 = (int)((long long)I * b / G), us1 = (int)((long long)I * (b + 1) / G);
+    ur0 = (int)((long long)TOPK * I * b / G), ur1 = (int)((long long)TOPK * I * (b + 1) / G);
+    sc0 = us0 / SU, nsc = us1 > us0 ? (us1 + SU - 1) / SU - sc0 : 0;
+    rc0 = ur0 / RU, nrc = ur1 > ur0 ? (ur1 + RU - 1) / RU - rc0 : 0;
+  }
+  DRB_DEV int chunks() const { return nsc + nrc; }
+  DRB_DEV int units() const { return (us1 - us0) + (ur1 - ur0); }
+  // Units [ua, ub) of chunk t and the aligned base of the chunk. Chunks are aligned to multiples of
+  // RU (SU), so a routed chunk never straddles two experts.
+  DRB_DEV void chunk(int t, bool& shared, int& base, int& ua, int& ub) const {
+    shared = t < nsc;
+    if (shared) {
+      base = (sc0 + t) * SU, ua = max(base, us0), ub = min(base + SU, us1);
+    } else {
+      base = (rc0 + t - nsc) * RU, ua = max(base, ur0), ub = min(base + RU, ur1);
+    }
+  }
+  // The o-th unit of the block: shared units first. Returns its chunk and its slot in the chunk.
+  DRB_DEV void unit(int o, bool& shared, int& u, int& t, int& slot) const {
+    shared = o < us1 - us0;
+    if (shared) {
+      u = us0 + o, t = u / SU - sc0, slot = u % SU;
+    } else {
+      u = ur0 + o - (us1 - us0), t = nsc + u / RU - rc0, slot = u % RU;
+    }
+  }
+};
+}  // namespace gu1
+namespace dn1 {
+constexpr int QA_BYTES = (TOPK * I / 32) * QB32_BYTES;  // routed activations as even/odd limb blocks
+constexpr int QS_BYTES = (I / 16) * QB16_BYTES;         // the shared expert's activations, natural order
+}  // namespace dn1
+
+
 namespace dn = moe::dn;
 
 constexpr int CW = 16;
@@ -68,15 +132,15 @@ struct Workspace {
 // Shared memory map.
 constexpr int CTL_BYTES = 4096;
 constexpr int XS_BYTES = H * 4;                          // normalised x in fp32 (router dot)
-constexpr int QX_BYTES = gu::QX_BYTES;                   // normalised x as limb blocks
+constexpr int QX_BYTES = gu1::QX_BYTES;                   // normalised x as limb blocks
 constexpr int RW_BYTES = 2 * 2 * H * 2;                  // two router rows, double-buffered over layers
-constexpr int QA_BYTES = dn::QA_BYTES + dn::QS_BYTES;    // act as limb blocks
-constexpr int RING_BYTES = gu::STAGES * gu::STAGE_BYTES; // gate/up chunks
+constexpr int QA_BYTES = dn1::QA_BYTES + dn1::QS_BYTES;    // act as limb blocks
+constexpr int RING_BYTES = gu1::STAGES * gu1::STAGE_BYTES; // gate/up chunks
 constexpr int DST_BYTES = dn::STAGE_BYTES;               // down rows
 constexpr size_t SMEM_BYTES = CTL_BYTES + XS_BYTES + QX_BYTES + RW_BYTES + QA_BYTES + RING_BYTES + DST_BYTES;
 
 struct Ctl {
-  uint64_t gfull[gu::STAGES];  // one phase per layer each
+  uint64_t gfull[gu1::STAGES];  // one phase per layer each
   uint64_t dfull_routed, dfull_shared;
   uint64_t rfull[2];           // router rows of even / odd layers
   float red[CW];
@@ -136,17 +200,17 @@ __global__ void __launch_bounds__(THREADS, 1)
   unsigned char* qx = dyn + CTL_BYTES + XS_BYTES;
   unsigned char* rw = qx + QX_BYTES;
   unsigned char* qa = rw + RW_BYTES;
-  unsigned char* qs = qa + dn::QA_BYTES;
-  unsigned char* ring = qs + dn::QS_BYTES;
+  unsigned char* qs = qa + dn1::QA_BYTES;
+  unsigned char* ring = qs + dn1::QS_BYTES;
   unsigned char* dst = ring + RING_BYTES;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned G = gridDim.x, b = blockIdx.x;
-  const gu::Plan plan(b, G);
+  const gu1::Plan plan(b, G);
   const int n0 = (int)((long long)H * b / G), n1 = (int)((long long)H * (b + 1) / G), nr = n1 - n0;
   const int rrow0 = 2 * (int)b, nrr = max(0, min(2, E + 1 - rrow0));
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < gu::STAGES; ++s) mbar_init(&ctl.gfull[s], 1);
+    for (int s = 0; s < gu1::STAGES; ++s) mbar_init(&ctl.gfull[s], 1);
     mbar_init(&ctl.dfull_routed, 1);
     mbar_init(&ctl.dfull_shared, 1);
     mbar_init(&ctl.rfull[0], 1);
@@ -170,16 +234,16 @@ __global__ void __launch_bounds__(THREADS, 1)
       bool shared;
       int base, ua, ub;
       plan.chunk(lane, shared, base, ua, ub);
-      unsigned char* d = ring + (size_t)lane * gu::STAGE_BYTES;
+      unsigned char* d = ring + (size_t)lane * gu1::STAGE_BYTES;
       const int n = ub - ua, slot = ua - base;
       const unsigned char* q = static_cast<const unsigned char*>(layers[l].sgu_q);
       const unsigned char* sp = static_cast<const unsigned char*>(layers[l].sgu_s);
       uint64_t* bar = &ctl.gfull[lane];
-      mbar_expect_tx(bar, (unsigned)(n * 2 * (H + gu::SSROW)));
+      mbar_expect_tx(bar, (unsigned)(n * 2 * (H + gu1::SSROW)));
       bulk_g2s(d + slot * H, q + (size_t)ua * H, (unsigned)(n * H), bar);
-      bulk_g2s(d + (gu::SU + slot) * H, q + ((size_t)I + ua) * H, (unsigned)(n * H), bar);
-      bulk_g2s(d + 2 * gu::SU * H + slot * gu::SSROW, sp + (size_t)ua * gu::SSROW, (unsigned)(n * gu::SSROW), bar);
-      bulk_g2s(d + 2 * gu::SU * H + (gu::SU + slot) * gu::SSROW, sp + ((size_t)I + ua) * gu::SSROW, (unsigned)(n * gu::SSROW), bar);
+      bulk_g2s(d + (gu1::SU + slot) * H, q + ((size_t)I + ua) * H, (unsigned)(n * H), bar);
+      bulk_g2s(d + 2 * gu1::SU * H + slot * gu1::SSROW, sp + (size_t)ua * gu1::SSROW, (unsigned)(n * gu1::SSROW), bar);
+      bulk_g2s(d + 2 * gu1::SU * H + (gu1::SU + slot) * gu1::SSROW, sp + ((size_t)I + ua) * gu1::SSROW, (unsigned)(n * gu1::SSROW), bar);
     }
   };
   auto issue_shared_dn = [&](int l) {  // the shared expert's down rows of this block
@@ -195,18 +259,18 @@ __global__ void __launch_bounds__(THREADS, 1)
       bool shared;
       int base, ua, ub;
       plan.chunk(t, shared, base, ua, ub);
-      unsigned char* d = ring + (size_t)t * gu::STAGE_BYTES;
+      unsigned char* d = ring + (size_t)t * gu1::STAGE_BYTES;
       const int n = ub - ua, slot = ua - base;
       const int k = ua / I, j = ua % I;
       const size_t ek = (size_t)ctl.idx[k];
-      const unsigned char* q = static_cast<const unsigned char*>(layers[l].gu_q) + ek * (2 * I) * gu::QROW;
-      const unsigned char* smp = static_cast<const unsigned char*>(layers[l].gu_sm) + ek * (2 * I) * gu::SMROW;
+      const unsigned char* q = static_cast<const unsigned char*>(layers[l].gu_q) + ek * (2 * I) * gu1::QROW;
+      const unsigned char* smp = static_cast<const unsigned char*>(layers[l].gu_sm) + ek * (2 * I) * gu1::SMROW;
       uint64_t* bar = &ctl.gfull[t];
-      mbar_expect_tx(bar, (unsigned)(n * 2 * (gu::QROW + gu::SMROW)));
-      bulk_g2s(d + slot * gu::QROW, q + (size_t)j * gu::QROW, (unsigned)(n * gu::QROW), bar);
-      bulk_g2s(d + (gu::RU + slot) * gu::QROW, q + ((size_t)I + j) * gu::QROW, (unsigned)(n * gu::QROW), bar);
-      bulk_g2s(d + 2 * gu::RU * gu::QROW + slot * gu::SMROW, smp + (size_t)j * gu::SMROW, (unsigned)(n * gu::SMROW), bar);
-      bulk_g2s(d + 2 * gu::RU * gu::QROW + (gu::RU + slot) * gu::SMROW, smp + ((size_t)I + j) * gu::SMROW, (unsigned)(n * gu::SMROW), bar);
+      mbar_expect_tx(bar, (unsigned)(n * 2 * (gu1::QROW + gu1::SMROW)));
+      bulk_g2s(d + slot * gu1::QROW, q + (size_t)j * gu1::QROW, (unsigned)(n * gu1::QROW), bar);
+      bulk_g2s(d + (gu1::RU + slot) * gu1::QROW, q + ((size_t)I + j) * gu1::QROW, (unsigned)(n * gu1::QROW), bar);
+      bulk_g2s(d + 2 * gu1::RU * gu1::QROW + slot * gu1::SMROW, smp + (size_t)j * gu1::SMROW, (unsigned)(n * gu1::SMROW), bar);
+      bulk_g2s(d + 2 * gu1::RU * gu1::QROW + (gu1::RU + slot) * gu1::SMROW, smp + ((size_t)I + j) * gu1::SMROW, (unsigned)(n * gu1::SMROW), bar);
     }
     if (nr > 0) {
       if (lane == 15) mbar_expect_tx(&ctl.dfull_routed, (unsigned)(nr * TOPK * (dn::QROW + dn::SMROW)));
@@ -315,22 +379,22 @@ __global__ void __launch_bounds__(THREADS, 1)
           int u, t, slot;
           plan.unit(o, shared, u, t, slot);
           uid[i] = shared ? TOPK * I + u : u;
-          const unsigned char* st = ring + (size_t)t * gu::STAGE_BYTES;
+          const unsigned char* st = ring + (size_t)t * gu1::STAGE_BYTES;
           mbar_wait(&ctl.gfull[t], par, DRB_ERR_FULL_WAIT);
           if (shared) {
             const uint4* gr = reinterpret_cast<const uint4*>(st + (size_t)slot * H);
-            const uint4* ur = reinterpret_cast<const uint4*>(st + (size_t)(gu::SU + slot) * H);
-            const __half* gs = reinterpret_cast<const __half*>(st + 2 * gu::SU * H + (size_t)slot * gu::SSROW);
-            const __half* us = reinterpret_cast<const __half*>(st + 2 * gu::SU * H + (size_t)(gu::SU + slot) * gu::SSROW);
+            const uint4* ur = reinterpret_cast<const uint4*>(st + (size_t)(gu1::SU + slot) * H);
+            const __half* gs = reinterpret_cast<const __half*>(st + 2 * gu1::SU * H + (size_t)slot * gu1::SSROW);
+            const __half* us = reinterpret_cast<const __half*>(st + 2 * gu1::SU * H + (size_t)(gu1::SU + slot) * gu1::SSROW);
             v[2 * i] = __half2float(gs[lane >> 2]) * x0.delta * dot32_q8_eo(gr[2 * lane], gr[2 * lane + 1], x0, 0) +
                        __half2float(gs[8 + (lane >> 2)]) * x1.delta * dot32_q8_eo(gr[64 + 2 * lane], gr[64 + 2 * lane + 1], x1, 0);
             v[2 * i + 1] = __half2float(us[lane >> 2]) * x0.delta * dot32_q8_eo(ur[2 * lane], ur[2 * lane + 1], x0, 0) +
                            __half2float(us[8 + (lane >> 2)]) * x1.delta * dot32_q8_eo(ur[64 + 2 * lane], ur[64 + 2 * lane + 1], x1, 0);
           } else {
-            const uint4* gr = reinterpret_cast<const uint4*>(st + (size_t)slot * gu::QROW);
-            const uint4* ur = reinterpret_cast<const uint4*>(st + (size_t)(gu::RU + slot) * gu::QROW);
-            const __half2* gs = reinterpret_cast<const __half2*>(st + 2 * gu::RU * gu::QROW + (size_t)slot * gu::SMROW);
-            const __half2* us = reinterpret_cast<const __half2*>(st + 2 * gu::RU * gu::QROW + (size_t)(gu::RU + slot) * gu::SMROW);
+            const uint4* gr = reinterpret_cast<const uint4*>(st + (size_t)slot * gu1::QROW);
+            const uint4* ur = reinterpret_cast<const uint4*>(st + (size_t)(gu1::RU + slot) * gu1::QROW);
+            const __half2* gs = reinterpret_cast<const __half2*>(st + 2 * gu1::RU * gu1::QROW + (size_t)slot * gu1::SMROW);
+            const __half2* us = reinterpret_cast<const __half2*>(st + 2 * gu1::RU * gu1::QROW + (size_t)(gu1::RU + slot) * gu1::SMROW);
             const float2 g0 = __half22float2(gs[lane >> 1]), g1 = __half22float2(gs[16 + (lane >> 1)]);
             const float2 u0 = __half22float2(us[lane >> 1]), u1 = __half22float2(us[16 + (lane >> 1)]);
             v[2 * i] = g0.x * x0.delta * dot32_q4_i(gr[lane], x0, 0) + g0.y * X0 + g1.x * x1.delta * dot32_q4_i(gr[32 + lane], x1, 0) + g1.y * X1;
@@ -455,7 +519,7 @@ extern "C" int drb_moe_stack_decode(const drb_moe_layer* layers, int n_layers, f
   if (h != moe::H || i != moe::I || topk != moe::TOPK || e < topk || e > stack::MAX_E || n_layers < 0) return -1;
   const DrbDevice& dev = drb_device(st);
   if (!dev.ready) return -2;
-  if (dev.sms < moe::gu::MIN_GRID) return -1;
+  if (dev.sms < stack::gu1::MIN_GRID) return -1;
   if (n_layers == 0) return 0;
   stack::Workspace* ws = static_cast<stack::Workspace*>(workspace);
   if (dev.sms > stack::MAX_BLOCKS) return -1;

@@ -41,14 +41,23 @@ class Op:
 class MoeDecoder:
     """Batch-1 decode over a stack of MoE layers: x <- x + moe_l(rmsnorm(x)) for each layer."""
 
-    def __init__(self, layers: list[MoeLayer], topk: int = 8, eps: float = 1e-6, st: Stream | None = None) -> None:
+    def __init__(self, layers: list[MoeLayer], topk: int = 8, eps: float = 1e-6, st: Stream | None = None,
+                 chained: bool = False, trace_routing: bool = False) -> None:
+        """chained (not in the reference): the layers run drb_moe_decode_chained, whose down kernel also produces the
+        next layer's routing, so only the first layer launches dr_router_topk. trace_routing copies every layer's
+        idx to `idx_trace` (tests)."""
         self.l = ffi.lib()
         self.st = st or Stream()
         self.layers = layers
         self.topk, self.eps = topk, eps
+        self.chained, self.trace_routing = chained, trace_routing
         h, i, e = layers[0].hidden, layers[0].inter, layers[0].experts
         self.hidden = h
         f32 = 4
+        self.idx_trace = DevBuf(len(layers) * topk * 4) if trace_routing else None
+        if chained:
+            check(self.l.drb_init(), "init")
+            self.chain_ws = DevBuf.zeros(int(self.l.drb_moe_chain_workspace_bytes()), self.st)
         self.x = DevBuf((h) * f32)
         self.rlog = DevBuf((e + 1) * f32)
         self.idx = DevBuf(topk * 4)
@@ -61,7 +70,8 @@ class MoeDecoder:
     def ops(self) -> list[Op]:
         ops: list[Op] = []
         l, st = self.l, self.st.raw
-        for layer in self.layers:
+        for li, layer in enumerate(self.layers):
+            nxt_layer = self.layers[li + 1] if li + 1 < len(self.layers) else None
             gq, gs = layer.gate_up.expert(0)
             dq, ds = layer.down.expert(0)
             sizes = (layer.gate_up.q_bytes_per_expert, layer.gate_up.sm_bytes_per_expert,
@@ -77,7 +87,11 @@ class MoeDecoder:
                     "router_topk",
                 )
 
-            ops.append(Op((layer.router.ptr, (layer.experts + 1) * layer.hidden * 2), router))
+            if not (self.chained and li > 0):  # chained: the previous layer's down kernel has left this layer's routing
+                ops.append(Op((layer.router.ptr, (layer.experts + 1) * layer.hidden * 2), router))
+            if self.trace_routing:
+                ops.append(Op(None, lambda pf, pfb, li=li: check(
+                    l.dr_d2d(self.idx_trace.at(li * self.topk * 4), self.idx.at(0), self.topk * 4, st), "d2d")))
             sgq, sgs = layer.shared_gate_up.rows(0)
             sdq, sds = layer.shared_down.rows(0)
 
@@ -91,7 +105,20 @@ class MoeDecoder:
                     "moe_decode",
                 )
 
-            ops.append(Op(None, decode))
+            def decode_chained(pf, pfb, li=li, layer=layer, nxt=nxt_layer, gq=gq, gs=gs, dq=dq, ds=ds, sgq=sgq, sgs=sgs, sdq=sdq,
+                               sds=sds):
+                launched(
+                    l.drb_moe_decode_chained(
+                        gq, gs, dq, ds, sgq, sgs, sdq, sds, self.x.at(0), self.idx.at(0), self.wts.at(0), self.sgate.at(0),
+                        self.x.at(0), self.act.at(0), self.x.at(0), layer.hidden, layer.inter, self.topk,
+                        layer.post_norm.at(0), self.eps, nxt.router.at(0) if nxt else NULL,
+                        nxt.post_norm.at(0) if nxt else NULL, nxt.experts if nxt else 0, self.rlog.at(0),
+                        self.chain_ws.at(0), 1 if li > 0 else 0, st,
+                    ),
+                    "moe_decode_chained",
+                )
+
+            ops.append(Op(None, decode_chained if self.chained else decode))
         return ops
 
     def record_step(self) -> None:
@@ -119,6 +146,10 @@ class MoeDecoder:
     def step_eager(self) -> np.ndarray:
         self.record_step()
         return self.x.download(np.float32, self.hidden, self.st)
+
+    def routing_trace(self) -> np.ndarray:
+        assert self.idx_trace is not None
+        return self.idx_trace.download(np.int32, len(self.layers) * self.topk, self.st).reshape(len(self.layers), self.topk)
 
     def routing(self) -> tuple[np.ndarray, np.ndarray, float]:
         """The last layer's idx, wts and sgate (for tests)."""

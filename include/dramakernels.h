@@ -155,6 +155,27 @@ int drb_moe_stack_decode(const drb_moe_layer* layers, int n_layers, float* x, vo
 /* offsets[e] = counts[0] + ... + counts[e-1] on the device: replaces the reference's host-side scan between
  * dr_moe_count and dr_moe_permute (src/engine.rs:567-574), so the prefill sequence needs no host round trip. */
 int drb_moe_offsets(const int* counts, int e, int* offsets, dr_stream st);
+/* Chained decode: dr_moe_decode as one link of a chain over consecutive MoE layers, on a caller-owned workspace of
+ * drb_moe_chain_workspace_bytes() bytes (zeroed once by the caller, private to one stream of launches).
+ *   next_router != NULL: the down kernel also computes the NEXT layer's routing. Every block adds its share of
+ *     next_router . (y * next_nw) and of sum(y^2) to fixed-point accumulators in the workspace (integer atomics: the
+ *     totals do not depend on the order of arrival); the last block to arrive applies rsqrt(mean(y^2) + eps), runs
+ *     softmax + top-k and OVERWRITES idx / wts / sgate (and logits [e_next + 1], if not NULL) with the next layer's
+ *     routing: what dr_router_topk(next_router, y, next_nw, eps, ...) would write. The router rows are fetched while
+ *     the kernel waits for its activations, so the next layer needs no router launch.
+ *   next_router == NULL ends the chain: idx / wts / sgate are left as they are.
+ *   have_prev != 0: this layer's routing was produced by the previous chained call on the same workspace and x is that
+ *     call's y; both are then read from replicas in the workspace (one per group of blocks, so that 148 blocks do not
+ *     read the same cache lines at once). idx / wts / sgate / x are still passed and hold the same values.
+ * topk == 8, 8 <= e_next <= 256, h == 2048; other limits and return codes as dr_moe_decode. In the reference's engine
+ * the call replaces dr_moe_decode(layer l) and dr_router_topk(layer l + 1) (src/engine.rs:959-1042). */
+int drb_moe_decode_chained(const uint8_t* gu_q, const dr_half* gu_sm, const uint8_t* d_q, const dr_half* d_sm,
+                           const int8_t* sgu_q, const dr_half* sgu_s, const int8_t* sd_q, const dr_half* sd_s,
+                           const float* x, int* idx, float* wts, float* sgate, const float* res, float* act, float* y,
+                           int h, int i, int topk, const float* nw, float eps, const dr_bf16* next_router,
+                           const float* next_nw, int e_next, float* logits, float* workspace, int have_prev,
+                           dr_stream st);
+size_t drb_moe_chain_workspace_bytes(void);
 int dr_stream_destroy(dr_stream s);
 int dr_cublas_destroy(void* h);
 int drb_init(void);                    /* per-device setup; also run by the pre-capture hooks above */

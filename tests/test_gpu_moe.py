@@ -157,6 +157,35 @@ def test_moe_decode_stack_of_layers(st, layers):
     assert device_error_word() == 0
 
 
+def test_moe_decode_chained_routing(st, layers):
+    """drb_moe_decode_chained: the down kernel of layer l also produces the routing of layer l + 1. Four layers (256 experts) and three layers of 16 experts: every layer's routing bit-exact against the
+    fp64 oracle, the hidden state within the layer bar, eager == graph replay, and within fp32 noise of the plain
+    dr_router_topk + dr_moe_decode sequence."""
+    for experts, seeds in ((256, (0, 1, 0, 1)), (16, (3, 4, 3))):
+        pairs = [layers(s, experts) for s in seeds]
+        x = synth.make_x(21, 1, 2048)[0]
+        ref = x.astype(np.float64)[None]
+        ref_idx = []
+        for host, _ in pairs:
+            ref, ridx, _, _, _ = orc.moe_layer(host, ref, 8, 1e-6, np.float64)
+            ref_idx.append(ridx[0])
+        dec = MoeDecoder([d for _, d in pairs], st=st, chained=True, trace_routing=True)
+        dec.set_x(x)
+        y = dec.step_eager()
+        assert device_error_word() == 0
+        assert np.array_equal(dec.routing_trace(), np.stack(ref_idx)), f"routing, {experts} experts"
+        scale = np.abs(ref).max()
+        assert_parity(y, ref[0], f"chained stack, {experts} experts", max_abs=max(1e-2, 4e-6 * scale))
+        plain = MoeDecoder([d for _, d in pairs], st=st)
+        plain.set_x(x)
+        assert np.abs(y - plain.step_eager()).max() <= 4e-6 * scale
+        dec.capture()
+        for _ in range(3):
+            dec.set_x(x)
+            assert np.array_equal(dec.step(), y), "graph replay of the chained sequence differs from the eager launches"
+        assert device_error_word() == 0
+
+
 def test_moe_stack_persistent_kernel(st, layers, golden_dir):
     """drb_moe_stack_decode: four layers in one persistent kernel, eager and from a graph, against the fp64
     oracle (routing of every layer bit-exact) and against the per-layer entry points."""
