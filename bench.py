@@ -547,8 +547,8 @@ def run_gpu(args) -> None:
                      "peak_source": f"{peak_kind} copy bandwidth", "kernel": "decode step graph (router, gate_up, down per layer)",
                      "algorithmic_bytes_per_launch": step_bytes,
                      # dram__bytes_read+write per step from the ncu capture summarised in profiles/decode_kernels_ncu_full.md
-                     # (19.61 MB per layer, measured on a 4-layer case; traffic is proportional to the layer count)
-                     "traffic": 19.607e6 * args.layers},
+                     # (19.62 MB per layer, measured on a 4-layer case; traffic is proportional to the layer count)
+                     "traffic": 19.623e6 * args.layers},
         "e2e": {"value": e2e_us, "unit": "us/layer", "h2d_bytes_per_step": hidden_bytes, "d2h_bytes_per_step": hidden_bytes},
         "gpu_launches": args.steps * args.layers * 3,
         "clocks": clocks.summary(),

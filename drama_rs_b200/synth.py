@@ -119,6 +119,43 @@ def make_layer(seed: int, shape: MoeShape = MoeShape(), norm_jitter: float = 0.1
     return out
 
 
+def e4m3_values() -> np.ndarray:
+    """The 256 values of FP8 E4M3 (finite-only) as float32; 0x7f and 0xff (NaN) are given as +-inf so that a
+    nearest-value search never picks them."""
+    b = np.arange(256, dtype=np.int64)
+    e, m = (b >> 3) & 15, b & 7
+    mag = np.where(e == 0, m / 8.0 * 2.0 ** -6, (1.0 + m / 8.0) * 2.0 ** (e - 7.0))
+    v = np.where(b & 128, -mag, mag).astype(np.float32)
+    v[0x7F], v[0xFF] = np.inf, -np.inf
+    return v
+
+
+def to_e4m3(a: np.ndarray) -> np.ndarray:
+    """Nearest E4M3 code of every element (|a| <= 448), as uint8."""
+    pos = e4m3_values()[:0x7F]  # 0 .. 448 ascending
+    mid = (pos[1:] + pos[:-1]) * np.float32(0.5)
+    code = np.searchsorted(mid, np.abs(a).astype(np.float32), side="left").astype(np.uint8)
+    return np.where(a < 0, code | np.uint8(0x80), code).astype(np.uint8)
+
+
+def make_fp8_experts(seed: int, shape: MoeShape = MoeShape()) -> dict[str, np.ndarray]:
+    """Routed experts in the checkpoint's block-FP8 form (src/model.rs:99-106): E4M3 codes with one f32
+    `scale_inv` per 128 x 128 block; gate rows then up rows. Values are N(0, 1) * 112 rounded to E4M3 (a block's
+    largest magnitude lands near the format's 448, as a block-scaled quantiser leaves it), scales ~ |N(0, 0.01)| / 112,
+    so that the effective weights have the spread of the int4 configuration."""
+    rng = np.random.Generator(np.random.PCG64(seed ^ 0xF8))
+    h, i, e = shape.hidden, shape.inter, shape.experts
+    out: dict[str, np.ndarray] = {}
+    for name, n, k in (("moe.gate_up", 2 * i, h), ("moe.down", h, i)):
+        w = np.empty((e, n, k), dtype=np.uint8)
+        for ex in range(e):  # expert by expert: the float32 draws of all experts at once would need gigabytes
+            w[ex] = to_e4m3(np.clip(rng.standard_normal((n, k), dtype=np.float32) * np.float32(112.0), -448.0, 448.0))
+        out[name + ".fp8"] = w
+        sc = np.abs(rng.standard_normal((e, n // 128, k // 128), dtype=np.float32)) * np.float32(0.01 / 112.0)
+        out[name + ".fp8_s"] = np.maximum(sc, np.float32(1e-7)).astype(np.float32)
+    return out
+
+
 def make_x(seed: int, rows: int, hidden: int = 2048) -> np.ndarray:
     """Activations ~ N(0,1), rounded to bf16 and widened back to f32 (what crosses the decode ABI)."""
     rng = np.random.Generator(np.random.PCG64(seed ^ 0x5EED))

@@ -66,6 +66,29 @@ def dequant_q4(packed: np.ndarray, sm: np.ndarray, dtype=np.float32) -> np.ndarr
 # ----------------------------------------------------------------------------- elementwise
 
 
+def e4m3_table() -> np.ndarray:
+    """The 256 values of the FP8 E4M3 (finite-only, "fn") encoding as float32: sign, 4 exponent bits (bias 7),
+    3 mantissa bits; exponent 0 is subnormal (m / 8 * 2^-6); 0x7f and 0xff are NaN.
+    What `__nv_cvt_fp8x2_to_halfraw2(.., __NV_E4M3)` returns per byte in kernels/drama.cu:606-618 (`fp8x16`)."""
+    b = np.arange(256, dtype=np.int64)
+    e, m = (b >> 3) & 15, b & 7
+    mag = np.where(e == 0, m / 8.0 * 2.0 ** -6, (1.0 + m / 8.0) * 2.0 ** (e - 7.0))
+    v = np.where(b & 128, -mag, mag)
+    v[[0x7F, 0xFF]] = np.nan
+    return v.astype(np.float32)
+
+
+_E4M3 = e4m3_table()
+
+
+def dequant_fp8(w: np.ndarray, s: np.ndarray, dtype=np.float32) -> np.ndarray:
+    """Block-FP8 weights: w u8 [..., N, K] E4M3 codes, s f32 [..., N/128, K/128] (the checkpoint's scale_inv);
+    value = e4m3(w) * s[n / 128, k / 128]. kernels/drama.cu:602-604 (layout), 620-645 (`dot_fp8`); src/model.rs:99-106."""
+    v = _E4M3[w].astype(dtype)
+    sc = np.repeat(np.repeat(s.astype(dtype), 128, axis=-2), 128, axis=-1)
+    return v * sc
+
+
 def rmsnorm(x: np.ndarray, w: np.ndarray | None, eps: float, dtype=np.float32) -> np.ndarray:
     """x * rsqrt(mean(x^2) + eps) * w, the weight's "+1" already folded in.
 
@@ -159,13 +182,20 @@ def expert_forward(layer: dict, e: int, xh: np.ndarray, dtype=np.float32, act_ro
     tools/reference.py:343-347; kernels/drama.cu:475-518 + 521-585 (decode),
     806-959 (prefill, which rounds the intermediate to bf16: pass act_round=round_bf16).
     """
-    gu = dequant_q4(layer["moe.gate_up.q4"][e], layer["moe.gate_up.sm"][e], dtype)
+    fp8 = "moe.gate_up.fp8" in layer  # block-FP8 experts: kernels/drama.cu:647-742 (decode), 971-1109 (prefill)
+    if fp8:
+        gu = dequant_fp8(layer["moe.gate_up.fp8"][e], layer["moe.gate_up.fp8_s"][e], dtype)
+    else:
+        gu = dequant_q4(layer["moe.gate_up.q4"][e], layer["moe.gate_up.sm"][e], dtype)
     inter = gu.shape[0] // 2
     h = xh.astype(dtype) @ gu.T
     act = silu(h[:, :inter]) * h[:, inter:]
     if act_round is not None:
         act = act_round(act.astype(np.float32)).astype(dtype)
-    dn = dequant_q4(layer["moe.down.q4"][e], layer["moe.down.sm"][e], dtype)
+    if fp8:
+        dn = dequant_fp8(layer["moe.down.fp8"][e], layer["moe.down.fp8_s"][e], dtype)
+    else:
+        dn = dequant_q4(layer["moe.down.q4"][e], layer["moe.down.sm"][e], dtype)
     return act @ dn.T
 
 
