@@ -284,6 +284,44 @@ def prefill_extra(torch, layers, st, ext_stream) -> dict:
     }
 
 
+def fp8_extra(torch, layers, st, ext_stream) -> dict:
+    """Batch-1 decode with block-FP8 routed experts (dr_moe_decode_fp8): eight layers in one graph, the router, norm
+    and shared expert of the int4 layers, E4M3 codes and block scales generated on the device (uniform codes below
+    2^5, scales ~1e-4). 8 x 28 MB of selected rows per step: more than L2, so the rows stream from HBM."""
+    from drama_rs_b200.engine import MoeDecoder
+    from drama_rs_b200.gpu import ExtBuf
+    from drama_rs_b200.model import Fp8Experts
+
+    n_layers = min(8, len(layers))
+    h, i, e = SHAPE.hidden, SHAPE.inter, SHAPE.experts
+    g = torch.Generator(device="cuda")
+    g.manual_seed(88)
+    f8s, keep = [], []
+    for _ in range(n_layers):
+        t = []
+        for n, k in ((2 * i, h), (h, i)):
+            code = torch.randint(0, 0x60, (e, n, k), dtype=torch.uint8, device="cuda", generator=g)
+            sign = torch.randint(0, 2, (e, n, k), dtype=torch.uint8, device="cuda", generator=g) << 7
+            w = code | sign
+            sc = (torch.rand((e, n // 128, k // 128), device="cuda", generator=g) + 0.5) * 1e-4
+            t += [w, sc.float().contiguous()]
+        keep.append(t)
+        f8s.append(Fp8Experts(ExtBuf(t[0].data_ptr(), t[0].numel()), ExtBuf(t[1].data_ptr(), t[1].numel() * 4),
+                              ExtBuf(t[2].data_ptr(), t[2].numel()), ExtBuf(t[3].data_ptr(), t[3].numel() * 4), e, h, i))
+    torch.cuda.synchronize()
+    dec = MoeDecoder(layers[:n_layers], st=st, fp8=f8s)
+    x0 = synth.make_x(99, 1, h)[0]
+    dec.set_x(x0)
+    dec.capture()
+    us = time_on_stream(torch, st, ext_stream, lambda k: dec.graph.launch(st), 100) / n_layers
+    y = dec.x.download(np.float32, h, st)
+    layer_bytes = SHAPE.router_bytes + SHAPE.topk * (3 * h * i + 4 * ((2 * i // 128) * (h // 128) + (h // 128) * (i // 128))) + SHAPE.shared_bytes
+    gbs = layer_bytes / us / 1e3
+    del keep
+    return {"workload": f"decode_stack{n_layers}_b1_fp8_experts", "us_per_layer": us, "algorithmic_bytes_per_layer": layer_bytes,
+            "hbm_gbs": gbs, "frac_of_measured_hbm": gbs / peaks()[0], "finite": bool(np.isfinite(y).all())}
+
+
 def gemv_extra(torch, st, ext_stream) -> list:
     """Benchmark configuration 1: int8 GEMV sweep, batch 1; >= 8 copies of each matrix rotated per launch so
     the reads come from HBM, not L2 (the method of the reference's bench/gemv_bench.cu:49-55)."""
@@ -561,6 +599,7 @@ def run_gpu(args) -> None:
     if not args.no_extras:
         line["prefill"] = prefill_extra(torch, layers, st, ext_stream)
         line["gemv_q8_sweep"] = gemv_extra(torch, st, ext_stream)
+        line["decode_fp8"] = fp8_extra(torch, layers, st, ext_stream)
     if not args.no_cpu:
         line["cpu_baseline"] = cpu_decode_baseline()
     print(json.dumps(line), flush=True)

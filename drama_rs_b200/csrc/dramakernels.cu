@@ -7,6 +7,7 @@
 #include "router.cuh"
 #include "moe_decode.cuh"
 #include "moe_decode_static.cuh"
+#include "moe_decode_fp8.cuh"
 #include "moe_prefill_mma.cuh"
 #include "moe_prefill.cuh"
 #include "stack_decode.cuh"

@@ -321,14 +321,32 @@ extern "C" int dr_moe_prefill(const uint8_t* gu_q, const __half2* gu_sm, const u
   if (!dev.ready) return -2;
   if (dev.prefill_mma) {
     // tensor-core path: two persistent grouped GEMMs (moe_prefill_mma.cuh)
-    drb_launch(pfmma::k_grouped<0>, dim3(2 * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, gu_q, gu_sm,
+    drb_launch(pfmma::k_grouped<0, 0>, dim3(2 * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, gu_q, (const void*)gu_sm,
                (const void*)xp, (void*)act, offsets, counts, E);
-    drb_launch(pfmma::k_grouped<1>, dim3(2 * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, d_q, d_sm,
+    drb_launch(pfmma::k_grouped<1, 0>, dim3(2 * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, d_q, (const void*)d_sm,
                (const void*)act, (void*)y, offsets, counts, E);
     return 0;
   }
   pf::k_pf_gate_up<<<dim3(E, I / 16), 256, 0, st>>>(gu_q, gu_sm, xp, offsets, counts, reinterpret_cast<__half*>(act));
   pf::k_pf_down<<<dim3(E, H / 32), 256, 0, st>>>(d_q, d_sm, reinterpret_cast<const __half*>(act), offsets, counts, y);
+  return 0;
+}
+
+// The same grouped GEMMs over block-FP8 experts (layouts as dr_moe_decode_fp8). Tensor-core path only: there is no
+// CUDA-core variant of it, so DRB_PREFILL=simt makes this call return -1.
+// Reference: kernels/drama.cu:971-1109; src/ffi.rs:52-55. H = 2048 and I = 512 only, else -1.
+extern "C" int dr_moe_prefill_fp8(const uint8_t* gu_w, const float* gu_s, const uint8_t* d_w, const float* d_s,
+                                  const __nv_bfloat16* xp, const int* offsets, const int* counts, __nv_bfloat16* act, float* y,
+                                  int E, int H, int I, cudaStream_t st) {
+  if (H != pf::H || I != pf::I) return -1;
+  if (E <= 0) return 0;
+  const DrbDevice& dev = drb_device(st);
+  if (!dev.ready) return -2;
+  if (!dev.prefill_mma) return -1;
+  drb_launch(pfmma::k_grouped<0, 1>, dim3(2 * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, gu_w, (const void*)gu_s,
+             (const void*)xp, (void*)act, offsets, counts, E);
+  drb_launch(pfmma::k_grouped<1, 1>, dim3(2 * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, d_w, (const void*)d_s,
+             (const void*)act, (void*)y, offsets, counts, E);
   return 0;
 }
 

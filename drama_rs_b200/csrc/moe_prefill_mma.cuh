@@ -124,6 +124,42 @@ DRB_DEV uint4 dequant8(uint32_t w, __half2 s2, __half2 m2) {
   return o;
 }
 
+// Sixteen E4M3 weights (k ascending) times one block scale -> sixteen fp16 in k order. s2 holds the scale, already
+// multiplied by the row block's power of two (see k_grouped), in both halves; the product rounds once.
+DRB_DEV void dequant16_fp8(const uint4& v, __half2 s2, uint4& lo, uint4& hi) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t a, b;
+    asm("{.reg .b16 t; cvt.u16.u32 t, %1; cvt.rn.f16x2.e4m3x2 %0, t;}" : "=r"(a) : "r"(w[i] & 0xffffu));
+    asm("{.reg .b16 t; cvt.u16.u32 t, %1; cvt.rn.f16x2.e4m3x2 %0, t;}" : "=r"(b) : "r"(w[i] >> 16));
+    const __half2 pa = __hmul2(*reinterpret_cast<const __half2*>(&a), s2), pb = __hmul2(*reinterpret_cast<const __half2*>(&b), s2);
+    o[2 * i] = *reinterpret_cast<const uint32_t*>(&pa), o[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&pb);
+  }
+  lo = make_uint4(o[0], o[1], o[2], o[3]);
+  hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+// 2^-floor(log2(s)) for a positive finite s: s times it lies in [1, 2).
+DRB_DEV float pow2_normaliser(float s) {
+  const int e = (int)((__float_as_uint(s) >> 23) & 0xffu);  // biased exponent (0 for zero / subnormal: treated as 2^-126)
+  return __uint_as_float((uint32_t)(254 - (e ? e : 1)) << 23);
+}
+
+// Eight bf16 activations (k ascending) -> fp16 in k order.
+DRB_DEV uint4 bf16x8_to_f16_nat(const uint4& v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint4 o;
+  uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 h = __floats2half2_rn(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+    op[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return o;
+}
+
 // Eight bf16 activations (k ascending) -> fp16 in the same (0,4,1,5,2,6,3,7) order.
 DRB_DEV uint4 bf16x8_to_f16_perm(const uint4& v) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};  // (0,1) (2,3) (4,5) (6,7)
@@ -152,15 +188,20 @@ DRB_DEV uint4 f16x8_perm(const uint4& v) {
 
 
 // GEMM = 0: gate/up (+ SwiGLU, fp16 out);  GEMM = 1: down (fp32 out).
-//   Q  [E, R, K/2] nibbles, SM [E, R, K/64] (scale, min);  R = 2I, K = H for gate/up;  R = H, K = I for down.
+// FMT = 0: int4 experts: Q [E, R, K/2] nibbles, SM [E, R, K/64] (scale, min);  R = 2I, K = H for gate/up;  R = H, K = I for down.
+// FMT = 1: block-FP8 experts: Q [E, R, K] E4M3 bytes, SM = f32 scales [E, R/128, K/128]. A row block's scales are
+//   brought into fp16 range by the power of two that normalises the block's first scale (the weights times the
+//   scaled scale round once to fp16); the epilogue multiplies the row's result by the inverse power, exactly.
 //   src: gate/up: xp bf16 [slots, H];  down: act fp16 [slots, I]
 //   dst: gate/up: act fp16 [slots, I]; down: y f32 [slots, H]
 // Warps 0-7 convert operands into the stage ring and run the epilogue; warp 8 issues the MMAs. They meet only
 // on mbarriers: full[s] (8 warp arrivals), empty[s] and done (tcgen05.commit), tfree (accumulator drained).
-template <int GEMM>
+template <int GEMM, int FMT = 0>
 __global__ void __launch_bounds__(THREADS, 2)
-    k_grouped(const uint8_t* __restrict__ Q, const __half2* __restrict__ SM, const void* __restrict__ src, void* __restrict__ dst,
+    k_grouped(const uint8_t* __restrict__ Q, const void* __restrict__ SMv, const void* __restrict__ src, void* __restrict__ dst,
               const int* __restrict__ offsets, const int* __restrict__ counts, int E) {
+  const __half2* SM = static_cast<const __half2*>(SMv);  // FMT 0
+  const float* SF = static_cast<const float*>(SMv);      // FMT 1
   constexpr int K = GEMM == 0 ? H : I;
   constexpr int R = GEMM == 0 ? 2 * I : H;
   constexpr int MT = R / TILE_M;  // tiles per expert: 8 / 16
@@ -243,8 +284,11 @@ __global__ void __launch_bounds__(THREADS, 2)
       const int off = offsets[e];
       // weight row of tile row r: gate/up interleaves gate j (even r) with up j (odd r)
       const int wrow = GEMM == 0 ? (arow & 1) * I + mt * (TILE_M / 2) + (arow >> 1) : mt * TILE_M + arow;
-      const uint8_t* qrow = Q + ((size_t)e * R + wrow) * (K / 2) + ahalf * 16;
+      constexpr int CB = FMT == 0 ? KC / 2 : KC;  // bytes of one K chunk of a weight row; this thread takes half of them
+      const uint8_t* qrow = Q + ((size_t)e * R + wrow) * (FMT == 0 ? K / 2 : K) + ahalf * (CB / 2);
       const __half2* smrow = SM + ((size_t)e * R + wrow) * (K / 64);
+      const float* sfrow = SF + ((size_t)e * (R / 128) + (wrow >> 7)) * (K / 128);  // FMT 1: this row block's scales
+      const float norm = FMT == 1 ? pow2_normaliser(__ldg(sfrow)) : 1.f;
 
       // token group g; the last enumerated group also takes whatever lies beyond NG * MAX_N tokens
       for (int n0 = g * MAX_N; n0 < cnt; n0 += MAX_N) {
@@ -265,21 +309,27 @@ __global__ void __launch_bounds__(THREADS, 2)
         };
         // weights two chunks ahead, activations one chunk ahead, all in registers
         uint4 q0 = __ldg(reinterpret_cast<const uint4*>(qrow));
-        __half2 sm0 = __ldg(smrow);
-        uint4 q1 = NKC > 1 ? __ldg(reinterpret_cast<const uint4*>(qrow + KC / 2)) : q0;
-        __half2 sm1 = NKC > 1 ? __ldg(smrow + 1) : sm0;
+        __half2 sm0 = FMT == 0 ? __ldg(smrow) : __half2();
+        uint4 q1 = NKC > 1 ? __ldg(reinterpret_cast<const uint4*>(qrow + CB)) : q0;
+        __half2 sm1 = FMT == 0 ? (NKC > 1 ? __ldg(smrow + 1) : sm0) : __half2();
+        uint4 p0 = q0, p1 = q1;  // FMT 1: the second 16 bytes of the thread's half chunk
+        if (FMT == 1) {
+          p0 = __ldg(reinterpret_cast<const uint4*>(qrow + 16));
+          p1 = NKC > 1 ? __ldg(reinterpret_cast<const uint4*>(qrow + CB + 16)) : p0;
+        }
         uint4 bn[BPT];
 #pragma unroll
         for (int i = 0; i < BPT; ++i) bn[i] = load_b(0, i);
         for (int kc = 0; kc < NKC; ++kc, ++chunk_no) {
           const int s = chunk_no % STAGES;
           unsigned char* st = stages + (size_t)s * STAGE_BYTES;
-          const uint4 qv = q0;
+          const uint4 qv = q0, pv = p0;
           const __half2 smv = sm0;
-          q0 = q1, sm0 = sm1;
+          q0 = q1, sm0 = sm1, p0 = p1;
           if (kc + 2 < NKC) {
-            q1 = __ldg(reinterpret_cast<const uint4*>(qrow + (kc + 2) * (KC / 2)));
-            sm1 = __ldg(smrow + kc + 2);
+            q1 = __ldg(reinterpret_cast<const uint4*>(qrow + (kc + 2) * CB));
+            if (FMT == 0) sm1 = __ldg(smrow + kc + 2);
+            else p1 = __ldg(reinterpret_cast<const uint4*>(qrow + (kc + 2) * CB + 16));
           }
           uint4 bv[BPT];
 #pragma unroll
@@ -290,15 +340,27 @@ __global__ void __launch_bounds__(THREADS, 2)
           }
           // the MMAs that read this stage STAGES chunks ago must have completed
           if (chunk_no >= STAGES && !dead) dead = !mbar_wait(&ctl.empty[s], ((chunk_no / STAGES) - 1) & 1, DRB_ERR_TMEM);
-          {
+          if (FMT == 0) {
             const __half2 s2 = __half2half2(__low2half(smv)), m2 = __half2half2(__high2half(smv));
             const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(st + a_off[j]) = dequant8(w[j], s2, m2);
+          } else {
+            const __half2 s2 = __float2half2_rn(__ldg(sfrow + (kc >> 1)) * norm);  // one scale per 128 inputs = two chunks
+            uint4 o0, o1, o2, o3;
+            dequant16_fp8(qv, s2, o0, o1);
+            dequant16_fp8(pv, s2, o2, o3);
+            *reinterpret_cast<uint4*>(st + a_off[0]) = o0, *reinterpret_cast<uint4*>(st + a_off[1]) = o1;
+            *reinterpret_cast<uint4*>(st + a_off[2]) = o2, *reinterpret_cast<uint4*>(st + a_off[3]) = o3;
           }
 #pragma unroll
           for (int i = 0; i < BPT; ++i)
-            if (bsrc[i]) *reinterpret_cast<uint4*>(st + b_off[i]) = GEMM == 0 ? bf16x8_to_f16_perm(bv[i]) : f16x8_perm(bv[i]);
+            if (bsrc[i]) {
+              uint4 o;
+              if (FMT == 0) o = GEMM == 0 ? bf16x8_to_f16_perm(bv[i]) : f16x8_perm(bv[i]);
+              else o = GEMM == 0 ? bf16x8_to_f16_nat(bv[i]) : bv[i];  // E4M3 pairs unpack in k order
+              *reinterpret_cast<uint4*>(st + b_off[i]) = o;
+            }
           fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
           __syncwarp();
           if (lane == 0) mbar_arrive(&ctl.full[s]);
@@ -307,9 +369,19 @@ __global__ void __launch_bounds__(THREADS, 2)
         if (!dead) dead = !mbar_wait(&ctl.done, acc_no & 1, DRB_ERR_TMEM);
         ++acc_no;
         tc_fence_after();
+        // FMT 1: undo the power of two that normalised the scales of this tile row's 128-row block
+        float unnorm = 1.f;
+        if (FMT == 1) {
+          const int erow = GEMM == 0 ? (r & 1) * I + mt * (TILE_M / 2) + (r >> 1) : mt * TILE_M + r;
+          unnorm = 1.f / pow2_normaliser(__ldg(SF + ((size_t)e * (R / 128) + (erow >> 7)) * (K / 128)));
+        }
         for (int c0 = (warp >> 2) * 16; c0 < N; c0 += 32) {  // warps 0-3 and 4-7 alternate 16-column groups
           uint32_t v[16];
           tmem_ld16(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0, v);
+          if (FMT == 1) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * unnorm);
+          }
           if (GEMM == 0) {
             __half* act = static_cast<__half*>(dst);
             const int j = mt * (TILE_M / 2) + (r >> 1);
@@ -339,10 +411,14 @@ __global__ void __launch_bounds__(THREADS, 2)
 
 static cudaError_t configure_all() {
   cudaError_t e;
-  if ((e = cudaFuncSetAttribute(k_grouped<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES)) != cudaSuccess) return e;
-  if ((e = cudaFuncSetAttribute(k_grouped<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES)) != cudaSuccess) return e;
-  if ((e = drb_carveout(k_grouped<0>)) != cudaSuccess) return e;
-  return drb_carveout(k_grouped<1>);
+  if ((e = cudaFuncSetAttribute(k_grouped<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(k_grouped<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(k_grouped<0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(k_grouped<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_grouped<0, 0>)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_grouped<0, 1>)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_grouped<1, 1>)) != cudaSuccess) return e;
+  return drb_carveout(k_grouped<1, 0>);
 }
 
 }  // namespace pfmma

@@ -25,7 +25,7 @@ static cudaError_t drb_carveout(K kernel) {
 namespace gemv { static cudaError_t configure_all(); }
 namespace router { static cudaError_t configure_all(); }
 namespace pf { static cudaError_t configure_all(); }
-namespace moe { static cudaError_t configure_all(); }
+namespace moe { static cudaError_t configure_all(); namespace f8 { static cudaError_t configure_all(); } }
 namespace stack { static cudaError_t configure_all(); }
 namespace pfmma { static cudaError_t configure_all(); }
 
@@ -60,6 +60,7 @@ static cudaError_t setup(int d) {
   if ((e = router::configure_all()) != cudaSuccess) return e;
   if ((e = pf::configure_all()) != cudaSuccess) return e;
   if ((e = moe::configure_all()) != cudaSuccess) return e;
+  if ((e = moe::f8::configure_all()) != cudaSuccess) return e;
   if ((e = stack::configure_all()) != cudaSuccess) return e;
   if ((e = pfmma::configure_all()) != cudaSuccess) return e;
   if ((e = cudaMalloc(&dv.grid_sync, GRID_SYNC_WORDS * sizeof(unsigned))) != cudaSuccess) return e;

@@ -42,7 +42,7 @@ class MoeDecoder:
     """Batch-1 decode over a stack of MoE layers: x <- x + moe_l(rmsnorm(x)) for each layer."""
 
     def __init__(self, layers: list[MoeLayer], topk: int = 8, eps: float = 1e-6, st: Stream | None = None,
-                 chained: bool = False, trace_routing: bool = False) -> None:
+                 chained: bool = False, trace_routing: bool = False, fp8: list | None = None) -> None:
         """chained (not in the reference): the layers run drb_moe_decode_chained, whose down kernel also produces the
         next layer's routing, so only the first layer launches dr_router_topk. trace_routing copies every layer's
         idx to `idx_trace` (tests)."""
@@ -51,6 +51,9 @@ class MoeDecoder:
         self.layers = layers
         self.topk, self.eps = topk, eps
         self.chained, self.trace_routing = chained, trace_routing
+        # fp8[l] (model.Fp8Experts) replaces layer l's int4 routed experts: src/engine.rs:949, 996-1003 (`Experts::Fp8`)
+        self.fp8 = fp8
+        assert not (chained and fp8), "the chained sequence exists for the int4 experts only"
         h, i, e = layers[0].hidden, layers[0].inter, layers[0].experts
         self.hidden = h
         f32 = 4
@@ -118,7 +121,18 @@ class MoeDecoder:
                     "moe_decode_chained",
                 )
 
-            ops.append(Op(None, decode_chained if self.chained else decode))
+            def decode_fp8(pf, pfb, li=li, layer=layer, sgq=sgq, sgs=sgs, sdq=sdq, sds=sds):
+                f8 = self.fp8[li]
+                launched(
+                    l.dr_moe_decode_fp8(
+                        f8.gu_w.at(0), f8.gu_s.at(0), f8.d_w.at(0), f8.d_s.at(0), sgq, sgs, sdq, sds, self.x.at(0), self.idx.at(0),
+                        self.wts.at(0), self.sgate.at(0), self.x.at(0), self.act.at(0), self.x.at(0), layer.hidden, layer.inter,
+                        self.topk, layer.post_norm.at(0), self.eps, pf, pfb, st,
+                    ),
+                    "moe_decode_fp8",
+                )
+
+            ops.append(Op(None, decode_fp8 if self.fp8 else decode_chained if self.chained else decode))
         return ops
 
     def record_step(self) -> None:

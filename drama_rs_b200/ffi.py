@@ -47,10 +47,12 @@ SIGNATURES: dict[str, tuple] = {
     "dr_router_topk": (I32, [P, P, P, F32, P, I32, I32, I32, P, P, P, P, P, P, P, P, SZ, SZ, SZ, SZ, P]),
     "dr_moe_topk": (I32, [P, I32, I32, I32, I32, P, P, P, P]),
     "dr_moe_decode": (I32, [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I32, I32, I32, P, F32, P, SZ, P]),
+    "dr_moe_decode_fp8": (I32, [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I32, I32, I32, P, F32, P, SZ, P]),
     "dr_moe_decode_static": (I32, [P, P, P, P, P, P, P, P, P, P, P, P, P, P, I32, I32, I32, P, F32, P, SZ, P]),
     "dr_moe_count": (I32, [P, I32, P, P]),
     "dr_moe_permute": (I32, [P, I32, I32, P, P, P, P, P, I32, P]),
     "dr_moe_prefill": (I32, [P, P, P, P, P, P, P, P, P, I32, I32, I32, P]),
+    "dr_moe_prefill_fp8": (I32, [P, P, P, P, P, P, P, P, P, I32, I32, I32, P]),
     "dr_moe_combine": (I32, [P, P, P, P, P, P, I32, I32, I32, P]),
     "dr_dequant_q8": (I32, [P, P, P, I32, I32, P]),
     "dr_f32_to_bf16": (I32, [P, P, SZ, P]),

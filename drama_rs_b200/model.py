@@ -55,6 +55,31 @@ class Q4:
 
 
 @dataclass
+class Fp8Experts:
+    """Routed experts in the checkpoint's block-FP8 form (src/model.rs:99-106): E4M3 bytes w [E, N, K] with one
+    f32 scale per 128 x 128 block, s [E, N/128, K/128]; gate rows then up rows in gate_up."""
+
+    gu_w: DevBuf
+    gu_s: DevBuf
+    d_w: DevBuf
+    d_s: DevBuf
+    e: int
+    hidden: int
+    inter: int
+
+    @classmethod
+    def upload(cls, t: dict[str, np.ndarray], st: Stream) -> "Fp8Experts":
+        e, n2, h = t["moe.gate_up.fp8"].shape
+        up = lambda name: DevBuf.from_array(t[name], st)
+        return cls(up("moe.gate_up.fp8"), up("moe.gate_up.fp8_s"), up("moe.down.fp8"), up("moe.down.fp8_s"), e, h, n2 // 2)
+
+    @property
+    def bytes_per_expert(self) -> int:
+        h, i = self.hidden, self.inter
+        return 3 * h * i + 4 * ((2 * i // 128) * (h // 128) + (h // 128) * (i // 128))
+
+
+@dataclass
 class MoeLayer:
     router: DevBuf  # bf16 [E + 1, H]
     post_norm: DevBuf  # f32 [H]

@@ -104,6 +104,15 @@ int dr_moe_decode(const uint8_t* gu_q, const dr_half* gu_sm, const uint8_t* d_q,
                   const int* idx, const float* wts, const float* sgate, const float* res, float* act, float* y, int h,
                   int i, int topk, const float* nw, float eps, const char* pf, size_t pf_bytes, dr_stream st);
 
+/* The same layer with block-FP8 routed experts (the checkpoint's own format): gu_w E4M3 [E, 2i, h] (gate rows, then
+ * up rows) with gu_s f32 [E, 2i/128, h/128], d_w E4M3 [E, h, i] with d_s f32 [E, h/128, i/128];
+ * weight = e4m3(byte) * scale of its 128 x 128 block. The shared expert stays int8. Same limits.
+ * drama.cu:602-742; ffi.rs:47-51 */
+int dr_moe_decode_fp8(const uint8_t* gu_w, const float* gu_s, const uint8_t* d_w, const float* d_s,
+                      const int8_t* sgu_q, const dr_half* sgu_s, const int8_t* sd_q, const dr_half* sd_s, const float* x,
+                      const int* idx, const float* wts, const float* sgate, const float* res, float* act, float* y, int h,
+                      int i, int topk, const float* nw, float eps, const char* pf, size_t pf_bytes, dr_stream st);
+
 /* ---- MoE prefill -------------------------------------------------------------------------- */
 
 int dr_moe_count(const int* idx, int n, int* counts, dr_stream st); /* drama.cu:745-753; ffi.rs:65 */
@@ -116,6 +125,9 @@ int dr_moe_permute(const int* idx, int rows, int topk, const int* offsets, int* 
 int dr_moe_prefill(const uint8_t* gu_q, const dr_half* gu_sm, const uint8_t* d_q, const dr_half* d_sm,
                    const dr_bf16* xp, const int* offsets, const int* counts, dr_bf16* act, float* y, int e, int h, int i,
                    dr_stream st);
+/* dr_moe_prefill over block-FP8 experts (layouts as dr_moe_decode_fp8). drama.cu:971-1109; ffi.rs:52-55 */
+int dr_moe_prefill_fp8(const uint8_t* gu_w, const float* gu_s, const uint8_t* d_w, const float* d_s, const dr_bf16* xp,
+                       const int* offsets, const int* counts, dr_bf16* act, float* y, int e, int h, int i, dr_stream st);
 /* drama.cu:780-797; ffi.rs:70-73 */
 int dr_moe_combine(float* x, const float* y, const int* slot_of, const float* wts, const float* sgate,
                    const float* shared, int rows, int topk, int h, dr_stream st);

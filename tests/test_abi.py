@@ -30,7 +30,7 @@ def test_bindings_cover_the_header():
 def test_reference_symbol_names_and_arity():
     # Argument counts of the launchers on the path, as the reference's src/ffi.rs binds them.
     arity = {"dr_gemv_q8": 12, "dr_gemv_q8_swiglu": 11, "dr_gemv_bf16": 10, "dr_router_topk": 21, "dr_moe_topk": 9,
-             "dr_moe_decode": 23, "dr_moe_count": 4, "dr_moe_permute": 10, "dr_moe_prefill": 13, "dr_moe_combine": 10,
+             "dr_moe_decode": 23, "dr_moe_decode_fp8": 23, "dr_moe_count": 4, "dr_moe_permute": 10, "dr_moe_prefill": 13, "dr_moe_prefill_fp8": 13, "dr_moe_combine": 10,
              "dr_dequant_q8": 6, "dr_f32_to_bf16": 4, "dr_swiglu_rows": 5, "dr_rmsnorm": 8, "dr_gemm": 8}
     for name, n in arity.items():
         assert len(ffi.SIGNATURES[name][1]) == n, name

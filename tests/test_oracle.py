@@ -85,3 +85,38 @@ def test_prefill_bookkeeping():
     counts = orc.moe_count(idx, 16)
     off = orc.moe_offsets(counts)
     assert counts.sum() == 40 and off[0] == 0 and np.all(np.diff(off) == counts[:-1])
+
+
+def test_e4m3_table_and_encoder_match_torch():
+    """The oracle's E4M3 decode table and the generator's encoder against torch's float8_e4m3fn (an independent
+    implementation of the format the reference's fp8 kernels convert with __nv_cvt_fp8x2_to_halfraw2)."""
+    import torch
+
+    t = orc.e4m3_table()
+    ref = torch.arange(256, dtype=torch.uint8).view(torch.float8_e4m3fn).float().numpy()
+    assert np.array_equal(np.isnan(t), np.isnan(ref)) and np.array_equal(t[~np.isnan(t)], ref[~np.isnan(ref)])
+    a = (np.random.default_rng(0).standard_normal(50000).astype(np.float32) * 112).clip(-448, 448)
+    mine = synth.to_e4m3(a)
+    th = torch.from_numpy(a).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    differ = mine != th  # only exact ties may round differently
+    assert np.allclose(np.abs(t[mine[differ]] - a[differ]), np.abs(t[th[differ]] - a[differ]))
+
+
+def test_dequant_fp8_blocks():
+    rng = np.random.default_rng(1)
+    w = rng.integers(0, 127, size=(256, 384), dtype=np.uint8)
+    s = rng.random((2, 3), dtype=np.float32) + 0.5
+    d = orc.dequant_fp8(w, s)
+    t = orc.e4m3_table()
+    for (r, c) in ((0, 0), (127, 127), (128, 128), (255, 383), (130, 5)):
+        assert d[r, c] == np.float32(t[w[r, c]] * s[r // 128, c // 128])
+
+
+def test_fp8_layer_oracle_runs_small():
+    shape = synth.MoeShape(experts=16)
+    host = synth.make_layer(5, shape)
+    host.update(synth.make_fp8_experts(5, shape))
+    x = synth.make_x(5, 2, 2048)
+    y32 = orc.moe_layer(host, x, 8, 1e-6, np.float32)[0]
+    y64 = orc.moe_layer(host, x.astype(np.float64), 8, 1e-6, np.float64)[0]
+    assert np.isfinite(y64).all() and np.abs(y32 - y64).max() <= 1e-4 * np.abs(y64).max()
