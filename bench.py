@@ -228,8 +228,10 @@ def prefill_extra(torch, layers, st, ext_stream) -> dict:
     x = synth.make_x(33, rows, SHAPE.hidden)
     bias = synth.zipf_router_bias(33, SHAPE.experts, 1.1)
     pres = [MoePrefill(ly, rows, st=st) for ly in layers[:4]]
+    y0 = None
     for p in pres:
-        p.run(x, logit_bias=bias)
+        y = p.run(x, logit_bias=bias)
+        y0 = y if y0 is None else y0
     counts = pres[0].counts.download(np.int32, SHAPE.experts, st)
     hit = int((counts > 0).sum())
 
@@ -275,6 +277,7 @@ def prefill_extra(torch, layers, st, ext_stream) -> dict:
     hbm_peak = peaks()[0]
     return {
         "workload": "prefill_300rows_zipf1.1_one_layer", "rows": rows, "experts_hit": hit, "max_group": int(counts.max()),
+        "output_sum": float(y0.astype(np.float64).sum()),
         "rows_per_s": rows / us_graph * 1e6, "us_layer_device_graph": us_graph,
         "rows_per_s_reference_call_sequence": rows / us_full * 1e6, "us_layer_reference_call_sequence_host_rows_in": us_full,
         "grouped_gemm_us": us_grouped, "grouped_gemm_rows_per_s": rows / us_grouped * 1e6,

@@ -69,7 +69,7 @@ def worker(rank, world, port, out, fixed=False):
 
 
 @pytest.mark.parametrize("fixed", [False, True], ids=["split-sizes", "fixed-capacity"])
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_ep_block_matches_single_process(tmp_path, world, fixed):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
