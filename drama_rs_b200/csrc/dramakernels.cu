@@ -11,4 +11,5 @@
 #include "moe_prefill_mma.cuh"
 #include "moe_prefill.cuh"
 #include "stack_decode.cuh"
+#include "quant.cuh"
 

@@ -63,6 +63,8 @@ SIGNATURES: dict[str, tuple] = {
     "drb_moe_offsets": (I32, [P, I32, P, P]),
     "drb_moe_decode_chained": (I32, [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I32, I32, I32, P, F32, P, P, I32, P, P, I32, P]),
     "drb_moe_chain_workspace_bytes": (SZ, []),
+    "drb_quant_q4": (I32, [P, SZ, P, P, P]),
+    "drb_quant_q8": (I32, [P, SZ, P, P, P]),
     "drb_init": (I32, []),
     "drb_device_error": (I32, [C.POINTER(U32)]),
     "drb_grid_blocks": (I32, []),

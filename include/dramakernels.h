@@ -188,6 +188,12 @@ int drb_moe_decode_chained(const uint8_t* gu_q, const dr_half* gu_sm, const uint
                            const float* next_nw, int e_next, float* logits, float* workspace, int have_prev,
                            dr_stream st);
 size_t drb_moe_chain_workspace_bytes(void);
+/* The checkpoint quantisers of the reference's converter on the GPU (tools/convert.py:33-41 `quant_q8`, 44-101
+ * `quant_q4_groups` / `quant_q4`: 24-step clipping search with a least-squares refit). w: `groups` x 64 (q4) or
+ * 128 (q8) consecutive floats, i.e. a row-major weight whose last dimension is a multiple of the group; outputs in
+ * the layouts above (q4: 32 bytes per group, low nibble = even k, and f16 (scale, min); q8: codes and f16 scale). */
+int drb_quant_q4(const float* w, size_t groups, uint8_t* q, dr_half* sm, dr_stream st);
+int drb_quant_q8(const float* w, size_t groups, int8_t* q, dr_half* s, dr_stream st);
 int dr_stream_destroy(dr_stream s);
 int dr_cublas_destroy(void* h);
 int drb_init(void);                    /* per-device setup; also run by the pre-capture hooks above */
