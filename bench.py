@@ -413,13 +413,27 @@ def prefill_ep_extra(torch, dist, layer, st, ext_stream, rank: int, world: int) 
         ops.logit_bias = torch.from_numpy(synth.zipf_router_bias(33, SHAPE.experts, 1.1)).cuda()
         x0 = torch.from_numpy(x_all[lo:hi].copy()).cuda()
         x = x0.clone()
+        # this rank's rows through the single-GPU sequence (every rank holds the whole layer): the check for what follows
+        from drama_rs_b200.engine import MoePrefill
+
+        ref = MoePrefill(layer, rows, st=st).run(x_all, logit_bias=synth.zipf_router_bias(33, SHAPE.experts, 1.1))[lo:hi]
+        ep.ep_moe_block_fixed(x, ops, SHAPE.experts, SHAPE.topk, cap)
+        torch.cuda.synchronize()
+        diff_eager = float(np.abs(x.cpu().numpy() - ref).max())
         us, graphed = _ep_time(torch, dist, ext_stream, ops.stream, lambda: ep.ep_moe_block_fixed(x, ops, SHAPE.experts, SHAPE.topk, cap),
                                lambda: x.copy_(x0), 20)
+        diff_graph = float(np.abs(x.cpu().numpy() - ref).max())
+        d = torch.tensor([diff_eager, diff_graph, float(np.abs(ref).max())], dtype=torch.float64, device="cuda")
+        dist.all_reduce(d, op=dist.ReduceOp.MAX)
         # checksum of the result, summed over ranks: identical for every N when the routing and the sums are
         cs = torch.tensor([float(x.double().sum())], dtype=torch.float64, device="cuda")
         dist.all_reduce(cs)
+        # read the reduced values while this stream is current: the default stream does not wait for it
+        torch.cuda.synchronize()
+        cs, d = cs.cpu(), d.cpu()
     return {"workload": "prefill_300rows_zipf1.1_one_layer_expert_parallel", "rows": rows, "experts_per_rank": SHAPE.experts // world,
             "us_layer": us, "rows_per_s": rows / us * 1e6, "output_sum": float(cs[0]), "cuda_graph": graphed,
+            "max_abs_diff_to_single_gpu": {"eager": float(d[0]), "graph_replay": float(d[1]), "output_scale": float(d[2])},
             "exchange": f"NCCL all_to_all_single at fixed capacity ({cap} row slots per peer): bf16 rows out, f32 rows back"}
 
 

@@ -232,6 +232,58 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// Router logits whose value for a row does not depend on how many rows are computed together: every (row, output)
+// pair is one warp's dot product in a fixed order (lane l takes the 16-byte chunks l, l + 32, ... of the K = 2048
+// inputs, products exact in fp32, one fixed butterfly). A library GEMM picks its kernel by the batch size (measured:
+// logits of the same row differ by 1.2e-6 between a batch of 300 and a batch of 38), which would let the routing of
+// a row depend on how the rows are spread over the GPUs. Block = RB rows x all outputs; warp w takes outputs w, w + 8, ...
+constexpr int RL_RB = 4, RL_K = 2048;
+__global__ void __launch_bounds__(256)
+    k_router_logits(const __nv_bfloat16* __restrict__ xb, const __nv_bfloat16* __restrict__ w, float* __restrict__ logits,
+                    int rows, int e1, float beta) {
+  pdl_wait();
+  __shared__ __align__(16) __nv_bfloat16 xs[RL_RB][RL_K];
+  const int r0 = blockIdx.x * RL_RB;
+  const int nr = min(RL_RB, rows - r0);
+  for (int i = threadIdx.x; i < RL_RB * RL_K / 8; i += blockDim.x) {
+    const int r = i / (RL_K / 8), c = i % (RL_K / 8);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < nr) v = __ldcg(reinterpret_cast<const uint4*>(xb + (size_t)(r0 + r) * RL_K) + c);
+    reinterpret_cast<uint4*>(&xs[r][0])[c] = v;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int o = warp; o < e1; o += 8) {
+    const uint4* wr = reinterpret_cast<const uint4*>(w + (size_t)o * RL_K);
+    float acc[RL_RB];
+#pragma unroll
+    for (int r = 0; r < RL_RB; ++r) acc[r] = 0.f;
+#pragma unroll
+    for (int j = 0; j < RL_K / 8 / 32; ++j) {
+      const uint4 wv = __ldg(wr + lane + 32 * j);
+      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+      for (int r = 0; r < RL_RB; ++r) {
+        const uint4 xv = reinterpret_cast<const uint4*>(&xs[r][0])[lane + 32 * j];
+        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          acc[r] = fmaf(__uint_as_float(ww[t] << 16), __uint_as_float(xw[t] << 16), acc[r]);
+          acc[r] = fmaf(__uint_as_float(ww[t] & 0xffff0000u), __uint_as_float(xw[t] & 0xffff0000u), acc[r]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < RL_RB; ++r) {
+      const float v = warp_sum(acc[r]);
+      if (lane == 0 && r < nr) {
+        float* out = logits + (size_t)(r0 + r) * e1 + o;
+        *out = beta != 0.f ? fmaf(beta, *out, v) : v;
+      }
+    }
+  }
+}
+
 // offsets[e] = sum of counts[0..e): the exclusive scan the reference does on the host between two launches
 // (src/engine.rs:567-574). One block, any number of experts.
 __global__ void __launch_bounds__(256) k_offsets(const int* __restrict__ counts, int E, int* __restrict__ offsets) {
@@ -264,6 +316,7 @@ __global__ void __launch_bounds__(256) k_offsets(const int* __restrict__ counts,
 static cudaError_t configure_all() {
   cudaError_t e;
   if ((e = drb_carveout(k_offsets)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_router_logits)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_count)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_permute)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_combine)) != cudaSuccess) return e;
@@ -289,6 +342,17 @@ extern "C" int dr_moe_count(const int* idx, int n, int* counts, cudaStream_t st)
 extern "C" int drb_moe_offsets(const int* counts, int e, int* offsets, cudaStream_t st) {
   if (e <= 0) return 0;
   pf::k_offsets<<<1, 256, 0, st>>>(counts, e, offsets);
+  return 0;
+}
+
+// logits [rows, e1] = xb [rows, h] . w [e1, h]^T + beta * logits, with per-row results that do not depend on `rows`
+// (see k_router_logits). The reference computes these logits with cublasGemmEx (src/engine.rs:554); this call is for
+// hosts that spread rows over several GPUs and need the same routing at every split. h == 2048, else -1.
+extern "C" int drb_router_logits(const __nv_bfloat16* xb, const __nv_bfloat16* w, float* logits, int rows, int e1, int h,
+                                 float beta, cudaStream_t st) {
+  if (h != pf::RL_K) return -1;
+  if (rows <= 0 || e1 <= 0) return 0;
+  pf::k_router_logits<<<(rows + pf::RL_RB - 1) / pf::RL_RB, 256, 0, st>>>(xb, w, logits, rows, e1, beta);
   return 0;
 }
 

@@ -203,6 +203,7 @@ class MoePrefill:
         self.yp = DevBuf(n * topk * h * 4)
         self.wbuf = DevBuf(2 * i * h * 2)
         self.device_scan = False  # True: offsets by drb_moe_offsets on the device instead of the reference's host scan
+        self.invariant_router = False  # True: router logits by drb_router_logits (independent of the batch size) instead of cuBLAS
         self.logit_bias: DevBuf | None = None  # [n, E + 1] f32 rows the router GEMM accumulates onto (not in the reference)
 
     def gemm_q8(self, a, w, c, m: int, beta: float) -> None:
@@ -237,7 +238,10 @@ class MoePrefill:
         if self.logit_bias is not None:
             check(l.dr_d2d(self.rlog.at(0), self.logit_bias.at(0), n * (e + 1) * 4, st), "d2d")
             beta = 1.0
-        check(l.dr_gemm(self.blas, self.hn_b.at(0), layer.router.at(0), self.rlog.at(0), n, e + 1, h, beta), "gemm")
+        if self.invariant_router:
+            launched(l.drb_router_logits(self.hn_b.at(0), layer.router.at(0), self.rlog.at(0), n, e + 1, h, beta, st), "router_logits")
+        else:
+            check(l.dr_gemm(self.blas, self.hn_b.at(0), layer.router.at(0), self.rlog.at(0), n, e + 1, h, beta), "gemm")
         launched(l.dr_moe_topk(self.rlog.at(0), n, e, topk, e + 1, self.idx.at(0), self.wts.at(0), self.sgate.at(0), st), "moe_topk")
         # Shared expert.
         self.gemm_q8(self.hn_b.at(0), layer.shared_gate_up, self.shh.at(0), n, 0.0)

@@ -311,7 +311,8 @@ class EpGpuFixed:
             rlog.zero_()
             rlog[:, :e] = self.logit_bias
             beta = 1.0
-        check(l.dr_gemm(self.blas, self._p(hn_b), ly.router.at(0), self._p(rlog), n, e + 1, h, beta), "gemm")
+        # batch-invariant logits: the routing of a row must not depend on how many rows this rank holds
+        launched(l.drb_router_logits(self._p(hn_b), ly.router.at(0), self._p(rlog), n, e + 1, h, beta, st), "router_logits", debug=False)
         launched(l.dr_moe_topk(self._p(rlog), n, e, topk, e + 1, self._p(idx), self._p(wts), self._p(sgate), st), "moe_topk", debug=False)
         self._gemm_q8(hn_b, ly.shared_gate_up, self.shh, n)
         launched(l.dr_swiglu_rows(self._p(self.shh), self._p(self.sh_act), n, i, st), "swiglu", debug=False)

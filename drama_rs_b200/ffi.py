@@ -61,6 +61,7 @@ SIGNATURES: dict[str, tuple] = {
     "drb_moe_stack_workspace_bytes": (I32, []),
     "drb_moe_stack_decode": (I32, [P, I32, P, P, I32, I32, I32, I32, F32, P, P, P]),
     "drb_moe_offsets": (I32, [P, I32, P, P]),
+    "drb_router_logits": (I32, [P, P, P, I32, I32, I32, F32, P]),
     "drb_moe_decode_chained": (I32, [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I32, I32, I32, P, F32, P, P, I32, P, P, I32, P]),
     "drb_moe_chain_workspace_bytes": (SZ, []),
     "drb_quant_q4": (I32, [P, SZ, P, P, P]),

@@ -167,6 +167,12 @@ int drb_moe_stack_decode(const drb_moe_layer* layers, int n_layers, float* x, vo
 /* offsets[e] = counts[0] + ... + counts[e-1] on the device: replaces the reference's host-side scan between
  * dr_moe_count and dr_moe_permute (src/engine.rs:567-574), so the prefill sequence needs no host round trip. */
 int drb_moe_offsets(const int* counts, int e, int* offsets, dr_stream st);
+/* logits [rows, e1] = xb [rows, h] . w [e1, h]^T + beta * logits (bf16 inputs, fp32 sums in a fixed order), such that a
+ * row's logits do not depend on how many rows are computed together. The reference uses cublasGemmEx for these
+ * logits (src/engine.rs:554), whose kernel choice, and with it the last bits of a row, changes with the batch size;
+ * a host that spreads rows over several GPUs uses this call so that the routing is the same at every split.
+ * h == 2048, else -1. */
+int drb_router_logits(const dr_bf16* xb, const dr_bf16* w, float* logits, int rows, int e1, int h, float beta, dr_stream st);
 /* Chained decode: dr_moe_decode as one link of a chain over consecutive MoE layers, on a caller-owned workspace of
  * drb_moe_chain_workspace_bytes() bytes (zeroed once by the caller, private to one stream of launches).
  *   next_router != NULL: the down kernel also computes the NEXT layer's routing. Every block adds its share of

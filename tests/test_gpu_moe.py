@@ -254,6 +254,32 @@ def test_moe_prefill_grouped_kernel_direct(st, layers):
     assert worst <= 8e-4, worst
 
 
+def test_router_logits_do_not_depend_on_the_batch(st, layers):
+    """drb_router_logits: a row's logits are bit-identical whether it is computed alone, in a batch of 7 or of 300
+    (what lets expert-parallel ranks with different row counts route identically), and agree with cuBLAS."""
+    host, dev = layers(2)
+    x = synth.make_x(8, 300, 2048)
+    runs = {}
+    for name, sl in (("all", slice(0, 300)), ("seven", slice(100, 107)), ("one", slice(103, 104))):
+        pre = MoePrefill(dev, 300, st=st)
+        pre.invariant_router = True
+        pre.run(x[sl])
+        n = sl.stop - sl.start
+        runs[name] = (pre.rlog.download(np.float32, n * 257, st).reshape(n, 257), pre.idx.download(np.int32, n * 8, st).reshape(n, 8))
+    assert np.array_equal(runs["all"][0][100:107].view(np.uint32), runs["seven"][0].view(np.uint32))
+    assert np.array_equal(runs["all"][0][103:104].view(np.uint32), runs["one"][0].view(np.uint32))
+    assert np.array_equal(runs["all"][1][100:107], runs["seven"][1])
+    blas = MoePrefill(dev, 300, st=st)
+    blas.run(x)
+    lb = blas.rlog.download(np.float32, 300 * 257, st).reshape(300, 257)
+    assert np.abs(lb - runs["all"][0]).max() <= 1e-5 * np.abs(lb).max()
+    xh = orc.round_bf16(orc.rmsnorm(x, host["post_norm"], 1e-6))
+    ref = orc.router_logits(host, xh.astype(np.float64), np.float64)
+    # the device's RMSNorm sums in another order, so a few normalised values round to the neighbouring bf16
+    assert np.abs(ref - runs["all"][0]).max() <= 2e-3 * np.abs(ref).max()
+    assert ffi.lib().drb_router_logits(NULL, NULL, NULL, 4, 257, 1024, 0.0, st.raw) == -1
+
+
 def test_moe_prefill_golden_rows40(st, layers, golden_dir):
     g = np.load(os.path.join(golden_dir, "moe_rows40_seed2.npz"))
     host, dev = layers(2)
