@@ -617,7 +617,7 @@ def run_gpu(args) -> None:
         line["prefill"] = prefill_extra(torch, layers, st, ext_stream)
         line["gemv_q8_sweep"] = gemv_extra(torch, st, ext_stream)
         line["decode_fp8"] = fp8_extra(torch, layers, st, ext_stream)
-    if not args.no_cpu:
+    if not args.no_cpu and world == 1:  # the CPU baseline is a single-GPU-run figure (torchrun also pins OMP to one thread)
         line["cpu_baseline"] = cpu_decode_baseline()
     print(json.dumps(line), flush=True)
     if world > 1:

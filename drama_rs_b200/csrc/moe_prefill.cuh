@@ -236,8 +236,9 @@ __global__ void __launch_bounds__(256)
 // pair is one warp's dot product in a fixed order (lane l takes the 16-byte chunks l, l + 32, ... of the K = 2048
 // inputs, products exact in fp32, one fixed butterfly). A library GEMM picks its kernel by the batch size (measured:
 // logits of the same row differ by 1.2e-6 between a batch of 300 and a batch of 38), which would let the routing of
-// a row depend on how the rows are spread over the GPUs. Block = RB rows x all outputs; warp w takes outputs w, w + 8, ...
-constexpr int RL_RB = 4, RL_K = 2048;
+// a row depend on how the rows are spread over the GPUs. Block (x, y) = RB rows x the outputs y, y + gridDim.y, ...;
+// its warp w takes every 8th of those. The split over y only adds parallelism: it does not change any sum.
+constexpr int RL_RB = 4, RL_K = 2048, RL_SPLIT = 9;
 __global__ void __launch_bounds__(256)
     k_router_logits(const __nv_bfloat16* __restrict__ xb, const __nv_bfloat16* __restrict__ w, float* __restrict__ logits,
                     int rows, int e1, float beta) {
@@ -253,14 +254,17 @@ __global__ void __launch_bounds__(256)
   }
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int o = warp; o < e1; o += 8) {
+  for (int o = blockIdx.y + gridDim.y * warp; o < e1; o += gridDim.y * 8) {
     const uint4* wr = reinterpret_cast<const uint4*>(w + (size_t)o * RL_K);
+    uint4 wv8[RL_K / 8 / 32];
+#pragma unroll
+    for (int j = 0; j < RL_K / 8 / 32; ++j) wv8[j] = __ldg(wr + lane + 32 * j);  // all eight in flight at once
     float acc[RL_RB];
 #pragma unroll
     for (int r = 0; r < RL_RB; ++r) acc[r] = 0.f;
 #pragma unroll
     for (int j = 0; j < RL_K / 8 / 32; ++j) {
-      const uint4 wv = __ldg(wr + lane + 32 * j);
+      const uint4 wv = wv8[j];
       const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
       for (int r = 0; r < RL_RB; ++r) {
@@ -352,7 +356,7 @@ extern "C" int drb_router_logits(const __nv_bfloat16* xb, const __nv_bfloat16* w
                                  float beta, cudaStream_t st) {
   if (h != pf::RL_K) return -1;
   if (rows <= 0 || e1 <= 0) return 0;
-  pf::k_router_logits<<<(rows + pf::RL_RB - 1) / pf::RL_RB, 256, 0, st>>>(xb, w, logits, rows, e1, beta);
+  pf::k_router_logits<<<dim3((rows + pf::RL_RB - 1) / pf::RL_RB, pf::RL_SPLIT), 256, 0, st>>>(xb, w, logits, rows, e1, beta);
   return 0;
 }
 
