@@ -136,6 +136,10 @@ def run_reference(args) -> None:
     layers = [synth.make_layer(1000 + i, SHAPE) for i in range(2)]
     structs = [c_oracle.layer_struct(t, SHAPE.topk, SHAPE.eps) for t in layers]
     lib = c_oracle.lib()
+    # torchrun pins OMP_NUM_THREADS to 1 for its workers; this arm is the CPU path with every host thread
+    lib.orc_set_threads.argtypes = [C.c_int]
+    lib.orc_set_threads.restype = None
+    lib.orc_set_threads(len(os.sched_getaffinity(0)))
     x0 = synth.make_x(1000, 1, SHAPE.hidden)[0]
     x = x0.copy()
     sample_layers = 8  # one step of the reference arm = 8 layers of the 40-layer stack (bounded sample)

@@ -220,6 +220,15 @@ int orc_moe_decode_layer(const orc_layer* L, float* x, int* idx_out, float* wts_
   return 0;
 }
 
+/* Overrides the thread count the environment chose (a launcher may pin OMP_NUM_THREADS to 1). */
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int orc_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();
