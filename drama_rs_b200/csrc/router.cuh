@@ -294,7 +294,7 @@ constexpr size_t SMEM_BYTES = CTL_BYTES + K * 4 + W_BYTES;
 
 struct Ctl {
   uint64_t full;
-  float red[16];
+  float red[8];
   float inv_rms;
   float logits[CLUSTER * ROWS];  // block 0's copy is the gathering point
   TopkSmem tk;
@@ -318,9 +318,7 @@ DRB_DEV void st_cluster_f32(uint32_t addr, float v) {
 DRB_DEV void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 DRB_DEV void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
-constexpr int CL_WARPS = 16, CL_THREADS = CL_WARPS * 32;
-static_assert(CL_THREADS == K / 4, "one float4 of x per thread");
-__global__ void __launch_bounds__(CL_THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 1)
     k_router_cluster(const __nv_bfloat16* __restrict__ W, const float* __restrict__ x, const float* __restrict__ nw, float eps,
                      float* __restrict__ logits, int E, int topk, int* __restrict__ idx, float* __restrict__ wts,
                      float* __restrict__ sgate, const char* gu_q, const char* gu_sm, const char* d_q, const char* d_sm,
@@ -347,25 +345,25 @@ __global__ void __launch_bounds__(CL_THREADS, 1)
   pdl_wait();  // x is the previous kernel's output
   DRB_TRACE_POINT(1, 0);
 
-  // 16 warps: thread t owns float4 t of x.
-  const float4 xa = __ldcg(reinterpret_cast<const float4*>(x) + threadIdx.x);
+  const float4 xa = __ldcg(reinterpret_cast<const float4*>(x) + threadIdx.x * 2), xb = __ldcg(reinterpret_cast<const float4*>(x) + threadIdx.x * 2 + 1);
   float inv = 1.f;
-  float4 wa = make_float4(1.f, 1.f, 1.f, 1.f);
+  float4 wa = make_float4(1.f, 1.f, 1.f, 1.f), wb = wa;
   if (nw) {
-    wa = reinterpret_cast<const float4*>(nw)[threadIdx.x];
-    float ss = xa.x * xa.x + xa.y * xa.y + xa.z * xa.z + xa.w * xa.w;
+    wa = reinterpret_cast<const float4*>(nw)[threadIdx.x * 2], wb = reinterpret_cast<const float4*>(nw)[threadIdx.x * 2 + 1];
+    float ss = xa.x * xa.x + xa.y * xa.y + xa.z * xa.z + xa.w * xa.w + xb.x * xb.x + xb.y * xb.y + xb.z * xb.z + xb.w * xb.w;
     ss = warp_sum(ss);
     if (lane == 0) ctl.red[warp] = ss;
     __syncthreads();
     float t = 0.f;
 #pragma unroll
-    for (int w = 0; w < CL_WARPS; ++w) t += ctl.red[w];
+    for (int w = 0; w < 8; ++w) t += ctl.red[w];
     inv = rsqrtf(t / K + eps);
   }
-  xs4[threadIdx.x] = make_float4(xa.x * inv * wa.x, xa.y * inv * wa.y, xa.z * inv * wa.z, xa.w * inv * wa.w);
+  xs4[threadIdx.x * 2] = make_float4(xa.x * inv * wa.x, xa.y * inv * wa.y, xa.z * inv * wa.z, xa.w * inv * wa.w);
+  xs4[threadIdx.x * 2 + 1] = make_float4(xb.x * inv * wb.x, xb.y * inv * wb.y, xb.z * inv * wb.z, xb.w * inv * wb.w);
   __syncthreads();
   DRB_TRACE_POINT(2, 0);
-  // Warp w takes rows w, w + 16, ...; lane l takes the 16-byte chunks l, l + 32, ... (8 weights each) of a row.
+  // Warp w takes rows w, w + 8, ...; lane l takes the 16-byte chunks l, l + 32, ... (8 weights each) of a row.
   unsigned long long xp[32];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -375,12 +373,12 @@ __global__ void __launch_bounds__(CL_THREADS, 1)
   if (nrows > 0) mbar_wait(&ctl.full, 0, DRB_ERR_FULL_WAIT);
   DRB_TRACE_POINT(3, 0);
   const uint32_t gather = map_to_rank(ctl.logits, 0);
-  // Two rows at a time per warp (rows warp, warp + 16): independent accumulators, one folded reduction.
-  for (int rb = warp; rb < nrows; rb += 2 * CL_WARPS) {
-    float d[2];
+  // Four rows at a time per warp (rows warp, warp + 8, ...): independent accumulators, one folded reduction.
+  for (int rb = warp; rb < nrows; rb += 32) {
+    float d[4];
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int r = rb + CL_WARPS * j;
+    for (int j = 0; j < 4; ++j) {
+      const int r = rb + 8 * j;
       d[j] = 0.f;
       if (r < nrows) {
         const uint4* wr = reinterpret_cast<const uint4*>(wsm + (size_t)r * K * 2);
@@ -396,26 +394,26 @@ __global__ void __launch_bounds__(CL_THREADS, 1)
         d[j] = (p0 + p1) + (p2 + p3);
       }
     }
-    const bool hi16 = lane & 16;
-    float sres = (hi16 ? d[1] : d[0]) + __shfl_xor_sync(0xffffffffu, hi16 ? d[0] : d[1], 16);
-    sres += __shfl_xor_sync(0xffffffffu, sres, 8);
+    const bool hi16 = lane & 16, hi8 = lane & 8;
+    const float r0 = (hi16 ? d[2] : d[0]) + __shfl_xor_sync(0xffffffffu, hi16 ? d[0] : d[2], 16);
+    const float r1 = (hi16 ? d[3] : d[1]) + __shfl_xor_sync(0xffffffffu, hi16 ? d[1] : d[3], 16);
+    float sres = (hi8 ? r1 : r0) + __shfl_xor_sync(0xffffffffu, hi8 ? r0 : r1, 8);
     sres += __shfl_xor_sync(0xffffffffu, sres, 4);
     sres += __shfl_xor_sync(0xffffffffu, sres, 2);
     sres += __shfl_xor_sync(0xffffffffu, sres, 1);
-    const int r = rb + CL_WARPS * (lane >> 4);  // lanes 0-15: row j = 0, 16-31: j = 1
-    if ((lane & 15) == 0 && r < nrows) st_cluster_f32(gather + 4u * (unsigned)(row0 + r), sres);
+    const int r = rb + 8 * (lane >> 3);  // lanes 0-7: row j = 0, 8-15: j = 1, 16-23: j = 2, 24-31: j = 3
+    if ((lane & 7) == 0 && r < nrows) st_cluster_f32(gather + 4u * (unsigned)(row0 + r), sres);
   }
   DRB_TRACE_POINT(4, 0);
   cluster_arrive();
   if (rank != 0) return;  // only block 0's shared memory is read from here on
   cluster_wait();
   DRB_TRACE_POINT(5, 0);
-  if (threadIdx.x >= THREADS) return;  // the tail is one probability per thread: the first 256 threads
   const int e = threadIdx.x;
   const float v = e < E ? ctl.logits[e] : -INFINITY;
   if (e < E) logits[e] = v;
   if (e == 0) logits[E] = ctl.logits[E];
-  softmax_topk<1>(v, E, topk, idx, wts, ctl.tk);
+  softmax_topk(v, E, topk, idx, wts, ctl.tk);
   if (threadIdx.x == 0) sgate[0] = ctl.logits[E];
   DRB_TRACE_POINT(6, 0);
   if (gu_q && threadIdx.x < 32) {
@@ -455,7 +453,7 @@ extern "C" int dr_router_topk(const __nv_bfloat16* W, const float* x, const floa
     // One cluster of 8 blocks, launched with the programmatic-dependency attribute as well.
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(router::cl::CLUSTER);
-    cfg.blockDim = dim3(router::cl::CL_THREADS);
+    cfg.blockDim = dim3(router::THREADS);
     cfg.dynamicSmemBytes = router::cl::SMEM_BYTES;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
