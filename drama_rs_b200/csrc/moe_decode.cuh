@@ -56,7 +56,10 @@ constexpr int UNITS = 32;                                 // units (gate row + u
 constexpr int ROUTED_BLOCKS = TOPK * I / UNITS;           // 128
 constexpr int SHARED_BLOCKS = I / UNITS;                  // 16
 constexpr int GRID = ROUTED_BLOCKS + SHARED_BLOCKS;       // 144
-constexpr int QUARTERS = 4, QU = UNITS / QUARTERS;        // the block's rows arrive in four parts of 8 units
+#ifndef DRB_GU_PARTS
+#define DRB_GU_PARTS 4
+#endif
+constexpr int QUARTERS = DRB_GU_PARTS, QU = UNITS / QUARTERS;  // the block's rows arrive in parts of QU units, one mbarrier each
 constexpr int QROW = H / 2;                               // 1024 bytes of nibbles per routed row
 constexpr int SMROW = (H / 64) * 4;                       // 128 bytes of (scale, min) per routed row
 constexpr int SSROW = (H / 128) * 2;                      // 32 bytes of scales per shared-expert row
