@@ -1,7 +1,7 @@
 """Golden vectors for the checkpoint quantisers, produced by the reference's own tools/convert.py
 (`quant_q4`, `quant_q8`) on seeded weights. Run where the reference checkout is present:
 
-    python tests/golden/make_quant_golden.py /root/reference
+    python tests/golden/make_quant_golden.py <path to the drama-rs checkout>
 
 Writes tests/golden/quant_seed7.npz: the float32 weights and the reference's packed int4 codes, (scale, min)
 pairs, int8 codes and scales.
@@ -37,4 +37,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_quant_golden.py <path to the drama-rs checkout>")
+    main(sys.argv[1])
