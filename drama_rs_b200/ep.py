@@ -253,10 +253,10 @@ class EpGpuFixed:
         check(self.l.dr_cublas_create(C.byref(self.blas), self.st.raw), "cublas_create")
         self.stream = torch.cuda.ExternalStream(self.st.raw.value)
         self.logit_bias = None
+        self.wcache: dict[int, torch.Tensor] = {}  # bf16 copies of the shared experts' int8 matrices, by matrix
         n, r = world * cap, max_rows
         dev = "cuda"
         f32, bf16, i32 = torch.float32, torch.bfloat16, torch.int32
-        self.wbuf = torch.empty(2 * i * h, dtype=bf16, device=dev)
         self.hn_b = torch.empty((r, h), dtype=bf16, device=dev)
         self.rlog = torch.empty((r, e + 1), dtype=f32, device=dev)
         self.idx = torch.empty((r, topk), dtype=i32, device=dev)
@@ -291,11 +291,18 @@ class EpGpuFixed:
         return self.recv_rows, self.recv_e, self.y_home
 
     def _gemm_q8(self, a: torch.Tensor, w, c: torch.Tensor, m: int) -> None:
+        """C = A . dequant(W)^T. The reference dequantises into one scratch buffer before every GEMM
+        (src/engine.rs:351-355); here the bf16 copy of a shared-expert matrix is kept after its first use
+        (6 MB per layer), which takes two launches out of every layer."""
         from .gpu import check, launched
 
-        q, s = w.rows(0)
-        launched(self.l.dr_dequant_q8(q, s, self._p(self.wbuf), w.n, w.k, self.st.raw), "dequant_q8", debug=False)
-        check(self.l.dr_gemm(self.blas, self._p(a), self._p(self.wbuf), self._p(c), m, w.n, w.k, 0.0), "gemm")
+        wb = self.wcache.get(id(w))
+        if wb is None:
+            q, s = w.rows(0)
+            wb = torch.empty(w.n * w.k, dtype=torch.bfloat16, device="cuda")
+            launched(self.l.dr_dequant_q8(q, s, self._p(wb), w.n, w.k, self.st.raw), "dequant_q8", debug=False)
+            self.wcache[id(w)] = wb
+        check(self.l.dr_gemm(self.blas, self._p(a), self._p(wb), self._p(c), m, w.n, w.k, 0.0), "gemm")
 
     def route(self, x: torch.Tensor):
         from .gpu import check, launched
