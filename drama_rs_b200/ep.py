@@ -15,7 +15,7 @@ prefill-side MoE block (src/engine.rs:544-604) that the benchmark configurations
     the shared expert and the residual (dr_moe_combine), so the result does not depend on N.
 
 The exchange is NCCL over NVLink on GPUs (gloo on CPU in the tests). Received rows land in this rank's
-own memory before any kernel reads them; nothing here uses peer pointers or multicast loads.
+own memory before any kernel reads them; nothing here reads a peer's memory directly.
 
 `ops` supplies the per-rank compute (the C-ABI kernels on a GPU; the tests plug in the oracle on CPU), so
 the bookkeeping below is the same code on both.
