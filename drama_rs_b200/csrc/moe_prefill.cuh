@@ -389,9 +389,9 @@ extern "C" int dr_moe_prefill(const uint8_t* gu_q, const __half2* gu_sm, const u
   if (!dev.ready) return -2;
   if (dev.prefill_mma) {
     // tensor-core path: two persistent grouped GEMMs (moe_prefill_mma.cuh)
-    drb_launch(pfmma::k_grouped<0, 0>, dim3(2 * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, gu_q, (const void*)gu_sm,
+    drb_launch(pfmma::k_grouped<0, 0>, dim3(pfmma::BLOCKS_PER_SM * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, gu_q, (const void*)gu_sm,
                (const void*)xp, (void*)act, offsets, counts, E);
-    drb_launch(pfmma::k_grouped<1, 0>, dim3(2 * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, d_q, (const void*)d_sm,
+    drb_launch(pfmma::k_grouped<1, 0>, dim3(pfmma::BLOCKS_PER_SM * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, d_q, (const void*)d_sm,
                (const void*)act, (void*)y, offsets, counts, E);
     return 0;
   }
@@ -411,9 +411,9 @@ extern "C" int dr_moe_prefill_fp8(const uint8_t* gu_w, const float* gu_s, const 
   const DrbDevice& dev = drb_device(st);
   if (!dev.ready) return -2;
   if (!dev.prefill_mma) return -1;
-  drb_launch(pfmma::k_grouped<0, 1>, dim3(2 * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, gu_w, (const void*)gu_s,
+  drb_launch(pfmma::k_grouped<0, 1>, dim3(pfmma::BLOCKS_PER_SM * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, gu_w, (const void*)gu_s,
              (const void*)xp, (void*)act, offsets, counts, E);
-  drb_launch(pfmma::k_grouped<1, 1>, dim3(2 * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, d_w, (const void*)d_s,
+  drb_launch(pfmma::k_grouped<1, 1>, dim3(pfmma::BLOCKS_PER_SM * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, d_w, (const void*)d_s,
              (const void*)act, (void*)y, offsets, counts, E);
   return 0;
 }

@@ -29,7 +29,11 @@
 namespace pfmma {
 
 constexpr int H = 2048, I = 512;
-constexpr int PRODUCER_WARPS = 8;
+#ifndef DRB_PF_PW
+#define DRB_PF_PW 8
+#endif
+constexpr int PRODUCER_WARPS = DRB_PF_PW;           // 8: two blocks per multiprocessor; 16: one block with twice the ring
+constexpr int BLOCKS_PER_SM = 16 / PRODUCER_WARPS;   // 4, 2 or 1
 constexpr int PRODUCERS = PRODUCER_WARPS * 32;
 constexpr int THREADS = PRODUCERS + 32;             // + the MMA-issuing warp
 constexpr int TILE_M = 128;
@@ -49,7 +53,10 @@ constexpr int STAGES = DRB_PF_STAGES;
 constexpr int CTL_BYTES = 1024;
 constexpr size_t SMEM_BYTES = CTL_BYTES + 1024 /* alignment slack */ + (size_t)STAGES * STAGE_BYTES;  // 98 KB
 constexpr int TMEM_COLS = MAX_N;
-constexpr int BPT = MAX_N * 8 / PRODUCERS;             // 16-byte B chunks per thread and K chunk: 4
+constexpr int BPT = MAX_N * 8 / PRODUCERS;             // 16-byte B chunks per thread and K chunk
+constexpr int SPLIT = PRODUCERS / TILE_M;              // threads per tile row: 1, 2 or 4
+constexpr int NST = 8 / SPLIT;                         // 16-byte operand chunks a thread writes per K chunk: 8, 4 or 2
+static_assert(BPT >= 1 && (SPLIT == 1 || SPLIT == 2 || SPLIT == 4), "operand mapping");
 
 struct Ctl {
   uint64_t full[STAGES];   // a stage has been filled (one arrival per producer warp)
@@ -204,7 +211,7 @@ DRB_DEV uint4 f16x8_perm(const uint4& v) {
 // Warps 0-7 convert operands into the stage ring and run the epilogue; warp 8 issues the MMAs. They meet only
 // on mbarriers: full[s] (8 warp arrivals), empty[s] and done (tcgen05.commit), tfree (accumulator drained).
 template <int GEMM, int FMT = 0>
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
     k_grouped(const uint8_t* __restrict__ Q, const void* __restrict__ SMv, const void* __restrict__ src, void* __restrict__ dst,
               const int* __restrict__ offsets, const int* __restrict__ counts, int E) {
   const __half2* SM = static_cast<const __half2*>(SMv);  // FMT 0
@@ -273,10 +280,10 @@ __global__ void __launch_bounds__(THREADS, 2)
   } else {
     // ================= producer / epilogue warps =================
     // This thread's share of the A tile: tile row t / 2, 32 of the chunk's 64 nibbles -> four 16-byte chunks.
-    const int arow = threadIdx.x >> 1, ahalf = threadIdx.x & 1;
-    uint32_t a_off[4];
+    const int arow = threadIdx.x / SPLIT, ahalf = threadIdx.x % SPLIT;
+    uint32_t a_off[NST];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) a_off[j] = swz_off(arow, 4 * ahalf + j);
+    for (int j = 0; j < NST; ++j) a_off[j] = swz_off(arow, NST * ahalf + j);
     // Its share of the B tile: 16-byte chunk c of token n for idx = t + i * 256.
     uint32_t b_off[BPT];
 #pragma unroll
@@ -292,7 +299,7 @@ __global__ void __launch_bounds__(THREADS, 2)
       // weight row of tile row r: gate/up interleaves gate j (even r) with up j (odd r)
       const int wrow = GEMM == 0 ? (arow & 1) * I + mt * (TILE_M / 2) + (arow >> 1) : mt * TILE_M + arow;
       constexpr int CB = FMT == 0 ? KC / 2 : KC;  // bytes of one K chunk of a weight row; this thread takes half of them
-      const uint8_t* qrow = Q + ((size_t)e * R + wrow) * (FMT == 0 ? K / 2 : K) + ahalf * (CB / 2);
+      const uint8_t* qrow = Q + ((size_t)e * R + wrow) * (FMT == 0 ? K / 2 : K) + ahalf * (CB / SPLIT);
       const __half2* smrow = SM + ((size_t)e * R + wrow) * (K / 64);
       const float* sfrow = SF + ((size_t)e * (R / 128) + (wrow >> 7)) * (K / 128);  // FMT 1: this row block's scales
       const float norm = FMT == 1 ? pow2_normaliser(__ldg(sfrow)) : 1.f;
@@ -315,28 +322,36 @@ __global__ void __launch_bounds__(THREADS, 2)
           return GEMM == 0 ? __ldg(p) : __ldcg(p);
         };
         // weights two chunks ahead, activations one chunk ahead, all in registers
-        uint4 q0 = __ldg(reinterpret_cast<const uint4*>(qrow));
+        // this thread's CB / SPLIT raw bytes of chunk kc as NL pieces of 16 bytes (one piece of 8 bytes when that is all)
+        constexpr int RAWB = CB / SPLIT;
+        constexpr int NL = RAWB >= 16 ? RAWB / 16 : 1;
+        auto load_w = [&](int kc, int piece) -> uint4 {
+          if (RAWB == 8) {
+            const uint2 v = __ldg(reinterpret_cast<const uint2*>(qrow + (size_t)kc * CB));
+            return make_uint4(v.x, v.y, 0u, 0u);
+          }
+          return __ldg(reinterpret_cast<const uint4*>(qrow + (size_t)kc * CB + 16 * piece));
+        };
+        uint4 q0[NL], q1[NL];
+#pragma unroll
+        for (int l = 0; l < NL; ++l) q0[l] = load_w(0, l), q1[l] = NKC > 1 ? load_w(1, l) : q0[l];
         __half2 sm0 = FMT == 0 ? __ldg(smrow) : __half2();
-        uint4 q1 = NKC > 1 ? __ldg(reinterpret_cast<const uint4*>(qrow + CB)) : q0;
         __half2 sm1 = FMT == 0 ? (NKC > 1 ? __ldg(smrow + 1) : sm0) : __half2();
-        uint4 p0 = q0, p1 = q1;  // FMT 1: the second 16 bytes of the thread's half chunk
-        if (FMT == 1) {
-          p0 = __ldg(reinterpret_cast<const uint4*>(qrow + 16));
-          p1 = NKC > 1 ? __ldg(reinterpret_cast<const uint4*>(qrow + CB + 16)) : p0;
-        }
         uint4 bn[BPT];
 #pragma unroll
         for (int i = 0; i < BPT; ++i) bn[i] = load_b(0, i);
         for (int kc = 0; kc < NKC; ++kc, ++chunk_no) {
           const int s = chunk_no % STAGES;
           unsigned char* st = stages + (size_t)s * STAGE_BYTES;
-          const uint4 qv = q0, pv = p0;
+          uint4 qv[NL];
+#pragma unroll
+          for (int l = 0; l < NL; ++l) qv[l] = q0[l], q0[l] = q1[l];
           const __half2 smv = sm0;
-          q0 = q1, sm0 = sm1, p0 = p1;
+          sm0 = sm1;
           if (kc + 2 < NKC) {
-            q1 = __ldg(reinterpret_cast<const uint4*>(qrow + (kc + 2) * CB));
+#pragma unroll
+            for (int l = 0; l < NL; ++l) q1[l] = load_w(kc + 2, l);
             if (FMT == 0) sm1 = __ldg(smrow + kc + 2);
-            else p1 = __ldg(reinterpret_cast<const uint4*>(qrow + (kc + 2) * CB + 16));
           }
           uint4 bv[BPT];
 #pragma unroll
@@ -349,16 +364,20 @@ __global__ void __launch_bounds__(THREADS, 2)
           if (chunk_no >= STAGES && !dead) dead = !mbar_wait(&ctl.empty[s], ((chunk_no / STAGES) - 1) & 1, DRB_ERR_TMEM);
           if (FMT == 0) {
             const __half2 s2 = __half2half2(__low2half(smv)), m2 = __half2half2(__high2half(smv));
-            const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(st + a_off[j]) = dequant8(w[j], s2, m2);
+            for (int l = 0; l < NL; ++l) {
+              const uint32_t w[4] = {qv[l].x, qv[l].y, qv[l].z, qv[l].w};
+#pragma unroll
+              for (int j = 0; j < NST / NL; ++j) *reinterpret_cast<uint4*>(st + a_off[l * (NST / NL) + j]) = dequant8(w[j], s2, m2);
+            }
           } else {
             const __half2 s2 = __float2half2_rn(__ldg(sfrow + (kc >> 1)) * norm);  // one scale per 128 inputs = two chunks
-            uint4 o0, o1, o2, o3;
-            dequant16_fp8(qv, s2, o0, o1);
-            dequant16_fp8(pv, s2, o2, o3);
-            *reinterpret_cast<uint4*>(st + a_off[0]) = o0, *reinterpret_cast<uint4*>(st + a_off[1]) = o1;
-            *reinterpret_cast<uint4*>(st + a_off[2]) = o2, *reinterpret_cast<uint4*>(st + a_off[3]) = o3;
+#pragma unroll
+            for (int l = 0; l < NL; ++l) {
+              uint4 o0, o1;
+              dequant16_fp8(qv[l], s2, o0, o1);
+              *reinterpret_cast<uint4*>(st + a_off[2 * l]) = o0, *reinterpret_cast<uint4*>(st + a_off[2 * l + 1]) = o1;
+            }
           }
 #pragma unroll
           for (int i = 0; i < BPT; ++i)
@@ -382,7 +401,7 @@ __global__ void __launch_bounds__(THREADS, 2)
           const int erow = GEMM == 0 ? (r & 1) * I + mt * (TILE_M / 2) + (r >> 1) : mt * TILE_M + r;
           unnorm = 1.f / pow2_normaliser(__ldg(SF + ((size_t)e * (R / 128) + (erow >> 7)) * (K / 128)));
         }
-        for (int c0 = (warp >> 2) * 16; c0 < N; c0 += 32) {  // warps 0-3 and 4-7 alternate 16-column groups
+        for (int c0 = (warp >> 2) * 16; c0 < N; c0 += 4 * PRODUCER_WARPS) {  // each set of four warps takes every (PRODUCER_WARPS / 4)-th 16-column group
           uint32_t v[16];
           tmem_ld16(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0, v);
           if (FMT == 1) {
