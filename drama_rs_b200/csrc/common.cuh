@@ -24,6 +24,15 @@ __device__ unsigned int g_drb_error = 0;
 // numbered points of a kernel into g_drb_trace. Compiled out of the product build.
 #ifdef DRB_TRACE
 __device__ unsigned long long g_drb_trace[64];
+__device__ unsigned long long g_drb_trace_blk[256 * 16];
+#define DRB_TRACE_BLK(i, tid)                                                     \
+  do {                                                                            \
+    if (threadIdx.x == (tid) && blockIdx.x < 256) {                               \
+      unsigned long long t_;                                                      \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                      \
+      g_drb_trace_blk[blockIdx.x * 16 + (i)] = t_;                                \
+    }                                                                             \
+  } while (0)
 #define DRB_TRACE_POINT(i, tid)                                                   \
   do {                                                                            \
     if (blockIdx.x == 0 && threadIdx.x == (tid)) {                                \
@@ -40,9 +49,18 @@ __device__ unsigned long long g_drb_trace[64];
       g_drb_trace[(i)] = t_;                                                      \
     }                                                                             \
   } while (0)
+#elif defined(DRB_TRACE_MODE) && DRB_TRACE_MODE == 1
+#define DRB_TRACE_POINT(i, tid) do { if (threadIdx.x == (tid)) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); } } while (0)
+#define DRB_TRACE_ANY(i, tid) ((void)0)
+#define DRB_TRACE_BLK(i, tid) DRB_TRACE_POINT(i, tid)
+#elif defined(DRB_TRACE_MODE) && DRB_TRACE_MODE == 2
+#define DRB_TRACE_POINT(i, tid) asm volatile("" ::: "memory")
+#define DRB_TRACE_ANY(i, tid) ((void)0)
+#define DRB_TRACE_BLK(i, tid) ((void)0)
 #else
 #define DRB_TRACE_POINT(i, tid) ((void)0)
 #define DRB_TRACE_ANY(i, tid) ((void)0)
+#define DRB_TRACE_BLK(i, tid) ((void)0)
 #endif
 
 enum DrbError : unsigned int {
@@ -98,6 +116,9 @@ DRB_DEV void mbar_init(uint64_t* bar, unsigned count) {
 DRB_DEV void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 
 DRB_DEV void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+#ifdef DRB_STACK_SKELETON
+  return;
+#endif
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 
@@ -130,6 +151,9 @@ DRB_DEV bool mbar_wait(uint64_t* bar, unsigned parity, unsigned err_code) {
 
 // Global -> shared bulk copy. dst, src 16-byte aligned; bytes a multiple of 16.
 DRB_DEV void bulk_g2s(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
+#ifdef DRB_STACK_SKELETON
+  return;
+#endif
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                    smem_u32(dst)),
                "l"(src), "r"(bytes), "r"(smem_u32(bar))

@@ -14,7 +14,8 @@
 //  * all calls share the one array per device. Two calls that overlap on the GPU (different streams, or a
 //    graph replay racing an eager call) overwrite each other's activations. Calls on one stream are safe.
 //  * the array keeps the previous call's values; that is harmless here, because the first kernel rewrites
-//    all 4608 entries before the second kernel reads any of them, so nothing needs clearing.
+//    every byte that the second kernel reads (16,384 of the 18,432: the activations cross as packed
+//    fixed-point blocks, the tail of the array is never touched), so nothing needs clearing.
 //
 // The first call on a device looks up the array's device address and sets the two kernels' launch
 // attributes (no allocation). Make that first call outside any stream capture.

@@ -5,10 +5,9 @@
 // logits in fp32, the k largest probabilities in descending order, ties to the lower expert index,
 // weights divided by their sum accumulated in rank order; logit E is the shared-expert gate.
 //
-// The top-k is done by rank counting instead of k serial arg-max rounds: every warp ranks its 32
-// probabilities against each other with shuffles, the at most 8*topk survivors are ranked against
-// each other through shared memory, and the entries whose final rank is below k write themselves
-// to their slot. Two block barriers instead of two per selected expert.
+// The top-k is done without k serial arg-max rounds: the per-warp maxima give a lower bound for the
+// selection, the few entries above it are ranked against each other through shared memory, and the ones
+// whose rank is below k write themselves to their slot. Two block barriers instead of two per selected expert.
 #pragma once
 
 #include "common.cuh"
@@ -24,6 +23,8 @@ DRB_DEV bool before(float pa, int ia, float pb, int ib) { return pa > pb || (pa 
 struct TopkSmem {
   float red[8];
   unsigned ured[8];
+  int cnt[8];
+  unsigned ukey[MAX_TOPK];
   __align__(16) unsigned long long comp[8 * MAX_TOPK];
   float top[MAX_TOPK];
 };
@@ -50,14 +51,18 @@ DRB_DEV float block_max_256(float v, float* red) {
 
 // Softmax + top-k of one row of logits by a 256-thread block. Thread e holds logit e (or -inf).
 //
-// Built for latency: no serial arg-max rounds. Probabilities are >= 0, so their bit patterns order
+// Built for latency: no serial arg-max rounds and no sort. Probabilities are >= 0, so their bit patterns order
 // like unsigned integers; key = bits + 1 for a valid entry, 0 otherwise.
-//   1. every lane ranks its key inside its warp with 31 independent shuffles (ties: lower lane first,
-//      and lane order is index order);
-//   2. the best min(topk, 32) of each warp go to shared memory as 64-bit composites
-//      (key << 32 | ~index), whose plain unsigned order is "larger probability, then lower index";
-//   3. each survivor counts the composites above its own (independent shared-memory reads);
-//      the ones whose count is below topk write themselves to their slot.
+//   1. The largest logit of every warp is known from the softmax's max step. When at least topk warps hold valid
+//      entries, the smallest of those maxima bounds the selection from below: topk entries are at least that large,
+//      so nothing smaller can be selected. The bound is carried over to probabilities by pushing it through the
+//      same exp and division every entry goes through (so entries that tie with it after rounding stay in).
+//   2. The entries at or above the bound (typically two or three dozen of 256) go to shared memory as 64-bit
+//      composites (key << 32 | ~index), whose plain unsigned order is "larger probability, then lower index";
+//      their position comes from a ballot, not from a ranking.
+//   3. Warp 0 ranks them against each other with shuffles (one survivor per lane; a loop over shared memory when
+//      ties at the bound leave more than 32) and the ones whose rank is below topk write themselves to their slot.
+// idx and wts are written by warp 0 only: other warps see them after the caller's next barrier.
 // The softmax sums use the reference's reduction tree (kernels/drama.cu:39-47) so z has the same bits.
 template <int BAR_ID = 0>
 DRB_DEV void topk_sync() {
@@ -65,10 +70,11 @@ DRB_DEV void topk_sync() {
   else asm volatile("bar.sync %0, 256;" ::"n"(BAR_ID) : "memory");
 }
 
+DRB_DEV float ord_to_float(unsigned o) { return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o); }
+
 // BAR_ID = 0: the block has exactly 256 threads. Otherwise threads 0..255 of a larger block call it and
 // synchronise on named barrier BAR_ID.
-// TK > 0 fixes topk at compile time (the loops over candidates unroll and their shared-memory reads
-// overlap instead of forming a 64-long dependent chain); TK = 0 takes it from the argument.
+// TK > 0 fixes topk at compile time; TK = 0 takes it from the argument.
 template <int BAR_ID = 0, int TK = 0>
 DRB_DEV void softmax_topk_impl(float v, int E, int topk, int* __restrict__ idx, float* __restrict__ wts, TopkSmem& sm) {
   if (TK > 0) topk = TK;
@@ -79,10 +85,15 @@ DRB_DEV void softmax_topk_impl(float v, int E, int topk, int* __restrict__ idx, 
   const unsigned wmax = __reduce_max_sync(0xffffffffu, ord);
   if (lane == 0) sm.ured[warp] = wmax;
   topk_sync<BAR_ID>();
-  unsigned mo = sm.ured[0];
+  const int nvalid = (E + 31) >> 5;  // warps that hold valid entries
+  unsigned mo = sm.ured[0], lo = sm.ured[0];
 #pragma unroll
-  for (int w = 1; w < 8; ++w) mo = max(mo, sm.ured[w]);
-  const float m = __uint_as_float((mo & 0x80000000u) ? (mo & 0x7fffffffu) : ~mo);
+  for (int w = 1; w < 8; ++w) {
+    const unsigned u = sm.ured[w];
+    mo = max(mo, u);
+    if (w < nvalid) lo = min(lo, u);
+  }
+  const float m = ord_to_float(mo);
   DRB_TRACE_ANY(40, 0);
   const float ex = e < E ? expf(v - m) : 0.f;
   const float ws = warp_sum(ex);
@@ -93,53 +104,82 @@ DRB_DEV void softmax_topk_impl(float v, int E, int topk, int* __restrict__ idx, 
   const float p = e < E ? ex / z : -1.f;
   DRB_TRACE_ANY(41, 0);
   const unsigned key = e < E ? __float_as_uint(p) + 1u : 0u;
-  int r = 0;
-#pragma unroll
-  for (int o = 1; o < 32; ++o) {
-    const int src = (lane + o) & 31;
-    const unsigned ko = __shfl_sync(0xffffffffu, key, src);
-    r += (ko > key || (ko == key && src < lane)) ? 1 : 0;
-  }
-  const int kk = topk < 32 ? topk : 32;
+  unsigned bound = 1u;  // every valid entry
+  if (nvalid >= topk) bound = __float_as_uint(expf(ord_to_float(lo) - m) / z) + 1u;
+  // a warp's largest entry is always kept, so at least min(topk, valid warps) entries are, whatever exp rounds to
+  const bool cand = key != 0u && (key >= bound || ord == wmax);
+  const unsigned bal = __ballot_sync(0xffffffffu, cand);
+  const unsigned long long mine = ((unsigned long long)key << 32) | (unsigned)(~e);
+  if (cand) sm.comp[warp * MAX_TOPK + __popc(bal & ((1u << lane) - 1u))] = mine;
+  if (lane == 0) sm.cnt[warp] = __popc(bal);
   DRB_TRACE_ANY(42, 0);
-  if (r < kk) sm.comp[warp * MAX_TOPK + r] = ((unsigned long long)key << 32) | (unsigned)(~e);
   topk_sync<BAR_ID>();
-  if (r < kk && key != 0u) {
-    const unsigned long long mine = ((unsigned long long)key << 32) | (unsigned)(~e);
-    int g = 0;
-    if (TK > 0) {
+  // Warp 0 finishes alone. The survivors sit in (warp, lane) order, which is index order, so among equal keys
+  // the earlier list position wins and 32-bit keys are all that has to travel.
+  if (warp != 0) return;
+  int off[9];
+  off[0] = 0;
 #pragma unroll
-      for (int w = 0; w < 8; ++w) {
+  for (int w = 0; w < 8; ++w) off[w + 1] = off[w] + sm.cnt[w];
+  const int n = off[8];
+  // survivor i sits in warp w's segment at position i - off[w]
+  auto fetch = [&](int i) {
+    int w = 0, ow = 0;
 #pragma unroll
-        for (int j = 0; j < TK; j += 2) {
-          const ulonglong2 c = *reinterpret_cast<const ulonglong2*>(&sm.comp[w * MAX_TOPK + j]);
-          g += (c.x > mine ? 1 : 0) + ((j + 1 < TK && c.y > mine) ? 1 : 0);
-        }
-      }
-    } else {
-      for (int w = 0; w < 8; ++w)
-        for (int j = 0; j < kk; ++j) g += sm.comp[w * MAX_TOPK + j] > mine ? 1 : 0;
+    for (int q = 1; q < 8; ++q) {
+      const bool past = i >= off[q];
+      w += past ? 1 : 0;
+      ow = past ? off[q] : ow;
     }
-    if (g < topk) {
-      idx[g] = e;
-      sm.top[g] = p;
+    return sm.comp[w * MAX_TOPK + (i - ow)];
+  };
+  if (n <= 32) {
+    // lane i takes survivor i; its rank is the number of survivors that come before it
+    const unsigned long long c = lane < n ? fetch(lane) : 0ull;
+    const unsigned k = (unsigned)(c >> 32);
+    int r = 0;
+#pragma unroll
+    for (int o = 1; o < 32; ++o) {
+      const int src = (lane + o) & 31;
+      const unsigned ko = __shfl_sync(0xffffffffu, k, src);
+      r += (ko > k || (ko == k && src < lane)) ? 1 : 0;
+    }
+    if (lane < n && r < topk) {
+      idx[r] = (int)(~(unsigned)c);
+      sm.top[r] = __uint_as_float(k - 1u);
+    }
+  } else {
+    // many ties at the bound: every lane ranks its survivors against the whole list
+    for (int i = lane; i < n; i += 32) {
+      const unsigned long long c = fetch(i);
+      int g = 0;
+#pragma unroll
+      for (int w2 = 0; w2 < 8; ++w2) {
+        const int c2 = off[w2 + 1] - off[w2];
+        for (int j = 0; j < c2; ++j) g += sm.comp[w2 * MAX_TOPK + j] > c ? 1 : 0;
+      }
+      if (g < topk) {
+        idx[g] = (int)(~(unsigned)c);
+        sm.top[g] = __uint_as_float((unsigned)(c >> 32) - 1u);
+      }
     }
   }
   DRB_TRACE_ANY(43, 0);
-  topk_sync<BAR_ID>();
-  if (e < topk) {
+  __syncwarp();
+  if (lane < topk) {
     float total = 0.f;
     if (TK > 0) {
       float t[TK > 0 ? TK : 1];
 #pragma unroll
-      for (int k = 0; k < TK; ++k) t[k] = sm.top[k];
+      for (int k2 = 0; k2 < TK; ++k2) t[k2] = sm.top[k2];
 #pragma unroll
-      for (int k = 0; k < TK; ++k) total += t[k];  // rank order, as the reference accumulates
+      for (int k2 = 0; k2 < TK; ++k2) total += t[k2];  // rank order, as the reference accumulates
     } else {
-      for (int k = 0; k < topk; ++k) total += sm.top[k];
+      for (int k2 = 0; k2 < topk; ++k2) total += sm.top[k2];
     }
-    wts[e] = sm.top[e] / total;
+    wts[lane] = sm.top[lane] / total;
   }
+  __syncwarp();
 }
 
 template <int BAR_ID = 0>

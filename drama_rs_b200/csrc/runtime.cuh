@@ -191,4 +191,7 @@ DRB_API int drb_grid_blocks(void) {
 DRB_API int drb_trace_read(unsigned long long* out, int n) {
   return (int)cudaMemcpyFromSymbol(out, g_drb_trace, sizeof(unsigned long long) * (n < 64 ? n : 64));
 }
+DRB_API int drb_trace_blk_read(unsigned long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_drb_trace_blk, sizeof(unsigned long long) * 256 * 16);
+}
 #endif

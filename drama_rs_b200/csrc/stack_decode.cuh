@@ -2,30 +2,38 @@
 //
 //   for each layer:  x <- x + moe_l(rmsnorm(x, post_norm_l))
 //
-// This is the 40-layer decode step of the benchmark (hidden state carried layer to layer) without
-// the 120 kernel boundaries of the per-layer calls. It has no counterpart in the reference's ABI
-// (there the token mixer sits between two MoE blocks); the per-layer entry points dr_router_topk and
-// dr_moe_decode remain the drop-in path and compute the same thing.
+// This is the 40-layer decode step of the benchmark (hidden state carried layer to layer). It has no
+// counterpart in the reference's ABI (there the token mixer sits between two MoE blocks); the per-layer
+// entry points dr_router_topk and dr_moe_decode remain the drop-in path and compute the same thing.
 //
-// One block per multiprocessor, launched cooperatively (all blocks resident). A layer has four phases
-// separated by three grid-wide barriers:
-//   P0  every block normalises and quantises x; blocks 0..128 compute two router logits each
-//   --- barrier: logits complete
-//   P1  every block reads the 257 logits and derives the top-8 itself (identical everywhere); its
-//       producer warp then requests its share of the chosen experts' gate/up rows AND down rows
-//   P2  gate/up + SwiGLU on the block's share -> act
-//   --- barrier: act complete
-//   P3  down + combine on the block's 13-14 output rows -> x
-//   --- barrier: x complete
-// Weights that do not depend on the routing (router rows, shared expert) are requested one phase to
-// one layer ahead, so they are in shared memory when needed. The code stays hot in the instruction
-// cache across layers, nothing is relaunched, and x / act / logits cross blocks through L2 only.
+// One block per multiprocessor, launched cooperatively (all blocks resident). A batch-1 layer is a chain
+// of three all-to-all hand-overs (logits -> routing, activations -> down projection, hidden state -> next
+// layer) around 18 MB of weight streaming, so what decides its duration is the cost of a hand-over, not
+// bandwidth. Nothing here uses a grid-wide barrier. Every value that crosses blocks travels as a 64-bit
+// word {payload, tag} written with one store and polled with plain loads by whoever needs it: the tag is
+// the layer number, a word is valid when its tag matches, and an aligned 64-bit access cannot tear. A
+// hand-over then costs one store and one load through L2 instead of store + fence + flag + poll + load,
+// and a consumer starts on the first words that arrive instead of waiting for the slowest producer.
 //
-// Every grid barrier is a bounded spin on a counter in global memory; when a wait runs out the
-// kernel sets the device error word, stops waiting anywhere else, and runs to its end.
+//   hidden state   y[2048]        {f32, tag}; written by the block that owns the row, read by every block
+//   router logits  logits[E + 1]  {f32, tag}; block b computes rows 2b, 2b + 1
+//   activations    routed: per 32 inputs of the down projection 24 limb words + delta + sum (the
+//                  block-fixed-point form of common.cuh), shared expert: per 16 inputs 12 limb words + delta;
+//                  one {word, tag} each, written by the gate/up block that produced the 32 values
+//
+// Work split per layer (G >= 144 blocks):
+//   gate/up  block b < 128: 32 units (gate row + up row) of routed expert slot b / 16; blocks 128..143: 32 units
+//            of the shared expert. All of a block's rows are requested at once (bulk copies, four mbarriers).
+//   down     block b: rows [2048 b / G, 2048 (b + 1) / G) of all eight chosen experts and of the shared expert.
+//   router   block b: rows 2b, 2b + 1 of the [E + 1, 2048] matrix; the eight warps of every block then derive the
+//            top-8 themselves from the E + 1 logits (identical everywhere), so the routing needs no second hand-over.
+// The producer warp requests the routed rows (gate/up and down) the moment the routing is known; rows that do
+// not depend on the routing (router, shared expert) are requested as soon as their buffer is free, up to a
+// layer ahead.
+//
+// Every wait is bounded: a poll that runs out sets the device error word and the block's abort flag, after
+// which no wait of that block spins again and the kernel runs to its end.
 #pragma once
-
-#include <cooperative_groups.h>
 
 #include "moe_decode.cuh"
 #include "router.cuh"
@@ -50,451 +58,812 @@ using moe::H;
 using moe::I;
 using moe::TOPK;
 
-// The persistent kernel keeps its own work split for the gate/up phase (byte-balanced shares of units, cut into
-// chunks that travel through a ring of stages) and quantises the activations per block in the down phase.
-namespace gu1 {
-constexpr int CW = 16;                                    // consumer warps, one unit (gate row + up row) at a time each
-constexpr int NT = CW * 32;                               // consumer threads
-constexpr int THREADS = NT + 32;                          // + one producer warp
-constexpr int MIN_GRID = 148;                             // a block then owns <= 28 routed and <= 4 shared units
-constexpr int UPW = 2;                                    // units per warp and pass: 32 units over 16 warps
-constexpr int RU = 4;                                     // routed units per chunk
-constexpr int SU = 2;                                     // shared-expert units per chunk
-constexpr int QROW = H / 2;                               // 1024 bytes of nibbles per routed row
-constexpr int SMROW = (H / 64) * 4;                       // 128 bytes of (scale, min) per routed row
-constexpr int SSROW = (H / 128) * 2;                      // 32 bytes of scales per shared-expert row
-constexpr int STAGE_BYTES = RU * 2 * (QROW + SMROW);      // 9216; a shared chunk needs SU*2*(H+32) = 8320
-constexpr int STAGES = 12;                                // >= 3 shared + 8 routed chunks (chunks are aligned)
-constexpr int CTL_BYTES = 1024;
-constexpr int QX_BYTES = (H / 32) * QB32_BYTES;           // the normalised activations as limb blocks
-constexpr size_t SMEM_BYTES = CTL_BYTES + QX_BYTES + (size_t)STAGES * STAGE_BYTES;
-static_assert(SU * 2 * (H + SSROW) <= STAGE_BYTES, "shared-expert chunk does not fit a stage");
-static_assert(NT == H / 4, "one float4 of x per consumer thread");
-
-struct Ctl {
-  uint64_t full[STAGES];
-  float red[CW];
-};
-
-struct Plan {
-  int us0, us1, ur0, ur1;  // this block's shared units and routed units
-  int sc0, nsc, rc0, nrc;  // aligned chunk ranges
-  DRB_DEV Plan(unsigned b, unsigned G) {
-    us0 = (int)((long long)I * b / G), us1 = (int)((long long)I * (b + 1) / G);
-    ur0 = (int)((long long)TOPK * I * b / G), ur1 = (int)((long long)TOPK * I * (b + 1) / G);
-    sc0 = us0 / SU, nsc = us1 > us0 ? (us1 + SU - 1) / SU - sc0 : 0;
-    rc0 = ur0 / RU, nrc = ur1 > ur0 ? (ur1 + RU - 1) / RU - rc0 : 0;
-  }
-  DRB_DEV int chunks() const { return nsc + nrc; }
-  DRB_DEV int units() const { return (us1 - us0) + (ur1 - ur0); }
-  // Units [ua, ub) of chunk t and the aligned base of the chunk. Chunks are aligned to multiples of
-  // RU (SU), so a routed chunk never straddles two experts.
-  DRB_DEV void chunk(int t, bool& shared, int& base, int& ua, int& ub) const {
-    shared = t < nsc;
-    if (shared) {
-      base = (sc0 + t) * SU, ua = max(base, us0), ub = min(base + SU, us1);
-    } else {
-      base = (rc0 + t - nsc) * RU, ua = max(base, ur0), ub = min(base + RU, ur1);
-    }
-  }
-  // The o-th unit of the block: shared units first. Returns its chunk and its slot in the chunk.
-  DRB_DEV void unit(int o, bool& shared, int& u, int& t, int& slot) const {
-    shared = o < us1 - us0;
-    if (shared) {
-      u = us0 + o, t = u / SU - sc0, slot = u % SU;
-    } else {
-      u = ur0 + o - (us1 - us0), t = nsc + u / RU - rc0, slot = u % RU;
-    }
-  }
-};
-}  // namespace gu1
-namespace dn1 {
-constexpr int QA_BYTES = (TOPK * I / 32) * QB32_BYTES;  // routed activations as even/odd limb blocks
-constexpr int QS_BYTES = (I / 16) * QB16_BYTES;         // the shared expert's activations, natural order
-}  // namespace dn1
-
-
-namespace dn = moe::dn;
-
-constexpr int CW = 16;
-constexpr int NT = CW * 32;
-constexpr int THREADS = NT + 32;
+constexpr int CW = 16;             // consumer warps
+constexpr int NT = CW * 32;        // consumer threads
+constexpr int THREADS = NT + 32;   // + the producer warp
 constexpr int MAX_E = 256;
 
-// Workspace in global memory (caller-provided, see drb_moe_stack_workspace_bytes).
-constexpr int MAX_BLOCKS = 256;
-struct Workspace {
-  unsigned flags[MAX_BLOCKS];  // flags[0] counts barrier arrivals; zeroed before every launch
-  float logits[MAX_E + 8];
-  float act[(TOPK + 1) * I];
-};
+// gate/up
+constexpr int UNITS = 32;                       // units per block; warp w takes units w and w + 16
+constexpr int ROUTED_UB = TOPK * I / UNITS;     // 128 blocks of routed units
+constexpr int SHARED_UB = I / UNITS;            // 16 blocks of shared-expert units
+constexpr int UNIT_BLOCKS = ROUTED_UB + SHARED_UB;
+constexpr int MIN_GRID = UNIT_BLOCKS;           // also >= (MAX_E + 2) / 2 router-row pairs and <= 16 down rows per block
+constexpr int MAX_GRID = 1024;
+constexpr int PARTS = 4, PU = UNITS / PARTS;    // a block's rows arrive in four parts of eight units
+constexpr int QROW = H / 2;                     // bytes of nibbles per routed gate/up row
+constexpr int SMROW = (H / 64) * 4;             // bytes of (scale, min) per routed gate/up row
+constexpr int SSROW = (H / 128) * 2;            // bytes of scales per shared-expert gate/up row
+constexpr int GU_STAGE_R = 2 * UNITS * (QROW + SMROW);  // 73,728
+constexpr int GU_STAGE_S = 2 * UNITS * (H + SSROW);     // 133,120
 
-// Shared memory map.
+// down
+constexpr int RT = 16;                          // rows per block at most
+constexpr int DQROW = I / 2;                    // 256 bytes of nibbles per routed down row
+constexpr int DSMROW = (I / 64) * 4;            // 32 bytes of (scale, min)
+constexpr int D_EXPERT = RT * (DQROW + DSMROW);
+constexpr int D_STAGE = TOPK * D_EXPERT + RT * I;  // 45,056
+
+// hand-over buffers
+constexpr int ACT_R_WORDS = 26;  // per routed block of 32 inputs: limbs [3][8] (even/odd order), delta, sum
+constexpr int ACT_S_WORDS = 14;  // per shared block of 16 inputs: limbs [3][4] (natural order), delta, pad
+// One replica of everything that crosses blocks. A cache line that every multiprocessor polls at the same
+// moment is served one request after the other, and the producer's store queues behind them, so the
+// producers write `reps` replicas and block b reads replica b % reps.
+struct alignas(128) Copy {
+  unsigned long long y[H];
+  unsigned long long logits[MAX_E + 8];
+  unsigned long long act_r[ROUTED_UB * ACT_R_WORDS];
+  unsigned long long act_s[2 * SHARED_UB * ACT_S_WORDS];
+};
+constexpr int MAX_REPS = 32;
+constexpr int COPY_WORDS = (int)(sizeof(Copy) / sizeof(unsigned long long));
+static_assert(sizeof(Copy) % 128 == 0 && (sizeof(unsigned long long) * (H + MAX_E + 8)) % 16 == 0, "aligned sections");
+
+// shared memory map
 constexpr int CTL_BYTES = 4096;
-constexpr int XS_BYTES = H * 4;                          // normalised x in fp32 (router dot)
-constexpr int QX_BYTES = gu1::QX_BYTES;                   // normalised x as limb blocks
-constexpr int RW_BYTES = 2 * 2 * H * 2;                  // two router rows, double-buffered over layers
-constexpr int QA_BYTES = dn1::QA_BYTES + dn1::QS_BYTES;    // act as limb blocks
-constexpr int RING_BYTES = gu1::STAGES * gu1::STAGE_BYTES; // gate/up chunks
-constexpr int DST_BYTES = dn::STAGE_BYTES;               // down rows
-constexpr size_t SMEM_BYTES = CTL_BYTES + XS_BYTES + QX_BYTES + RW_BYTES + QA_BYTES + RING_BYTES + DST_BYTES;
+constexpr int QX_BYTES = (H / 32) * QB32_BYTES;       // normalised x as limb blocks (gate/up)
+constexpr int RW_BYTES = 2 * H * 2;                   // this block's two router rows
+constexpr int QS_BYTES = (I / 16) * QB16_BYTES;       // the shared expert's activations as limb blocks (down)
+constexpr int PA_WARP_BYTES = 8 * ACT_R_WORDS * 4;     // a warp's eight routed activation blocks, payload words only
+constexpr int PA_BYTES = CW * PA_WARP_BYTES;
+constexpr size_t SMEM_BYTES = CTL_BYTES + QX_BYTES + RW_BYTES + QS_BYTES + PA_BYTES + GU_STAGE_S + D_STAGE;
+static_assert(SMEM_BYTES <= 232448, "does not fit one multiprocessor");
+
+// named barriers (0 is __syncthreads)
+constexpr int BAR_CONS = 1;   // the 512 consumer threads
+constexpr int BAR_TOPK = 2;   // warps 0..7 inside softmax_topk
+constexpr int BAR_IDX = 3;    // warps 0..7 arrive, the producer waits: the routing is in shared memory
+constexpr int BAR_GU = 4;     // consumers arrive, the producer waits: the gate/up stage is free
+constexpr int BAR_DN = 5;     // consumers arrive, the producer waits: the down stage is free
+constexpr int BAR_RT = 6;     // warps 0, 1 arrive, the producer waits: the router rows are free
 
 struct Ctl {
-  uint64_t gfull[gu1::STAGES];  // one phase per layer each
-  uint64_t dfull_routed, dfull_shared;
-  uint64_t rfull[2];           // router rows of even / odd layers
-  float red[CW];
-  float part[TOPK + 1][dn::RT];
-  float rpart[2][8];
+  uint64_t gfull[PARTS];
+  uint64_t dfull_r, dfull_s, rfull;
+  float red[3][CW];  // per warp: sum of squares, the two router rows' partial dot products
+  float actv[UNITS];
+  float part[TOPK][2][RT];
+  float part_s[RT];
   int idx[TOPK];
   float wts[TOPK];
   float sgate;
-  int abort;                   // set once a grid barrier timed out: no further waiting
+  int abort;  // a wait of this block ran out: no wait spins again
   router::TopkSmem tk;
 };
 static_assert(sizeof(Ctl) <= CTL_BYTES, "control block too large");
 
 template <int N>
-DRB_DEV void bar_named(int id) {
+DRB_DEV void bar_sync(int id) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(N) : "memory");
 }
-
-// Grid-wide barrier number `n` (1, 2, 3, ...): everyone adds one to a counter, then thread 0 of every block
-// polls it until it reaches n * blocks. Measured on B200 (148 blocks): 1.3 us, the same as cooperative-groups
-// grid.sync. A variant with one flag word per block, polled by a warp of every block, measured 3-7 us: any
-// cache line that all 148 multiprocessors read at once is slow on this two-die L2, and fewer lines win.
-// Bounded: ~2^17 polls, then the error word is set and `abort` makes every later barrier of this block fall
-// through.
-DRB_DEV void grid_barrier(Workspace* ws, Ctl& ctl, unsigned n) {
-  __syncthreads();
-  if (threadIdx.x == 0 && !ctl.abort) {
-    __threadfence();
-    atomicAdd(&ws->flags[0], 1u);
-    const unsigned target = n * gridDim.x;
-    bool ok = false;
-    for (unsigned it = 0; it < (1u << 17); ++it) {
-      unsigned v;
-      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(&ws->flags[0]) : "memory");
-      if (v >= target) {
-        ok = true;
-        break;
-      }
-      if (it > 256) __nanosleep(200);
-      if (it > 1024 && *reinterpret_cast<volatile unsigned*>(&g_drb_error) != 0u) break;  // someone else gave up
-    }
-    if (!ok) {
-      atomicMax(&g_drb_error, (unsigned)DRB_ERR_GRID_WAIT);
-      ctl.abort = 1;
-    }
-  }
-  __syncthreads();
+template <int N>
+DRB_DEV void bar_arrive(int id) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "n"(N) : "memory");
 }
 
+// ---- tagged 64-bit words ------------------------------------------------------------------------------
+DRB_DEV void ll_store(unsigned long long* p, uint32_t payload, uint32_t tag) {
+  const unsigned long long v = ((unsigned long long)tag << 32) | payload;
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// The same word into every replica (p points into replica 0).
+DRB_DEV void ll_store_all(unsigned long long* p, int reps, uint32_t payload, uint32_t tag) {
+  for (int r = 0; r < reps; ++r) ll_store(p + (size_t)r * COPY_WORDS, payload, tag);
+}
+#ifndef DRB_LL_LOAD
+#define DRB_LL_LOAD 0
+#endif
+#if DRB_LL_LOAD == 0
+#define DRB_LL_LD "ld.relaxed.gpu.global"
+#elif DRB_LL_LOAD == 1
+#define DRB_LL_LD "ld.global.cg"
+#else
+#define DRB_LL_LD "ld.volatile.global"
+#endif
+DRB_DEV void ll_load2(const unsigned long long* p, unsigned long long& a, unsigned long long& b) {
+  asm volatile(DRB_LL_LD ".v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+DRB_DEV unsigned long long ll_load1(const unsigned long long* p) {
+  unsigned long long a;
+  asm volatile(DRB_LL_LD ".u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+  return a;
+}
+
+#ifndef DRB_POLL_SLEEP
+#define DRB_POLL_SLEEP 0
+#endif
+// What a poll does when its data has not arrived. A hand-over completes within a few round trips through L2 and a
+// sleeping warp wakes up late (measured: any sleep between retries costs more than a microsecond per layer), so
+// retries go out back to back; what keeps them cheap is that every poll asks for whole cache lines. Only a wait
+// that has already lasted milliseconds backs off. Every so often the poll looks whether this block or any other
+// has given up. Returns true when the caller must stop waiting.
+DRB_DEV bool poll_failed(unsigned it, unsigned limit, volatile int* abort_flag) {
+  if (it >= limit) {
+    atomicMax(&g_drb_error, (unsigned)DRB_ERR_GRID_WAIT);
+    *abort_flag = 1;
+    return true;
+  }
+  if (DRB_POLL_SLEEP > 0 || it > 8192) __nanosleep(it > 8192 ? 400 : DRB_POLL_SLEEP);
+  if ((it & 1023u) == 1023u && (*abort_flag || *reinterpret_cast<volatile unsigned*>(&g_drb_error) != 0u)) {
+    *abort_flag = 1;
+    return true;
+  }
+  return false;
+}
+
+#ifndef DRB_POLL_STAGGER
+#define DRB_POLL_STAGGER 0  // clocks between the two requests a waiting thread keeps in flight (0: one request at a time)
+#endif
+DRB_DEV void poll_stagger() {
+  if (DRB_POLL_STAGGER > 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < DRB_POLL_STAGGER) {}
+  }
+}
+
+// Waits for NV consecutive 16-byte pieces (two tagged words each) at p and returns their 2 NV payloads.
+// Pieces that have arrived are not requested again. On give-up the missing payloads are zero.
+template <int NV>
+DRB_DEV void ll_poll(const unsigned long long* p, uint32_t tag, uint32_t (&out)[2 * NV], unsigned limit, volatile int* abort_flag) {
+  unsigned need = (1u << NV) - 1u;
+#pragma unroll
+  for (int i = 0; i < 2 * NV; ++i) out[i] = 0u;
+  if (*abort_flag) return;
+  unsigned long long ra[2 * NV], rb[2 * NV];
+  unsigned ma = 0u, mb = 0u;
+  auto issue = [&](unsigned long long (&r)[2 * NV], unsigned& m) {
+    m = need;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if ((m >> i) & 1u) ll_load2(p + 2 * i, r[2 * i], r[2 * i + 1]);
+  };
+  auto take = [&](const unsigned long long (&r)[2 * NV], unsigned m) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (((m & need) >> i) & 1u) {
+        if ((uint32_t)(r[2 * i] >> 32) == tag && (uint32_t)(r[2 * i + 1] >> 32) == tag) {
+          out[2 * i] = (uint32_t)r[2 * i], out[2 * i + 1] = (uint32_t)r[2 * i + 1];
+          need &= ~(1u << i);
+        }
+      }
+  };
+  issue(ra, ma);
+  if (DRB_POLL_STAGGER > 0) {
+    poll_stagger();
+    issue(rb, mb);
+  }
+  for (unsigned it = 0;; ++it) {
+    take(ra, ma);
+    if (need == 0u) break;
+    issue(ra, ma);
+    if (DRB_POLL_STAGGER > 0) {
+      take(rb, mb);
+      if (need == 0u) break;
+      issue(rb, mb);
+    }
+    if (poll_failed(it, limit, abort_flag)) break;
+  }
+}
+
+DRB_DEV uint32_t ll_poll1(const unsigned long long* p, uint32_t tag, unsigned limit, volatile int* abort_flag) {
+  if (*abort_flag) return 0u;
+  unsigned long long a = ll_load1(p), b2 = 0ull;
+  if (DRB_POLL_STAGGER > 0) {
+    poll_stagger();
+    b2 = ll_load1(p);
+  }
+  for (unsigned it = 0;; ++it) {
+    if ((uint32_t)(a >> 32) == tag) return (uint32_t)a;
+    a = ll_load1(p);
+    if (DRB_POLL_STAGGER > 0) {
+      if ((uint32_t)(b2 >> 32) == tag) return (uint32_t)b2;
+      b2 = ll_load1(p);
+    }
+    if (poll_failed(it, limit, abort_flag)) return 0u;
+  }
+}
+
+// The whole warp waits for NP consecutive 16-byte pieces at p and writes their 2 NP payload words to `pay` (shared
+// memory, private to the warp). Lane i asks for pieces i, i + 32, ...: every request of the warp covers whole cache
+// lines, a quarter of the requests that lanes fetching their own scattered pieces would make.
+template <int NP>
+DRB_DEV void ll_poll_warp(const unsigned long long* p, uint32_t tag, uint32_t* pay, int lane, unsigned limit, volatile int* abort_flag) {
+  constexpr int PER = (NP + 31) / 32;
+  unsigned need = 0u;
+#pragma unroll
+  for (int i = 0; i < PER; ++i)
+    if (lane + 32 * i < NP) need |= 1u << i;
+  const bool skip = *abort_flag != 0;
+  unsigned long long ra[2 * PER], rb[2 * PER];
+  unsigned ma = 0u, mb = 0u;
+  auto issue = [&](unsigned long long (&r)[2 * PER], unsigned& m) {
+    m = need;
+#pragma unroll
+    for (int i = 0; i < PER; ++i)
+      if ((m >> i) & 1u) ll_load2(p + 2 * (lane + 32 * i), r[2 * i], r[2 * i + 1]);
+  };
+  auto take = [&](const unsigned long long (&r)[2 * PER], unsigned m) {
+#pragma unroll
+    for (int i = 0; i < PER; ++i)
+      if (((m & need) >> i) & 1u) {
+        if ((uint32_t)(r[2 * i] >> 32) == tag && (uint32_t)(r[2 * i + 1] >> 32) == tag) {
+          *reinterpret_cast<uint2*>(pay + 2 * (lane + 32 * i)) = make_uint2((uint32_t)r[2 * i], (uint32_t)r[2 * i + 1]);
+          need &= ~(1u << i);
+        }
+      }
+  };
+  if (!skip) {
+    issue(ra, ma);
+    if (DRB_POLL_STAGGER > 0) {
+      poll_stagger();
+      issue(rb, mb);
+    }
+    for (unsigned it = 0;; ++it) {
+      take(ra, ma);
+      if (!__any_sync(0xffffffffu, need != 0u)) break;
+      issue(ra, ma);
+      if (DRB_POLL_STAGGER > 0) {
+        take(rb, mb);
+        if (!__any_sync(0xffffffffu, need != 0u)) break;
+        issue(rb, mb);
+      }
+      if (poll_failed(it, limit, abort_flag)) break;  // the same decision in every lane
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < PER; ++i)
+    if ((need >> i) & 1u) *reinterpret_cast<uint2*>(pay + 2 * (lane + 32 * i)) = make_uint2(0u, 0u);
+  __syncwarp();
+}
+
+// mbarrier wait that honours the abort flag; bounded like the polls, and without sleeping while the wait is short.
+DRB_DEV void wait_full(uint64_t* bar, unsigned parity, unsigned limit, volatile int* abort_flag) {
+#ifdef DRB_STACK_SKELETON
+  return;
+#endif
+  if (*abort_flag) return;
+  for (unsigned it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity)) return;
+    if (it >= limit) {
+      atomicMax(&g_drb_error, (unsigned)DRB_ERR_FULL_WAIT);
+      *abort_flag = 1;
+      return;
+    }
+    if (it > 8192) __nanosleep(400);
+    if ((it & 1023u) == 1023u && *abort_flag) return;
+  }
+}
+
+// One warp turns 32 values (lane = input index) into the 26 tagged words of a routed activation block, in every replica.
+DRB_DEV void publish_block32(float v, unsigned long long* dst, int reps, uint32_t tag, int lane) {
+  const float m = warp_max(fabsf(v));
+  const float sum = warp_sum(v);
+  const float delta = m > 0.f ? m * (1.f / 1048576.f) : 1.f;
+  int l0, l1, l2;
+  limbs3(__float2int_rn(v * (1.f / delta)), l0, l1, l2);
+  const uint32_t pack = (uint32_t)(l0 & 0xff) | ((uint32_t)(l1 & 0xff) << 8) | ((uint32_t)(l2 & 0xff) << 16);
+  // word w (lanes 0..7) holds inputs 8 (w / 2) + (w & 1) + {0, 2, 4, 6}
+  const int base = 8 * ((lane >> 1) & 3) + (lane & 1);
+  const uint32_t t0 = __shfl_sync(0xffffffffu, pack, base), t1 = __shfl_sync(0xffffffffu, pack, base + 2);
+  const uint32_t t2 = __shfl_sync(0xffffffffu, pack, base + 4), t3 = __shfl_sync(0xffffffffu, pack, base + 6);
+  // lane 8 j + i (j < 3, i < 8) stores limb word j of input group i; lane 24 the delta, lane 25 the sum
+  const uint32_t sel = lane < 8 ? 0x0040u : lane < 16 ? 0x0051u : 0x0062u;
+  uint32_t w = prmt(prmt(t0, t1, sel), prmt(t2, t3, sel), 0x5410u);
+  if (lane == 24) w = __float_as_uint(delta);
+  if (lane == 25) w = __float_as_uint(sum);
+  if (lane < ACT_R_WORDS) ll_store_all(dst + lane, reps, w, tag);
+}
+
+// Each half-warp turns 16 values (lane & 15 = input index) into the 14 tagged words of a shared-expert block
+// at dst + 14 * half, in every replica.
+DRB_DEV void publish_block16x2(float v, unsigned long long* dst, int reps, uint32_t tag, int lane) {
+  float m = fabsf(v);
+#pragma unroll
+  for (int o = 1; o < 16; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  const float delta = m > 0.f ? m * (1.f / 1048576.f) : 1.f;
+  int l0, l1, l2;
+  limbs3(__float2int_rn(v * (1.f / delta)), l0, l1, l2);
+  const uint32_t pack = (uint32_t)(l0 & 0xff) | ((uint32_t)(l1 & 0xff) << 8) | ((uint32_t)(l2 & 0xff) << 16);
+  // lane 16 h + 4 j + q (j < 3, q < 4) stores limb word j of inputs 4 q .. 4 q + 3 of half h; lane 16 h + 12 the delta, 16 h + 13 a pad
+  const int h = lane >> 4, li = lane & 15, q = li & 3;
+  const int base = 16 * h + 4 * q;
+  const uint32_t t0 = __shfl_sync(0xffffffffu, pack, base), t1 = __shfl_sync(0xffffffffu, pack, base + 1);
+  const uint32_t t2 = __shfl_sync(0xffffffffu, pack, base + 2), t3 = __shfl_sync(0xffffffffu, pack, base + 3);
+  const uint32_t sel = li < 4 ? 0x0040u : li < 8 ? 0x0051u : 0x0062u;
+  uint32_t w = prmt(prmt(t0, t1, sel), prmt(t2, t3, sel), 0x5410u);
+  if (li == 12) w = __float_as_uint(delta);
+  if (li == 13) w = 0u;
+  if (li < ACT_S_WORDS) ll_store_all(dst + h * ACT_S_WORDS + li, reps, w, tag);
+}
+
+#ifndef DRB_STACK_DOWN_AFTER
+#define DRB_STACK_DOWN_AFTER 3  // the down rows are requested once this part of the block's gate/up rows has landed (-1: at once)
+#endif
 
 __global__ void __launch_bounds__(THREADS, 1)
-    k_moe_stack(const drb_moe_layer* __restrict__ layers, int n_layers, float* x, Workspace* ws, int E, float eps,
-                int* __restrict__ idx_trace, float* __restrict__ wts_trace) {
+    k_moe_stack(const drb_moe_layer* __restrict__ layers, int n_layers, float* x, Copy* ws, int reps, int E, float eps,
+                int* __restrict__ idx_trace, float* __restrict__ wts_trace, unsigned poll_limit) {
   extern __shared__ __align__(128) unsigned char dyn[];
   Ctl& ctl = *reinterpret_cast<Ctl*>(dyn);
-  float4* xs4 = reinterpret_cast<float4*>(dyn + CTL_BYTES);
-  unsigned char* qx = dyn + CTL_BYTES + XS_BYTES;
+  unsigned char* qx = dyn + CTL_BYTES;
   unsigned char* rw = qx + QX_BYTES;
-  unsigned char* qa = rw + RW_BYTES;
-  unsigned char* qs = qa + dn1::QA_BYTES;
-  unsigned char* ring = qs + dn1::QS_BYTES;
-  unsigned char* dst = ring + RING_BYTES;
+  unsigned char* qs = rw + RW_BYTES;
+  unsigned char* pa = qs + QS_BYTES;
+  unsigned char* gst = pa + PA_BYTES;
+  unsigned char* dst = gst + GU_STAGE_S;
+  volatile int* abort_flag = &ctl.abort;
+
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const unsigned G = gridDim.x, b = blockIdx.x;
-  const gu1::Plan plan(b, G);
-  const int n0 = (int)((long long)H * b / G), n1 = (int)((long long)H * (b + 1) / G), nr = n1 - n0;
-  const int rrow0 = 2 * (int)b, nrr = max(0, min(2, E + 1 - rrow0));
+  const int G = (int)gridDim.x, b = (int)blockIdx.x;
+  const bool has_units = b < UNIT_BLOCKS;
+  const bool shared_blk = b >= ROUTED_UB && b < UNIT_BLOCKS;
+  const bool routed_blk = b < ROUTED_UB;
+  const int j0 = shared_blk ? (b - ROUTED_UB) * UNITS : (b % (I / UNITS)) * UNITS;  // first unit of the block
+  const int n0 = (int)((long long)H * b / G), n1 = (int)((long long)H * (b + 1) / G), nr = n1 - n0;  // down rows
+  const int rrow0 = 2 * b, nrr = max(0, min(2, E + 1 - rrow0));                                     // router rows
+  const bool needs_x = has_units || nrr > 0;
+  const Copy* mine = ws + (b % reps);  // the replica this block reads
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < gu1::STAGES; ++s) mbar_init(&ctl.gfull[s], 1);
-    mbar_init(&ctl.dfull_routed, 1);
-    mbar_init(&ctl.dfull_shared, 1);
-    mbar_init(&ctl.rfull[0], 1);
-    mbar_init(&ctl.rfull[1], 1);
+    for (int q = 0; q < PARTS; ++q) mbar_init(&ctl.gfull[q], 1);
+    mbar_init(&ctl.dfull_r, 1);
+    mbar_init(&ctl.dfull_s, 1);
+    mbar_init(&ctl.rfull, 1);
     ctl.abort = 0;
     mbar_fence_init();
   }
   __syncthreads();
 
-  // ---- producer-warp requests ------------------------------------------------------------------
-  auto issue_router = [&](int l) {  // this block's two router rows of layer l
-    if (lane == 0 && nrr > 0 && l < n_layers) {
-      uint64_t* bar = &ctl.rfull[l & 1];
-      mbar_expect_tx(bar, (unsigned)(nrr * H * 2));
-      bulk_g2s(rw + (l & 1) * (2 * H * 2), static_cast<const unsigned char*>(layers[l].router) + (size_t)rrow0 * H * 2,
-               (unsigned)(nrr * H * 2), bar);
-    }
-  };
-  auto issue_shared_gu = [&](int l) {  // shared-expert gate/up chunks: lane t = chunk t
-    if (l < n_layers && lane < plan.nsc) {
-      bool shared;
-      int base, ua, ub;
-      plan.chunk(lane, shared, base, ua, ub);
-      unsigned char* d = ring + (size_t)lane * gu1::STAGE_BYTES;
-      const int n = ub - ua, slot = ua - base;
-      const unsigned char* q = static_cast<const unsigned char*>(layers[l].sgu_q);
-      const unsigned char* sp = static_cast<const unsigned char*>(layers[l].sgu_s);
-      uint64_t* bar = &ctl.gfull[lane];
-      mbar_expect_tx(bar, (unsigned)(n * 2 * (H + gu1::SSROW)));
-      bulk_g2s(d + slot * H, q + (size_t)ua * H, (unsigned)(n * H), bar);
-      bulk_g2s(d + (gu1::SU + slot) * H, q + ((size_t)I + ua) * H, (unsigned)(n * H), bar);
-      bulk_g2s(d + 2 * gu1::SU * H + slot * gu1::SSROW, sp + (size_t)ua * gu1::SSROW, (unsigned)(n * gu1::SSROW), bar);
-      bulk_g2s(d + 2 * gu1::SU * H + (gu1::SU + slot) * gu1::SSROW, sp + ((size_t)I + ua) * gu1::SSROW, (unsigned)(n * gu1::SSROW), bar);
-    }
-  };
-  auto issue_shared_dn = [&](int l) {  // the shared expert's down rows of this block
-    if (lane == 0 && l < n_layers && nr > 0) {
-      mbar_expect_tx(&ctl.dfull_shared, (unsigned)(nr * I));
-      bulk_g2s(dst + TOPK * dn::EXPERT_BYTES, static_cast<const unsigned char*>(layers[l].sd_q) + (size_t)n0 * I, (unsigned)(nr * I),
-               &ctl.dfull_shared);
-    }
-  };
-  auto issue_routed = [&](int l) {  // needs ctl.idx: lanes 0.. = routed gate/up chunks, lanes 16..23 = down rows per expert
-    if (lane < plan.nrc) {
-      const int t = plan.nsc + lane;
-      bool shared;
-      int base, ua, ub;
-      plan.chunk(t, shared, base, ua, ub);
-      unsigned char* d = ring + (size_t)t * gu1::STAGE_BYTES;
-      const int n = ub - ua, slot = ua - base;
-      const int k = ua / I, j = ua % I;
-      const size_t ek = (size_t)ctl.idx[k];
-      const unsigned char* q = static_cast<const unsigned char*>(layers[l].gu_q) + ek * (2 * I) * gu1::QROW;
-      const unsigned char* smp = static_cast<const unsigned char*>(layers[l].gu_sm) + ek * (2 * I) * gu1::SMROW;
-      uint64_t* bar = &ctl.gfull[t];
-      mbar_expect_tx(bar, (unsigned)(n * 2 * (gu1::QROW + gu1::SMROW)));
-      bulk_g2s(d + slot * gu1::QROW, q + (size_t)j * gu1::QROW, (unsigned)(n * gu1::QROW), bar);
-      bulk_g2s(d + (gu1::RU + slot) * gu1::QROW, q + ((size_t)I + j) * gu1::QROW, (unsigned)(n * gu1::QROW), bar);
-      bulk_g2s(d + 2 * gu1::RU * gu1::QROW + slot * gu1::SMROW, smp + (size_t)j * gu1::SMROW, (unsigned)(n * gu1::SMROW), bar);
-      bulk_g2s(d + 2 * gu1::RU * gu1::QROW + (gu1::RU + slot) * gu1::SMROW, smp + ((size_t)I + j) * gu1::SMROW, (unsigned)(n * gu1::SMROW), bar);
-    }
-    if (nr > 0) {
-      if (lane == 15) mbar_expect_tx(&ctl.dfull_routed, (unsigned)(nr * TOPK * (dn::QROW + dn::SMROW)));
-      if (lane >= 16 && lane < 16 + TOPK) {
+  if (warp == CW) {
+    // =========================== producer warp ===========================
+    auto issue_router = [&](const drb_moe_layer& L) {
+      if (lane == 0 && nrr > 0) {
+        mbar_expect_tx(&ctl.rfull, (unsigned)(nrr * H * 2));
+        bulk_g2s(rw, static_cast<const unsigned char*>(L.router) + (size_t)rrow0 * H * 2, (unsigned)(nrr * H * 2), &ctl.rfull);
+      }
+    };
+    // lane 4 q + c requests copy c (gate rows, up rows, gate scales, up scales) of part q
+    auto issue_shared_gu = [&](const drb_moe_layer& L) {
+      if (!shared_blk) return;
+      const int q = lane >> 2, c = lane & 3;
+      if (q >= PARTS) return;
+      if (c == 0) mbar_expect_tx(&ctl.gfull[q], (unsigned)(2 * PU * (H + SSROW)));
+      __syncwarp(0x0000ffffu);
+      const unsigned char* shq = static_cast<const unsigned char*>(L.sgu_q);
+      const unsigned char* sp = static_cast<const unsigned char*>(L.sgu_s);
+      const int u0 = j0 + q * PU, l0 = q * PU;
+      if (c == 0) bulk_g2s(gst + (size_t)l0 * H, shq + (size_t)u0 * H, PU * H, &ctl.gfull[q]);
+      else if (c == 1) bulk_g2s(gst + (size_t)(UNITS + l0) * H, shq + ((size_t)I + u0) * H, PU * H, &ctl.gfull[q]);
+      else if (c == 2) bulk_g2s(gst + (size_t)2 * UNITS * H + l0 * SSROW, sp + (size_t)u0 * SSROW, PU * SSROW, &ctl.gfull[q]);
+      else bulk_g2s(gst + (size_t)2 * UNITS * H + (UNITS + l0) * SSROW, sp + ((size_t)I + u0) * SSROW, PU * SSROW, &ctl.gfull[q]);
+    };
+    auto issue_shared_dn = [&](const drb_moe_layer& L) {
+      if (lane == 0 && nr > 0) {
+        mbar_expect_tx(&ctl.dfull_s, (unsigned)(nr * I));
+        bulk_g2s(dst + TOPK * D_EXPERT, static_cast<const unsigned char*>(L.sd_q) + (size_t)n0 * I, (unsigned)(nr * I), &ctl.dfull_s);
+      }
+    };
+    // Needs ctl.idx (the gate/up rows are requested by consumer warp 0, which finishes the selection). Lanes 16..23: the down rows of expert slot lane - 16.
+    auto issue_routed_dn = [&](const drb_moe_layer& L) {
+      if (nr > 0 && lane >= 16 && lane < 16 + TOPK) {
+        if (lane == 16) mbar_expect_tx(&ctl.dfull_r, (unsigned)(nr * TOPK * (DQROW + DSMROW)));
+        __syncwarp(0x00ff0000u);
         const int k = lane - 16;
         const size_t row = (size_t)ctl.idx[k] * H + n0;
-        bulk_g2s(dst + k * dn::EXPERT_BYTES, static_cast<const unsigned char*>(layers[l].d_q) + row * dn::QROW, (unsigned)(nr * dn::QROW),
-                 &ctl.dfull_routed);
-        bulk_g2s(dst + k * dn::EXPERT_BYTES + dn::RT * dn::QROW, static_cast<const unsigned char*>(layers[l].d_sm) + row * dn::SMROW,
-                 (unsigned)(nr * dn::SMROW), &ctl.dfull_routed);
+        bulk_g2s(dst + k * D_EXPERT, static_cast<const unsigned char*>(L.d_q) + row * DQROW, (unsigned)(nr * DQROW), &ctl.dfull_r);
+        bulk_g2s(dst + k * D_EXPERT + RT * DQROW, static_cast<const unsigned char*>(L.d_sm) + row * DSMROW,
+                 (unsigned)(nr * DSMROW), &ctl.dfull_r);
       }
+    };
+
+    drb_moe_layer Lc = layers[0], Ln = Lc;
+    issue_router(Lc);
+    issue_shared_gu(Lc);
+    issue_shared_dn(Lc);
+    for (int l = 0; l < n_layers; ++l) {
+      const bool more = l + 1 < n_layers;
+      if (more) Ln = layers[l + 1];  // in registers before the routing arrives
+      bar_sync<256 + 32>(BAR_IDX);   // the routing of layer l is in ctl
+      // The gate/up rows are what the layer waits for; the down rows are needed a hand-over later. Requested together
+      // they share the memory system and delay the activations, so they follow once part of the gate/up rows is here.
+      if (DRB_STACK_DOWN_AFTER >= 0 && routed_blk) wait_full(&ctl.gfull[DRB_STACK_DOWN_AFTER < 0 ? 0 : DRB_STACK_DOWN_AFTER], (unsigned)l & 1u, poll_limit, abort_flag);
+      issue_routed_dn(Lc);
+      if (nrr > 0) {
+        bar_sync<64 + 32>(BAR_RT);
+        if (more) issue_router(Ln);
+      }
+      bar_sync<THREADS>(BAR_GU);
+      if (more) issue_shared_gu(Ln);
+      bar_sync<THREADS>(BAR_DN);
+      if (more) issue_shared_dn(Ln);
+      Lc = Ln;
+    }
+    return;
+  }
+
+  // =========================== consumer warps ===========================
+  const int t = threadIdx.x;
+  float xres = (t < nr) ? __ldcg(x + n0 + t) : 0.f;  // the residual of this thread's output row, carried in a register
+  // Warp w fetches the shared expert's activation blocks 2w, 2w + 1 into shared memory (7 pieces each).
+  auto fetch_shared_act = [&](uint32_t tag) {
+    if (lane < 14) {
+      const int sb = 2 * warp + lane / 7, piece = lane % 7;
+      uint32_t o[2];
+      ll_poll<1>(mine->act_s + (size_t)sb * ACT_S_WORDS + 2 * piece, tag, o, poll_limit, abort_flag);
+      *reinterpret_cast<uint2*>(qs + (size_t)sb * QB16_BYTES + piece * 8) = make_uint2(o[0], o[1]);
     }
   };
-
-  if (warp == CW) {
-    issue_router(0);
-    issue_shared_gu(0);
-    issue_shared_dn(0);
-  }
-  unsigned nbar = 0;
+  // Constants of the coming layer are fetched a layer ahead: a pointer out of the layer table and then the value
+  // behind it are two dependent trips to memory, which would otherwise open every layer.
+  const unsigned char* guq_next = static_cast<const unsigned char*>(layers[0].gu_q);
+  const unsigned char* gusm_next = static_cast<const unsigned char*>(layers[0].gu_sm);
+  const float* pn_next = static_cast<const float*>(layers[0].post_norm);
+  const __half* sds_next = static_cast<const __half*>(layers[0].sd_s);
+  float4 wv_next = needs_x ? reinterpret_cast<const float4*>(pn_next)[t] : make_float4(0.f, 0.f, 0.f, 0.f);
+  float ssc_next = warp < nr ? __half2float(__ldg(sds_next + (size_t)(n0 + warp) * (I / 128) + (lane >> 3))) : 0.f;
   for (int l = 0; l < n_layers; ++l) {
-    const drb_moe_layer L = layers[l];
-    const unsigned par = l & 1;
-    DRB_TRACE_POINT(0, 0);
-    // ================= P0: normalise + quantise x, router logits =================
-    if (warp < CW) {
-      const float4 wv = reinterpret_cast<const float4*>(L.post_norm)[threadIdx.x];
-      const float4 xv = __ldcg(reinterpret_cast<const float4*>(x) + threadIdx.x);
-      const float ss = warp_sum(xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w);
-      if (lane == 0) ctl.red[warp] = ss;
-      bar_named<NT>(1);
-      float t = 0.f;
-#pragma unroll
-      for (int w = 0; w < CW; ++w) t += ctl.red[w];
-      const float inv = rsqrtf(t / H + eps);
-      const float4 xh = make_float4(xv.x * inv * wv.x, xv.y * inv * wv.y, xv.z * inv * wv.z, xv.w * inv * wv.w);
-      xs4[threadIdx.x] = xh;
-      quant_store_eo(qx, threadIdx.x, xh, true);
-      bar_named<NT>(1);
-      DRB_TRACE_POINT(1, 0);
-      if (warp < 8 && nrr > 0) {  // threads 0..255: one 16-byte chunk (8 weights) of each of the block's two rows
-        const float4 a = xs4[2 * threadIdx.x], c = xs4[2 * threadIdx.x + 1];
-        unsigned long long xp[4] = {pack2(a.x, a.y), pack2(a.z, a.w), pack2(c.x, c.y), pack2(c.z, c.w)};
-        mbar_wait(&ctl.rfull[par], (l >> 1) & 1, DRB_ERR_FULL_WAIT);
-        const unsigned char* rows = rw + par * (2 * H * 2);
+    const uint32_t tag = (uint32_t)l + 1u;
+    const unsigned par = (unsigned)l & 1u;
+    const float4 wv = wv_next;
+    const float ssc = ssc_next;
+    const unsigned char* guq_cur = guq_next;
+    const unsigned char* gusm_cur = gusm_next;
+    if (l + 1 < n_layers) {
+      guq_next = static_cast<const unsigned char*>(layers[l + 1].gu_q);
+      gusm_next = static_cast<const unsigned char*>(layers[l + 1].gu_sm);
+      pn_next = static_cast<const float*>(layers[l + 1].post_norm);
+      sds_next = static_cast<const __half*>(layers[l + 1].sd_s);
+    }
+    DRB_TRACE_POINT(0, 0); DRB_TRACE_BLK(0, 0);
+
+    // ---- the hidden state: sum of squares and this block's two router rows in one pass, then the limb blocks.
+    // The logits are linear in the hidden state, so the rows are multiplied with y * norm weight as it arrives and
+    // the 1 / rms factor is applied to the two sums: the routing does not wait for a second pass over x.
+    if (needs_x) {
+      if (nrr > 0) wait_full(&ctl.rfull, par, poll_limit, abort_flag);
+      float4 xv;
+      if (l == 0) {
+        xv = __ldcg(reinterpret_cast<const float4*>(x) + t);
+      } else {
+        uint32_t o[4];
+        ll_poll<2>(mine->y + 4 * t, tag - 1u, o, poll_limit, abort_flag);
+        xv = make_float4(__uint_as_float(o[0]), __uint_as_float(o[1]), __uint_as_float(o[2]), __uint_as_float(o[3]));
+      }
+      DRB_TRACE_POINT(1, 0); DRB_TRACE_BLK(1, 0);
+      DRB_TRACE_POINT(32 + warp, warp * 32 + 31);
+      const float4 xw = make_float4(xv.x * wv.x, xv.y * wv.y, xv.z * wv.z, xv.w * wv.w);
+      float v[4] = {xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w, 0.f, 0.f, 0.f};
+      if (nrr > 0) {
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-          float d = 0.f;
-          if (r < nrr) {
-            float p0, p1;
-            unpack2(dot8_bf16(*reinterpret_cast<const uint4*>(rows + (size_t)r * H * 2 + threadIdx.x * 16), xp, 0ull), p0, p1);
-            d = p0 + p1;
-          }
-          d = warp_sum(d);
-          if (lane == 0) ctl.rpart[r][warp] = d;
-        }
-        bar_named<256>(2);
-        if ((int)threadIdx.x < nrr) {
-          float tt = 0.f;
-#pragma unroll
-          for (int w = 0; w < 8; ++w) tt += ctl.rpart[threadIdx.x][w];
-          __stcg(&ws->logits[rrow0 + threadIdx.x], tt);
+          const uint2 w = *reinterpret_cast<const uint2*>(rw + (size_t)r * H * 2 + 8 * t);
+          v[1 + r] = (xw.x * __uint_as_float(w.x << 16) + xw.y * __uint_as_float(w.x & 0xffff0000u)) +
+                     (xw.z * __uint_as_float(w.y << 16) + xw.w * __uint_as_float(w.y & 0xffff0000u));
         }
       }
-    } else {
-      issue_router(l + 1);
+      {
+        const bool hi16 = lane & 16, hi8 = lane & 8;
+        const float r0 = (hi16 ? v[2] : v[0]) + __shfl_xor_sync(0xffffffffu, hi16 ? v[0] : v[2], 16);
+        const float r1 = (hi16 ? v[3] : v[1]) + __shfl_xor_sync(0xffffffffu, hi16 ? v[1] : v[3], 16);
+        float s = (hi8 ? r1 : r0) + __shfl_xor_sync(0xffffffffu, hi8 ? r0 : r1, 8);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        // lanes 0..7 carry v[0], 8..15 v[1], 16..23 v[2]
+        if ((lane & 7) == 0 && lane < 24) ctl.red[lane >> 3][warp] = s;
+      }
+      bar_sync<NT>(BAR_CONS);
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < CW; ++w) tot += ctl.red[0][w];
+      const float inv = rsqrtf(tot / H + eps);
+      DRB_TRACE_POINT(2, 0); DRB_TRACE_BLK(2, 0);
+      if (t < nrr) {
+        float u = 0.f;
+#pragma unroll
+        for (int w = 0; w < CW; ++w) u += ctl.red[1 + t][w];
+        ll_store_all(ws->logits + rrow0 + t, reps, __float_as_uint(u * inv), tag);
+      }
+      DRB_TRACE_POINT(3, 0); DRB_TRACE_BLK(3, 0);
+      if (warp < 2 && nrr > 0) bar_arrive<64 + 32>(BAR_RT);  // every warp read its part of the rows before the barrier above
+      if (has_units) {
+        quant_store_eo(qx, t, make_float4(xw.x * inv, xw.y * inv, xw.z * inv, xw.w * inv), true);
+        bar_sync<NT>(BAR_CONS);
+      }
+      DRB_TRACE_POINT(15, 0); DRB_TRACE_BLK(15, 0);
     }
-    DRB_TRACE_POINT(2, 0);
-    grid_barrier(ws, ctl, ++nbar);
-    DRB_TRACE_POINT(3, 0);
 
-    // ================= P1: every block derives the routing itself =================
-    if (threadIdx.x < 256) {
-      const int e = threadIdx.x;
-      const float v = e < E ? __ldcg(&ws->logits[e]) : -INFINITY;
-      if (v == 12345.678f) ctl.sgate = 0.f;  // keep the load before the probe
-      DRB_TRACE_ANY(39, 0);
-      router::softmax_topk<3>(v, E, TOPK, ctl.idx, ctl.wts, ctl.tk);
-      if (e == 0) ctl.sgate = __ldcg(&ws->logits[E]);
-    }
-    __syncthreads();
-    if (b == 0 && threadIdx.x < TOPK) {
-      if (idx_trace) idx_trace[l * TOPK + threadIdx.x] = ctl.idx[threadIdx.x];
-      if (wts_trace) wts_trace[l * TOPK + threadIdx.x] = ctl.wts[threadIdx.x];
-    }
-    DRB_TRACE_POINT(4, 0);
-    if (warp == CW) issue_routed(l);
+    // ---- warps 0..7 of every block derive the routing from the E + 1 logits. A shared-expert block does its gate/up
+    // rows first: they do not depend on the routing, and every other block needs their activations.
+    //
+    // What the layer waits for is the request for the chosen experts' rows, so the selection is made on the logits
+    // alone (softmax is monotone: the eight largest logits are the eight largest probabilities) and warp 0, which
+    // finishes the selection, requests this block's gate/up rows itself. The probabilities and weights follow while
+    // the rows are on their way. Selection: the per-warp maxima bound it from below (eight entries are at least as
+    // large as the smallest of eight warp maxima), the few entries at or above the bound are ranked against each
+    // other by warp 0 with shuffles, ties to the lower index. An entry whose probability merely rounds to that of a
+    // larger logit is never preferred to it, which is the one place where this differs from ranking rounded
+    // probabilities.
+    auto derive_routing = [&]() {
+      // the shared expert's gate logit is fetched by a thread that has no logit of its own to wait for (two waits in
+      // one thread are two round trips); it is read after the next barrier of all consumers
+      if (t == 256) ctl.sgate = __uint_as_float(ll_poll1(mine->logits + E, tag, poll_limit, abort_flag));
+      if (warp >= 8) return;
+      router::TopkSmem& tk = ctl.tk;
+      const bool valid = t < E;
+      float v = -INFINITY;
+      if (valid) v = __uint_as_float(ll_poll1(mine->logits + t, tag, poll_limit, abort_flag));
+      DRB_TRACE_POINT(4, 0); DRB_TRACE_BLK(4, 0);
+      const unsigned vb = __float_as_uint(v);
+      const unsigned ord = (vb & 0x80000000u) ? ~vb : (vb | 0x80000000u);  // orders like the floats
+      const unsigned wmax = __reduce_max_sync(0xffffffffu, ord);
+      if (lane == 0) tk.ured[warp] = wmax;
+      bar_sync<256>(BAR_TOPK);
+      const int nvalid = (E + 31) >> 5;  // warps that hold valid entries
+      unsigned mo = tk.ured[0], lo = tk.ured[0];
+#pragma unroll
+      for (int w = 1; w < 8; ++w) {
+        const unsigned u = tk.ured[w];
+        mo = max(mo, u);
+        if (w < nvalid) lo = min(lo, u);
+      }
+      if (nvalid < TOPK) lo = 0u;  // fewer than eight maxima: every valid entry stays in
+      const bool cand = valid && ord >= lo;
+      const unsigned bal = __ballot_sync(0xffffffffu, cand);
+      if (cand) tk.comp[warp * router::MAX_TOPK + __popc(bal & ((1u << lane) - 1u))] = ((unsigned long long)ord << 32) | (unsigned)(~t);
+      if (lane == 0) tk.cnt[warp] = __popc(bal);
+      bar_sync<256>(BAR_TOPK);
+      // the softmax denominator does not depend on the selection and is off the path to the requests:
+      // same reduction tree as dr_router_topk
+      const float m = router::ord_to_float(mo);
+      if (warp != 0) {
+        bar_arrive<256 + 32>(BAR_IDX);
+        const float wsum = warp_sum(valid ? expf(v - m) : 0.f);
+        if (lane == 0) tk.red[warp] = wsum;
+        bar_sync<256>(BAR_TOPK);
+        return;
+      }
+      int off[9];
+      off[0] = 0;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) off[w + 1] = off[w] + tk.cnt[w];
+      const int n = off[8];
+      auto fetch = [&](int i) {  // survivor i sits in warp w's segment at position i - off[w]; list order is index order
+        int w = 0, ow = 0;
+#pragma unroll
+        for (int q = 1; q < 8; ++q) {
+          const bool past = i >= off[q];
+          w += past ? 1 : 0;
+          ow = past ? off[q] : ow;
+        }
+        return tk.comp[w * router::MAX_TOPK + (i - ow)];
+      };
+      if (n <= 32) {
+        const unsigned long long c = lane < n ? fetch(lane) : 0ull;
+        const unsigned k = (unsigned)(c >> 32);
+        int r = 0;
+#pragma unroll
+        for (int o = 1; o < 32; ++o) {
+          const int src = (lane + o) & 31;
+          const unsigned ko = __shfl_sync(0xffffffffu, k, src);
+          r += (ko > k || (ko == k && src < lane)) ? 1 : 0;
+        }
+        if (lane < n && r < TOPK) ctl.idx[r] = (int)(~(unsigned)c), tk.ukey[r] = k;
+      } else {
+        for (int i = lane; i < n; i += 32) {  // many ties at the bound: rank against the whole list
+          const unsigned long long c = fetch(i);
+          int g = 0;
+#pragma unroll
+          for (int w2 = 0; w2 < 8; ++w2) {
+            const int c2 = off[w2 + 1] - off[w2];
+            for (int j = 0; j < c2; ++j) g += tk.comp[w2 * router::MAX_TOPK + j] > c ? 1 : 0;
+          }
+          if (g < TOPK) ctl.idx[g] = (int)(~(unsigned)c), tk.ukey[g] = (unsigned)(c >> 32);
+        }
+      }
+      __syncwarp();
+      DRB_TRACE_POINT(5, 0); DRB_TRACE_BLK(5, 0);
+      // this block's gate/up rows: lane 4 q + c requests copy c (gate rows, up rows, gate scales, up scales) of part q
+      if (routed_blk && lane < 4 * PARTS) {
+        const int q = lane >> 2, c = lane & 3;
+        if (c == 0) mbar_expect_tx(&ctl.gfull[q], (unsigned)(2 * PU * (QROW + SMROW)));
+        __syncwarp(0x0000ffffu);
+        const size_t ek = (size_t)ctl.idx[b / (I / UNITS)];
+        const unsigned char* qp = guq_cur + ek * (2 * I) * QROW;
+        const unsigned char* smp = gusm_cur + ek * (2 * I) * SMROW;
+        const int u0 = j0 + q * PU, l0 = q * PU;
+        if (c == 0) bulk_g2s(gst + (size_t)l0 * QROW, qp + (size_t)u0 * QROW, PU * QROW, &ctl.gfull[q]);
+        else if (c == 1) bulk_g2s(gst + (size_t)(UNITS + l0) * QROW, qp + ((size_t)I + u0) * QROW, PU * QROW, &ctl.gfull[q]);
+        else if (c == 2) bulk_g2s(gst + (size_t)2 * UNITS * QROW + l0 * SMROW, smp + (size_t)u0 * SMROW, PU * SMROW, &ctl.gfull[q]);
+        else bulk_g2s(gst + (size_t)2 * UNITS * QROW + (UNITS + l0) * SMROW, smp + ((size_t)I + u0) * SMROW, PU * SMROW, &ctl.gfull[q]);
+      }
+      bar_arrive<256 + 32>(BAR_IDX);  // the producer warp requests the down rows
+      DRB_TRACE_POINT(6, 0); DRB_TRACE_BLK(6, 0);
+      {
+        const float wsum = warp_sum(valid ? expf(v - m) : 0.f);
+        if (lane == 0) tk.red[0] = wsum;
+      }
+      bar_sync<256>(BAR_TOPK);
+      // weights: p = exp(v - m) / z of the chosen eight, renormalised over their sum taken in the order
+      // "larger probability, then lower index" (kernels/drama.cu:397-435 of the reference)
+      const float z = ((tk.red[0] + tk.red[4]) + (tk.red[2] + tk.red[6])) + ((tk.red[1] + tk.red[5]) + (tk.red[3] + tk.red[7]));
+      const int sl = lane & (TOPK - 1);
+      const float pj = expf(router::ord_to_float(tk.ukey[sl]) - m) / z;
+      const int ej = ctl.idx[sl];
+      int rj = 0;
+#pragma unroll
+      for (int o = 1; o < TOPK; ++o) {
+        const int src = (lane & ~(TOPK - 1)) | ((sl + o) & (TOPK - 1));
+        const float po = __shfl_sync(0xffffffffu, pj, src);
+        const int eo = __shfl_sync(0xffffffffu, ej, src);
+        rj += (po > pj || (po == pj && eo < ej)) ? 1 : 0;
+      }
+      if (lane < TOPK) tk.top[rj] = pj;
+      __syncwarp();
+      float total = 0.f;
+#pragma unroll
+      for (int k2 = 0; k2 < TOPK; ++k2) total += tk.top[k2];
+      if (lane < TOPK) {
+        ctl.wts[lane] = pj / total;  // per slot; the slots are in logit order
+        if (b == 0) {                // the routing as the reference reports it
+          if (idx_trace) idx_trace[l * TOPK + rj] = ej;
+          if (wts_trace) wts_trace[l * TOPK + rj] = pj / total;
+        }
+      }
+    };
+    if (!shared_blk) derive_routing();
 
-    // ================= P2: gate/up + SwiGLU on this block's share =================
-    if (warp < CW) {
+    // ---- gate/up + SwiGLU on this block's 32 units
+    if (has_units) {
+      // This lane owns k in [32 lane, +32) and [1024 + 32 lane, +32).
       QAct<32, true> x0, x1;
       float X0, X1;
       qact_load(x0, X0, qx + (size_t)lane * QB32_BYTES);
       qact_load(x1, X1, qx + (size_t)(32 + lane) * QB32_BYTES);
-      const int nunits = plan.units();
-      for (int o0 = warp; o0 < nunits; o0 += CW * 2) {
-        float v[4];
-        int uid[2];
+      float v[4];  // v[2i] = gate, v[2i + 1] = up partial sums of unit warp + 16 i
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int o = o0 + i * CW;
-          v[2 * i] = v[2 * i + 1] = 0.f;
-          uid[i] = -1;
-          if (o >= nunits) continue;
-          bool shared;
-          int u, t, slot;
-          plan.unit(o, shared, u, t, slot);
-          uid[i] = shared ? TOPK * I + u : u;
-          const unsigned char* st = ring + (size_t)t * gu1::STAGE_BYTES;
-          mbar_wait(&ctl.gfull[t], par, DRB_ERR_FULL_WAIT);
-          if (shared) {
-            const uint4* gr = reinterpret_cast<const uint4*>(st + (size_t)slot * H);
-            const uint4* ur = reinterpret_cast<const uint4*>(st + (size_t)(gu1::SU + slot) * H);
-            const __half* gs = reinterpret_cast<const __half*>(st + 2 * gu1::SU * H + (size_t)slot * gu1::SSROW);
-            const __half* us = reinterpret_cast<const __half*>(st + 2 * gu1::SU * H + (size_t)(gu1::SU + slot) * gu1::SSROW);
-            v[2 * i] = __half2float(gs[lane >> 2]) * x0.delta * dot32_q8_eo(gr[2 * lane], gr[2 * lane + 1], x0, 0) +
-                       __half2float(gs[8 + (lane >> 2)]) * x1.delta * dot32_q8_eo(gr[64 + 2 * lane], gr[64 + 2 * lane + 1], x1, 0);
-            v[2 * i + 1] = __half2float(us[lane >> 2]) * x0.delta * dot32_q8_eo(ur[2 * lane], ur[2 * lane + 1], x0, 0) +
-                           __half2float(us[8 + (lane >> 2)]) * x1.delta * dot32_q8_eo(ur[64 + 2 * lane], ur[64 + 2 * lane + 1], x1, 0);
-          } else {
-            const uint4* gr = reinterpret_cast<const uint4*>(st + (size_t)slot * gu1::QROW);
-            const uint4* ur = reinterpret_cast<const uint4*>(st + (size_t)(gu1::RU + slot) * gu1::QROW);
-            const __half2* gs = reinterpret_cast<const __half2*>(st + 2 * gu1::RU * gu1::QROW + (size_t)slot * gu1::SMROW);
-            const __half2* us = reinterpret_cast<const __half2*>(st + 2 * gu1::RU * gu1::QROW + (size_t)(gu1::RU + slot) * gu1::SMROW);
-            const float2 g0 = __half22float2(gs[lane >> 1]), g1 = __half22float2(gs[16 + (lane >> 1)]);
-            const float2 u0 = __half22float2(us[lane >> 1]), u1 = __half22float2(us[16 + (lane >> 1)]);
-            v[2 * i] = g0.x * x0.delta * dot32_q4_i(gr[lane], x0, 0) + g0.y * X0 + g1.x * x1.delta * dot32_q4_i(gr[32 + lane], x1, 0) + g1.y * X1;
-            v[2 * i + 1] = u0.x * x0.delta * dot32_q4_i(ur[lane], x0, 0) + u0.y * X0 + u1.x * x1.delta * dot32_q4_i(ur[32 + lane], x1, 0) + u1.y * X1;
-          }
-        }
-        const bool hi16 = lane & 16, hi8 = lane & 8;
-        const float r0 = (hi16 ? v[2] : v[0]) + __shfl_xor_sync(0xffffffffu, hi16 ? v[0] : v[2], 16);
-        const float r1 = (hi16 ? v[3] : v[1]) + __shfl_xor_sync(0xffffffffu, hi16 ? v[1] : v[3], 16);
-        float sres = (hi8 ? r1 : r0) + __shfl_xor_sync(0xffffffffu, hi8 ? r0 : r1, 8);
-        sres += __shfl_xor_sync(0xffffffffu, sres, 4);
-        sres += __shfl_xor_sync(0xffffffffu, sres, 2);
-        sres += __shfl_xor_sync(0xffffffffu, sres, 1);
-        const float upv = __shfl_xor_sync(0xffffffffu, sres, 8);
-        if ((lane & 15) == 0) {
-          const int id = (lane & 16) ? uid[1] : uid[0];
-          if (id >= 0) __stcg(&ws->act[id], silu_f(sres) * upv);
+      for (int i = 0; i < 2; ++i) {
+        const int u = warp + CW * i;
+        // Between its two units a routed block picks up the shared expert's activations: they were published while this
+        // block waited for its rows (a shared block fetches them after it has published its own).
+        if (i == 1 && routed_blk) fetch_shared_act(tag);
+        wait_full(&ctl.gfull[u / PU], par, poll_limit, abort_flag);
+        if (i == 0) { DRB_TRACE_POINT(7, 0); DRB_TRACE_BLK(7, 0); }
+        if (shared_blk) {
+          const uint4* gr = reinterpret_cast<const uint4*>(gst + (size_t)u * H);
+          const uint4* ur = reinterpret_cast<const uint4*>(gst + (size_t)(UNITS + u) * H);
+          const __half* gs = reinterpret_cast<const __half*>(gst + (size_t)2 * UNITS * H + (size_t)u * SSROW);
+          const __half* us = reinterpret_cast<const __half*>(gst + (size_t)2 * UNITS * H + (size_t)(UNITS + u) * SSROW);
+          v[2 * i] = __half2float(gs[lane >> 2]) * x0.delta * dot32_q8_eo(gr[2 * lane], gr[2 * lane + 1], x0, 0) +
+                     __half2float(gs[8 + (lane >> 2)]) * x1.delta * dot32_q8_eo(gr[64 + 2 * lane], gr[64 + 2 * lane + 1], x1, 0);
+          v[2 * i + 1] = __half2float(us[lane >> 2]) * x0.delta * dot32_q8_eo(ur[2 * lane], ur[2 * lane + 1], x0, 0) +
+                         __half2float(us[8 + (lane >> 2)]) * x1.delta * dot32_q8_eo(ur[64 + 2 * lane], ur[64 + 2 * lane + 1], x1, 0);
+        } else {
+          const uint4* gr = reinterpret_cast<const uint4*>(gst + (size_t)u * QROW);
+          const uint4* ur = reinterpret_cast<const uint4*>(gst + (size_t)(UNITS + u) * QROW);
+          const __half2* gs = reinterpret_cast<const __half2*>(gst + (size_t)2 * UNITS * QROW + (size_t)u * SMROW);
+          const __half2* us = reinterpret_cast<const __half2*>(gst + (size_t)2 * UNITS * QROW + (size_t)(UNITS + u) * SMROW);
+          // w = s q + m: sum_k w x = s delta sum(q n) + m sum(x) per 64-group; chunk c belongs to group c / 2.
+          const float2 g0 = __half22float2(gs[lane >> 1]), g1 = __half22float2(gs[16 + (lane >> 1)]);
+          const float2 u0 = __half22float2(us[lane >> 1]), u1 = __half22float2(us[16 + (lane >> 1)]);
+          v[2 * i] = g0.x * x0.delta * dot32_q4_i(gr[lane], x0, 0) + g0.y * X0 + g1.x * x1.delta * dot32_q4_i(gr[32 + lane], x1, 0) + g1.y * X1;
+          v[2 * i + 1] = u0.x * x0.delta * dot32_q4_i(ur[lane], x0, 0) + u0.y * X0 + u1.x * x1.delta * dot32_q4_i(ur[32 + lane], x1, 0) + u1.y * X1;
         }
       }
+      bar_arrive<THREADS>(BAR_GU);  // nothing of the stage is read after this point
+      DRB_TRACE_POINT(8, 0); DRB_TRACE_BLK(8, 0);
+      // Fold the four per-lane sums into one reduction.
+      const bool hi16 = lane & 16, hi8 = lane & 8;
+      const float r0 = (hi16 ? v[2] : v[0]) + __shfl_xor_sync(0xffffffffu, hi16 ? v[0] : v[2], 16);
+      const float r1 = (hi16 ? v[3] : v[1]) + __shfl_xor_sync(0xffffffffu, hi16 ? v[1] : v[3], 16);
+      float s = (hi8 ? r1 : r0) + __shfl_xor_sync(0xffffffffu, hi8 ? r0 : r1, 8);
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      // lanes 0..7: gate of unit warp, 8..15: its up, 16..23: gate of unit warp + 16, 24..31: its up
+      const float upv = __shfl_xor_sync(0xffffffffu, s, 8);
+      if ((lane & 15) == 0) ctl.actv[warp + (lane & 16)] = silu_f(s) * upv;
+      bar_sync<NT>(BAR_CONS);
+      if (warp == 0) {
+        const float a = ctl.actv[lane];
+        if (shared_blk) publish_block16x2(a, ws->act_s + (size_t)(b - ROUTED_UB) * 2 * ACT_S_WORDS, reps, tag, lane);
+        else publish_block32(a, ws->act_r + (size_t)b * ACT_R_WORDS, reps, tag, lane);
+      }
+      DRB_TRACE_POINT(9, 0); DRB_TRACE_BLK(9, 0);
+    } else {
+      bar_arrive<THREADS>(BAR_GU);
     }
-    DRB_TRACE_POINT(5, 0);
-    grid_barrier(ws, ctl, ++nbar);
-    DRB_TRACE_POINT(6, 0);
-    if (warp == CW) issue_shared_gu(l + 1);  // the ring is free again
+    if (shared_blk) derive_routing();
 
-    // ================= P3: down + combine on this block's rows =================
-    if (warp < CW) {
-      const int ke = warp & (TOPK - 1), rh = warp >> 3;
-      const float ssc = warp < nr ? __half2float(__ldg(static_cast<const __half*>(L.sd_s) + (size_t)(n0 + warp) * (I / 128) + (lane >> 3))) : 0.f;
-      const float xres = (int)threadIdx.x < nr ? __ldcg(x + n0 + threadIdx.x) : 0.f;  // residual, fetched early
-      const float sgv = sigmoid_f(ctl.sgate);
-      constexpr int NR4 = TOPK * I / 4, NS4 = I / 4;
-      constexpr int AV = (NR4 + NS4 + NT - 1) / NT;
-      float4 av[AV];
-#pragma unroll
-      for (int i = 0; i < AV; ++i) {
-        const int g = threadIdx.x + i * NT;
-        av[i] = g < NR4 + NS4 ? __ldcg(reinterpret_cast<const float4*>(ws->act) + g) : make_float4(0.f, 0.f, 0.f, 0.f);
+    // ---- down + combine on this block's rows
+    {
+      if (!routed_blk) {  // a routed block fetched them between its two units; the barrier there made them visible
+        fetch_shared_act(tag);
+        bar_sync<NT>(BAR_CONS);
       }
-#pragma unroll
-      for (int i = 0; i < AV; ++i) {
-        const int g = threadIdx.x + i * NT;
-        if (g - lane < NR4) quant_store_eo(qa, g, av[i], true);
-        else quant_store_nat(qs, g - NR4, av[i], g < NR4 + NS4);
+      if (l + 1 < n_layers) {  // the next layer's constants, needed a layer from now
+        if (needs_x) wv_next = reinterpret_cast<const float4*>(pn_next)[t];
+        if (warp < nr) ssc_next = __half2float(__ldg(sds_next + (size_t)(n0 + warp) * (I / 128) + (lane >> 3)));
       }
-      bar_named<NT>(1);
-      DRB_TRACE_POINT(7, 0);
-      const int cc = lane & 15, half = lane >> 4;
+      QAct<16, false> sq;  // the shared expert: the whole warp per row, lane = 16-byte chunk of 16 int8
+      qact_load(sq, qs + (size_t)lane * QB16_BYTES);
+      // routed: warp (ke, kh) covers inputs [256 kh, +256) of expert slot ke; lane (rsub, c): row 4 pass + rsub, 16-byte chunk 8 kh + c
+      const int ke = warp & (TOPK - 1), kh = warp >> 3;
+      const int c = lane & 7, rsub = lane >> 3;
+      const int chunk = kh * 8 + c;
       QAct<32, true> aq;
       float A;
-      qact_load(aq, A, qa + (size_t)(ke * (I / 32) + cc) * QB32_BYTES);
-      QAct<16, false> sq;
-      qact_load(sq, qs + (size_t)lane * QB16_BYTES);
-      if (nr > 0) {
-        mbar_wait(&ctl.dfull_routed, par, DRB_ERR_FULL_WAIT);
-        mbar_wait(&ctl.dfull_shared, par, DRB_ERR_FULL_WAIT);
-      }
-      const unsigned char* eq = dst + ke * dn::EXPERT_BYTES;
-      const unsigned char* esm = eq + dn::RT * dn::QROW;
-      float v[4];
+      {
+        // the warp's eight blocks are contiguous: fetched together, then every lane takes the 26 words of its block
+        uint32_t* mypa = reinterpret_cast<uint32_t*>(pa + (size_t)warp * PA_WARP_BYTES);
+        ll_poll_warp<8 * ACT_R_WORDS / 2>(mine->act_r + (size_t)(ke * (I / 32) + kh * 8) * ACT_R_WORDS, tag, mypa, lane, poll_limit, abort_flag);
+        const uint2* src = reinterpret_cast<const uint2*>(mypa + c * ACT_R_WORDS);
+        uint32_t o[ACT_R_WORDS];
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        const int lr = 2 * (rh * 4 + p) + half;
-        v[p] = 0.f;
-        if (lr < nr) {
-          const uint4 w = *reinterpret_cast<const uint4*>(eq + (size_t)lr * dn::QROW + 16 * cc);
-          const float2 sm = __half22float2(*reinterpret_cast<const __half2*>(esm + (size_t)lr * dn::SMROW + 4 * (cc >> 1)));
-          v[p] = sm.x * aq.delta * dot32_q4_i(w, aq, 0) + sm.y * A;
+        for (int i = 0; i < ACT_R_WORDS / 2; ++i) {
+          const uint2 w2 = src[i];
+          o[2 * i] = w2.x, o[2 * i + 1] = w2.y;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 3; ++j)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) aq.l[j][i] = o[j * 8 + i];
+        aq.delta = __uint_as_float(o[24]);
+        A = __uint_as_float(o[25]);
+      }
+      DRB_TRACE_POINT(11, 0); DRB_TRACE_BLK(11, 0);
+      DRB_TRACE_POINT(48 + warp, warp * 32 + 31);
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      float s_sh = 0.f;
+      if (nr > 0) {
+        wait_full(&ctl.dfull_r, par, poll_limit, abort_flag);
+        DRB_TRACE_POINT(12, 0); DRB_TRACE_BLK(12, 0);
+        const unsigned char* eq = dst + ke * D_EXPERT;
+        const unsigned char* esm = eq + RT * DQROW;
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const int lr = 4 * p + rsub;
+          if (lr < nr) {
+            const uint4 w = *reinterpret_cast<const uint4*>(eq + (size_t)lr * DQROW + 16 * chunk);
+            const float2 sm = __half22float2(*reinterpret_cast<const __half2*>(esm + (size_t)lr * DSMROW + 4 * (chunk >> 1)));
+            v[p] = sm.x * aq.delta * dot32_q4_i(w, aq, 0) + sm.y * A;
+          }
+        }
+        if (warp < nr) {
+          wait_full(&ctl.dfull_s, par, poll_limit, abort_flag);
+          s_sh = ssc * sq.delta * dot16_q8_i(*reinterpret_cast<const uint4*>(dst + TOPK * D_EXPERT + (size_t)warp * I + 16 * lane), sq, 0);
         }
       }
+      bar_arrive<THREADS>(BAR_DN);  // nothing of the stage is read after this point
+      DRB_TRACE_POINT(13, 0); DRB_TRACE_BLK(13, 0);
       {
-        const bool hi8 = lane & 8, hi4 = lane & 4;
-        const float r0 = (hi8 ? v[2] : v[0]) + __shfl_xor_sync(0xffffffffu, hi8 ? v[0] : v[2], 8);
-        const float r1 = (hi8 ? v[3] : v[1]) + __shfl_xor_sync(0xffffffffu, hi8 ? v[1] : v[3], 8);
-        float sres = (hi4 ? r1 : r0) + __shfl_xor_sync(0xffffffffu, hi4 ? r0 : r1, 4);
-        sres += __shfl_xor_sync(0xffffffffu, sres, 2);
-        sres += __shfl_xor_sync(0xffffffffu, sres, 1);
-        const int p = (hi8 ? 2 : 0) + (hi4 ? 1 : 0);
-        const int lr = 2 * (rh * 4 + p) + half;
-        if ((lane & 3) == 0 && lr < nr) ctl.part[ke][lr] = sres;
+        // Fold the four sums (each to be reduced over the 8 lanes of a row group) into one reduction.
+        const bool hi4 = lane & 4, hi2 = lane & 2;
+        const float r0 = (hi4 ? v[2] : v[0]) + __shfl_xor_sync(0xffffffffu, hi4 ? v[0] : v[2], 4);
+        const float r1 = (hi4 ? v[3] : v[1]) + __shfl_xor_sync(0xffffffffu, hi4 ? v[1] : v[3], 4);
+        float s = (hi2 ? r1 : r0) + __shfl_xor_sync(0xffffffffu, hi2 ? r0 : r1, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        const int p = (hi4 ? 2 : 0) + (hi2 ? 1 : 0);
+        const int lr = 4 * p + rsub;
+        if ((lane & 1) == 0 && lr < nr) ctl.part[ke][kh][lr] = s;
       }
-      {
-        float sres = 0.f;
-        if (warp < nr) sres = ssc * sq.delta * dot16_q8_i(*reinterpret_cast<const uint4*>(dst + TOPK * dn::EXPERT_BYTES + (size_t)warp * I + 16 * lane), sq, 0);
-        sres = warp_sum(sres);
-        if (lane == 0 && warp < nr) ctl.part[TOPK][warp] = sres;
-      }
-      bar_named<NT>(1);
-      if ((int)threadIdx.x < nr) {
-        const int lr = threadIdx.x;
+      s_sh = warp_sum(s_sh);
+      if (lane == 0 && warp < nr) ctl.part_s[warp] = s_sh;
+      bar_sync<NT>(BAR_CONS);
+      DRB_TRACE_POINT(10, 0); DRB_TRACE_BLK(10, 0);
+      if (t < nr) {
         float acc = 0.f;
 #pragma unroll
-        for (int k = 0; k < TOPK; ++k) acc += ctl.wts[k] * ctl.part[k][lr];
-        x[n0 + lr] = xres + sgv * ctl.part[TOPK][lr] + acc;
+        for (int k = 0; k < TOPK; ++k) acc += ctl.wts[k] * (ctl.part[k][0][t] + ctl.part[k][1][t]);
+        const float yn = xres + sigmoid_f(ctl.sgate) * ctl.part_s[t] + acc;
+        xres = yn;
+        if (l + 1 < n_layers) ll_store_all(ws->y + n0 + t, reps, __float_as_uint(yn), tag);
+        else x[n0 + t] = yn;
       }
+      DRB_TRACE_POINT(14, 0); DRB_TRACE_BLK(14, 0);
     }
-    DRB_TRACE_POINT(8, 0);
-    grid_barrier(ws, ctl, ++nbar);
-    DRB_TRACE_POINT(9, 0);
-    if (warp == CW) issue_shared_dn(l + 1);  // the down stage is free again
   }
 }
 
@@ -503,29 +872,36 @@ static cudaError_t configure_all() {
   if (e != cudaSuccess) return e;
   return drb_carveout(k_moe_stack);
 }
+
+constexpr unsigned POLL_LIMIT = 1u << 20;  // about half a second of polling
+constexpr int REPS = 1;
+
 }  // namespace stack
 
-// Bytes of device workspace drb_moe_stack_decode needs (any contents; the call zeroes what it must).
-extern "C" int drb_moe_stack_workspace_bytes(void) { return (int)sizeof(stack::Workspace); }
+// Bytes of device workspace drb_moe_stack_decode needs (any contents; every call clears what it uses first).
+extern "C" int drb_moe_stack_workspace_bytes(void) { return (int)(sizeof(stack::Copy) * stack::MAX_REPS); }
 
 // x <- x + moe_l(rmsnorm(x)) for l = 0 .. n_layers - 1, in place, in one cooperative kernel launch.
 // layers: device array of n_layers drb_moe_layer. workspace: drb_moe_stack_workspace_bytes() bytes of
 // device memory, 256-byte aligned. idx_trace / wts_trace: optional device arrays [n_layers, topk]
 // receiving every layer's routing (NULL to skip). Only h = 2048, i = 512, topk = 8, e <= 256, and a
-// device with at least 148 multiprocessors are supported (-1 otherwise). Capturable in a graph.
+// device with at least 144 multiprocessors are supported (-1 otherwise). Capturable in a graph.
 // Calls that share a workspace must not overlap on the GPU.
 extern "C" int drb_moe_stack_decode(const drb_moe_layer* layers, int n_layers, float* x, void* workspace, int e, int topk,
                                     int h, int i, float eps, int* idx_trace, float* wts_trace, cudaStream_t st) {
   if (h != moe::H || i != moe::I || topk != moe::TOPK || e < topk || e > stack::MAX_E || n_layers < 0) return -1;
   const DrbDevice& dev = drb_device(st);
   if (!dev.ready) return -2;
-  if (dev.sms < stack::gu1::MIN_GRID) return -1;
+  if (dev.sms < stack::MIN_GRID || dev.sms > stack::MAX_GRID) return -1;
   if (n_layers == 0) return 0;
-  stack::Workspace* ws = static_cast<stack::Workspace*>(workspace);
-  if (dev.sms > stack::MAX_BLOCKS) return -1;
-  cudaError_t err = cudaMemsetAsync(ws->flags, 0, sizeof(ws->flags), st);
+  stack::Copy* ws = static_cast<stack::Copy*>(workspace);
+  int reps = stack::REPS;
+  if (const char* v = getenv("DRB_STACK_REPS")) reps = atoi(v) > 0 && atoi(v) <= stack::MAX_REPS ? atoi(v) : reps;
+  // tags restart at 1 with every launch, so whatever an earlier launch left must not look valid
+  cudaError_t err = cudaMemsetAsync(ws, 0, sizeof(stack::Copy) * reps, st);
   if (err != cudaSuccess) return (int)err;
-  void* args[] = {(void*)&layers, (void*)&n_layers, (void*)&x, (void*)&ws, (void*)&e, (void*)&eps, (void*)&idx_trace, (void*)&wts_trace};
+  unsigned limit = stack::POLL_LIMIT;
+  void* args[] = {(void*)&layers, (void*)&n_layers, (void*)&x, (void*)&ws, (void*)&reps, (void*)&e, (void*)&eps, (void*)&idx_trace, (void*)&wts_trace, (void*)&limit};
   err = cudaLaunchCooperativeKernel((const void*)stack::k_moe_stack, dim3(dev.sms), dim3(stack::THREADS), args, stack::SMEM_BYTES, st);
   return err == cudaSuccess ? 0 : (int)err;
 }

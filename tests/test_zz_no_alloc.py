@@ -3,7 +3,8 @@
 Meant for hosts that cannot allocate device memory when they call (fixed memory budget, foreign allocator,
 a capture in progress elsewhere). The test calls it through the C ABI next to dr_moe_decode on the same
 inputs, twice in a row with different activations, and expects identical results: both entry points run the
-same two kernels and differ only in where the 4608 scratch floats live. Collected last on purpose.
+same two kernels and differ only in where the 4608 scratch floats live. Each round ends with the call form the
+reference's engine uses, one buffer passed as x, res and y. Collected last on purpose.
 """
 
 import numpy as np
@@ -47,6 +48,12 @@ def test_static_scratch_entry_point_matches_dr_moe_decode():
         b = y_new.download(np.float32, 2048, st)
         assert np.isfinite(a).all() and np.abs(a).max() > 1.0
         assert np.array_equal(a, b), f"call {call}: max difference {np.abs(a - b).max()}"
+        # the way the reference's engine calls the layer: one buffer is input, residual and output at once
+        launched(
+            l.dr_moe_decode_static(gq, gs, dq, ds, sgq, sgs, sdq, sds, dx.at(0), didx.at(0), dw.at(0), dsg.at(0), dx.at(0),
+                                   dx.at(0), 2048, 512, 8, dev.post_norm.at(0), 1e-6, NULL, 0, st.raw), "moe_decode_static in place")
+        c = dx.download(np.float32, 2048, st)
+        assert np.array_equal(a, c), f"call {call}, x == res == y: max difference {np.abs(a - c).max()}"
     # a shape whose scratch would not fit the built-in array is refused, not truncated
     assert l.dr_moe_decode_static(gq, gs, dq, ds, sgq, sgs, sdq, sds, dx.at(0), didx.at(0), dw.at(0), dsg.at(0), dx.at(0),
                                   y_new.at(0), 2048, 1024, 8, dev.post_norm.at(0), 1e-6, NULL, 0, st.raw) == -1
