@@ -512,12 +512,8 @@ static inline cudaError_t drb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 b
 // dr_malloc, dr_cublas_create, dr_sample_init) or lazily by the first launcher call on a stream that
 // is not capturing; a first call inside a capture finds ready == false and the launcher returns -2.
 struct DrbDevice {
-  int sms;              // blocks of a persistent grid (multiprocessors, or the DRB_SMS override)
+  int sms;              // blocks of a persistent grid: the multiprocessor count
   bool pdl;             // programmatic dependent launch enabled (DRB_PDL=0 turns it off)
   bool ready;           // attributes set
-  bool prefill_mma;     // dr_moe_prefill on tcgen05 (DRB_PREFILL=simt selects the CUDA-core kernels)
-  bool router_cluster;  // decode router as one 8-block cluster (DRB_ROUTER=grid selects the multi-block variant)
-  bool down_warmup;     // gate/up warms the down projection's rows into L2 (off; DRB_DOWN_WARMUP=1 turns it on)
-  unsigned* grid_sync;  // zeroed words used by grid-wide barriers
 };
 const DrbDevice& drb_device(cudaStream_t st);

@@ -599,7 +599,7 @@ extern "C" int dr_moe_decode(const uint8_t* gu_q, const __half2* gu_sm, const ui
   const int g_gu = moe::gu::GRID;
   const int g_dn = dev.sms > moe::dn::MIN_GRID ? dev.sms : moe::dn::MIN_GRID;
   drb_launch(moe::gu::k_moe_gate_up<false>, dim3(g_gu), dim3(moe::gu::THREADS), moe::gu::SMEM_BYTES, st, dev.pdl, gu_q, gu_sm,
-             sgu_q, sgu_s, x, idx, reinterpret_cast<unsigned char*>(act), nw, eps, (float*)nullptr, 0, dev.down_warmup ? d_q : nullptr, d_sm, sd_q,
+             sgu_q, sgu_s, x, idx, reinterpret_cast<unsigned char*>(act), nw, eps, (float*)nullptr, 0, (const uint8_t*)nullptr, d_sm, sd_q,
              (const char*)nullptr, (size_t)0);
   drb_launch(moe::dn::k_moe_down<false>, dim3(g_dn), dim3(moe::dn::THREADS), moe::dn::SMEM_BYTES, st, dev.pdl, d_q, d_sm, sd_q,
              sd_s, reinterpret_cast<const unsigned char*>(act), idx, wts, sgate, res, y, pf, pf_bytes, moe::dn::Chain{});
@@ -633,7 +633,7 @@ extern "C" int drb_moe_decode_chained(const uint8_t* gu_q, const __half2* gu_sm,
   const int g_dn = moe::dn::MIN_GRID;  // 16 rows per block: the block's columns of a router row are 32 aligned bytes
   drb_launch(moe::gu::k_moe_gate_up<true>, dim3(g_gu), dim3(moe::gu::THREADS), moe::gu::SMEM_BYTES, st, dev.pdl, gu_q, gu_sm,
              sgu_q, sgu_s, x, (const int*)idx, reinterpret_cast<unsigned char*>(act), nw, eps, workspace, have_prev,
-             dev.down_warmup ? d_q : nullptr, d_sm, sd_q, reinterpret_cast<const char*>(next_router),
+             (const uint8_t*)nullptr, d_sm, sd_q, reinterpret_cast<const char*>(next_router),
              next_router ? (size_t)(e_next + 1) * moe::H * 2 : (size_t)0);
   drb_launch(moe::dn::k_moe_down<true>, dim3(g_dn), dim3(moe::dn::THREADS), moe::dn::SMEM_BYTES, st, dev.pdl, d_q, d_sm, sd_q,
              sd_s, reinterpret_cast<const unsigned char*>(act), (const int*)idx, (const float*)wts, (const float*)sgate, res, y,

@@ -1,6 +1,6 @@
-// Prefill-side kernels of the MoE path: per-row routing bookkeeping (count / permute / combine),
-// the expert-grouped int4 "GEMM" (dr_moe_prefill), and the elementwise helpers the reference's
-// prefill calls around cuBLAS (dequant_q8, f32_to_bf16, swiglu_rows, rmsnorm).
+// Prefill-side kernels of the MoE path: per-row routing bookkeeping (count / permute / combine and the fused
+// grouping step), the launchers of the expert-grouped GEMMs (moe_prefill_mma.cuh), and the elementwise helpers the
+// reference's prefill calls around cuBLAS (dequant_q8, f32_to_bf16, swiglu_rows, rmsnorm).
 //
 // Replaces kernels/drama.cu:744-968 and 1114-1202 of the reference, same C signatures
 // (src/ffi.rs:61-77).
@@ -15,28 +15,112 @@ constexpr int H = 2048, I = 512;
 // ------------------------------------------------------------------------------------------
 // bookkeeping
 
-__global__ void k_count(const int* __restrict__ idx, int n, int* __restrict__ counts) {
+// Histogram of the chosen experts. Each block counts its 1024 pairs in shared memory and adds only its non-empty
+// bins to the global counts: a few hundred global atomics per block instead of one per pair on a handful of hot
+// addresses (with Zipf routing a fifth of all pairs name the same expert).
+constexpr int CNT_BINS = 1024;
+__global__ void __launch_bounds__(256) k_count(const int* __restrict__ idx, int n, int* __restrict__ counts) {
   pdl_wait();
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) atomicAdd(counts + idx[i], 1);
+  __shared__ int bins[CNT_BINS];
+  for (int i = threadIdx.x; i < CNT_BINS; i += blockDim.x) bins[i] = 0;
+  __syncthreads();
+  const int base = blockIdx.x * 1024;
+  int big[4], nbig = 0;  // experts beyond the shared bins go straight to global memory
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = base + j * 256 + threadIdx.x;
+    if (i < n) {
+      const int e = __ldg(idx + i);
+      if (e < CNT_BINS) atomicAdd(&bins[e], 1);
+      else big[nbig++] = e;
+    }
+  }
+  for (int j = 0; j < nbig; ++j) atomicAdd(counts + big[j], 1);
+  __syncthreads();
+  for (int i = threadIdx.x; i < CNT_BINS; i += blockDim.x)
+    if (bins[i]) atomicAdd(counts + i, bins[i]);
 }
 
-// One block per (row, k) pair: claim the next slot of the pair's expert, remember it, copy the row.
-__global__ void __launch_bounds__(128)
-    k_permute(const int* __restrict__ idx, int topk, const int* __restrict__ offsets, int* __restrict__ fill,
+// One warp per (row, k) pair: lane 0 claims the next slot of the pair's expert, the warp copies the row with
+// 16-byte accesses. Eight pairs per block.
+__global__ void __launch_bounds__(256)
+    k_permute(const int* __restrict__ idx, int pairs, int topk, const int* __restrict__ offsets, int* __restrict__ fill,
               int* __restrict__ slot_of, const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ xp, int Hd) {
   pdl_wait();
-  const int i = blockIdx.x;
-  __shared__ int slot;
-  if (threadIdx.x == 0) {
-    const int e = idx[i];
-    slot = offsets[e] + atomicAdd(fill + e, 1);
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (i >= pairs) return;
+  int slot = 0;
+  if (lane == 0) {
+    const int e = __ldg(idx + i);
+    slot = __ldg(offsets + e) + atomicAdd(fill + e, 1);
     slot_of[i] = slot;
   }
-  __syncthreads();
+  slot = __shfl_sync(0xffffffffu, slot, 0);
   const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(i / topk) * Hd);
   uint4* dst = reinterpret_cast<uint4*>(xp + (size_t)slot * Hd);
-  for (int c = threadIdx.x; c < Hd / 8; c += blockDim.x) dst[c] = src[c];
+  for (int c = lane; c < Hd / 8; c += 32) dst[c] = __ldg(src + c);
+}
+
+// Count, scan and slot assignment in ONE launch of one block (drb_moe_group): what the reference does with a count
+// kernel, a download, a host scan, an upload, a memset and the permute kernel's atomics (src/engine.rs:565-580).
+// counts[e], offsets[e] (exclusive scan), slot_of[pair] = offsets[e] + rank of the pair among its expert's pairs,
+// row_of[slot] = pair / topk. The grouped GEMM reads its operand rows through row_of, so no permuted copy of the
+// rows is ever written. e_lo / e_n restrict the grouping to experts [e_lo, e_lo + e_n) (an expert-parallel rank's
+// slice; pairs of other experts get slot -1); local expert ids are e - e_lo.
+constexpr int GRP_THREADS = 1024, GRP_MAX_E = 1024;
+__global__ void __launch_bounds__(GRP_THREADS)
+    k_group(const int* __restrict__ idx, int pairs, int topk, int e_lo, int e_n, int* __restrict__ counts,
+            int* __restrict__ offsets, int* __restrict__ slot_of, int* __restrict__ row_of) {
+  pdl_wait();
+  __shared__ int cnt[GRP_MAX_E];
+  __shared__ int offs[GRP_MAX_E];
+  __shared__ int warp_tot[GRP_THREADS / 32];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  for (int i = t; i < e_n; i += GRP_THREADS) cnt[i] = 0;
+  __syncthreads();
+  // rank of every pair among its expert's pairs (the order inside an expert is arbitrary: every slot is computed
+  // independently and the combine step sums in a fixed order)
+  for (int p = t; p < pairs; p += GRP_THREADS) {
+    const int e = __ldg(idx + p) - e_lo;
+    slot_of[p] = (e >= 0 && e < e_n) ? atomicAdd(&cnt[e], 1) : -1;
+  }
+  __syncthreads();
+  // exclusive scan of the counts: one value per thread (e_n <= 1024)
+  const int c = t < e_n ? cnt[t] : 0;
+  int incl = c;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int v = warp_tot[lane], in2 = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, in2, o);
+      if (lane >= o) in2 += u;
+    }
+    warp_tot[lane] = in2 - v;  // exclusive over the warps
+  }
+  __syncthreads();
+  if (t < e_n) {
+    const int o = warp_tot[warp] + incl - c;
+    offs[t] = o;
+    counts[t] = c;
+    offsets[t] = o;
+  }
+  __syncthreads();
+  for (int p = t; p < pairs; p += GRP_THREADS) {
+    const int e = __ldg(idx + p) - e_lo;
+    if (e >= 0 && e < e_n) {
+      const int slot = offs[e] + slot_of[p];
+      slot_of[p] = slot;
+      row_of[slot] = p / topk;
+    }
+  }
 }
 
 // x[r] += sigmoid(sgate[r]) * shared[r] + sum_k w[r,k] * Y[slot_of[r,k]], k ascending (fixed order, so
@@ -60,116 +144,6 @@ __global__ void __launch_bounds__(256)
     float4 o = *xo;
     o.x += acc.x, o.y += acc.y, o.z += acc.z, o.w += acc.w;
     *xo = o;
-  }
-}
-
-// ------------------------------------------------------------------------------------------
-// expert-grouped int4 contraction on CUDA cores.
-//
-// Rows of xp are sorted by expert. A block owns 16 (gate, up) row pairs (gate/up kernel) or 32 output
-// rows (down kernel) of one expert, keeps those weight rows packed in registers for its whole
-// life, and walks the expert's tokens; the weights are read from memory once per block.
-// The intermediate is kept in fp16 (the buffer is 16 bits per element by the ABI; fp16 carries three
-// more mantissa bits than bf16 at these magnitudes, which the 1e-3 output tolerance needs).
-
-__global__ void __launch_bounds__(256)
-    k_pf_gate_up(const uint8_t* __restrict__ Q, const __half2* __restrict__ SM, const __nv_bfloat16* __restrict__ xp,
-                 const int* __restrict__ offsets, const int* __restrict__ counts, __half* __restrict__ act) {
-  pdl_wait();
-  const int e = blockIdx.x;
-  const int cnt = counts[e];
-  if (cnt == 0) return;
-  const int off = offsets[e];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int j0 = (blockIdx.y * 8 + warp) * 2;
-  const uint8_t* q = Q + (size_t)e * (2 * I) * (H / 2);
-  const __half2* sm = SM + (size_t)e * (2 * I) * (H / 64);
-  // rows: r = 0,1 -> gate j0, j0+1 ; r = 2,3 -> up j0, j0+1. Chunks lane and lane+32 of each.
-  uint4 w[4][2];
-  float2 s[4][2];
-#pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    const size_t row = (size_t)(r >> 1) * I + j0 + (r & 1);
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      w[r][h] = __ldg(reinterpret_cast<const uint4*>(q + row * (H / 2)) + lane + 32 * h);
-      s[r][h] = __half22float2(sm[row * (H / 64) + 16 * h + (lane >> 1)]);
-    }
-  }
-  for (int t = 0; t < cnt; ++t) {
-    const __nv_bfloat16* xr = xp + (size_t)(off + t) * H;
-    unsigned long long xv[32];
-    float X[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      float sum = 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(xr + h * 1024 + 32 * lane) + c);
-        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float a = __uint_as_float(u[i] << 16), b = __uint_as_float(u[i] & 0xffff0000u);
-          xv[h * 16 + c * 4 + i] = pack2(a, b);
-          sum += a + b;
-        }
-      }
-      X[h] = sum;
-    }
-    float d[4];
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      d[r] = s[r][0].x * dot32_q4(w[r][0], xv) + (s[r][0].y - 16.f * s[r][0].x) * X[0] +
-             s[r][1].x * dot32_q4(w[r][1], xv + 16) + (s[r][1].y - 16.f * s[r][1].x) * X[1];
-      d[r] = warp_sum(d[r]);
-    }
-    if (lane < 2) act[(size_t)(off + t) * I + j0 + lane] = __float2half_rn(silu_f(lane ? d[1] : d[0]) * (lane ? d[3] : d[2]));
-  }
-}
-
-__global__ void __launch_bounds__(256)
-    k_pf_down(const uint8_t* __restrict__ Q, const __half2* __restrict__ SM, const __half* __restrict__ act,
-              const int* __restrict__ offsets, const int* __restrict__ counts, float* __restrict__ y) {
-  pdl_wait();
-  const int e = blockIdx.x;
-  const int cnt = counts[e];
-  if (cnt == 0) return;
-  const int off = offsets[e];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int cc = lane & 15, half = lane >> 4;
-  const int n0 = (blockIdx.y * 8 + warp) * 4;
-  const uint8_t* q = Q + (size_t)e * H * (I / 2);
-  const __half2* sm = SM + (size_t)e * H * (I / 64);
-  uint4 w[2];
-  float2 s[2];
-#pragma unroll
-  for (int p = 0; p < 2; ++p) {
-    const size_t row = n0 + 2 * p + half;
-    w[p] = __ldg(reinterpret_cast<const uint4*>(q + row * (I / 2)) + cc);
-    s[p] = __half22float2(sm[row * (I / 64) + (cc >> 1)]);
-  }
-  for (int t = 0; t < cnt; ++t) {
-    const __half* ar = act + (size_t)(off + t) * I + 32 * cc;
-    unsigned long long av[16];
-    float A = 0.f;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(ar) + c);
-      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u[i]));
-        av[c * 4 + i] = pack2(f.x, f.y);
-        A += f.x + f.y;
-      }
-    }
-#pragma unroll
-    for (int p = 0; p < 2; ++p) {
-      float v = s[p].x * dot32_q4(w[p], av) + (s[p].y - 16.f * s[p].x) * A;
-#pragma unroll
-      for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      if (cc == 0) y[(size_t)(off + t) * H + n0 + 2 * p + half] = v;
-    }
   }
 }
 
@@ -207,7 +181,8 @@ __global__ void k_swiglu_rows(const float* __restrict__ h, __nv_bfloat16* __rest
   y[i] = __float2bfloat16(silu_f(h[r * 2 * Id + j]) * h[r * 2 * Id + Id + j]);
 }
 
-// Row-wise RMSNorm ("+1" already folded into w). Writes f32 and/or bf16.
+// Row-wise RMSNorm ("+1" already folded into w). Writes f32 and/or a 16-bit copy: bf16, or (F16) fp16 clamped to its range.
+template <bool F16>
 __global__ void __launch_bounds__(256)
     k_rmsnorm(const float* __restrict__ x, const float* __restrict__ w, float* y, __nv_bfloat16* yb, int D, float eps) {
   pdl_wait();
@@ -228,7 +203,10 @@ __global__ void __launch_bounds__(256)
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     const float v = xr[i] * inv * w[i];
     if (y) y[(size_t)blockIdx.x * D + i] = v;
-    if (yb) yb[(size_t)blockIdx.x * D + i] = __float2bfloat16(v);
+    if (yb) {
+      if (F16) reinterpret_cast<__half*>(yb)[(size_t)blockIdx.x * D + i] = pfmma::f2h_sat(v);
+      else yb[(size_t)blockIdx.x * D + i] = __float2bfloat16(v);
+    }
   }
 }
 
@@ -238,7 +216,9 @@ __global__ void __launch_bounds__(256)
 // logits of the same row differ by 1.2e-6 between a batch of 300 and a batch of 38), which would let the routing of
 // a row depend on how the rows are spread over the GPUs. Block (x, y) = RB rows x the outputs y, y + gridDim.y, ...;
 // its warp w takes every 8th of those. The split over y only adds parallelism: it does not change any sum.
+// F16: the rows are fp16 instead of bf16 (the weights are bf16 either way).
 constexpr int RL_RB = 4, RL_K = 2048, RL_SPLIT = 9;
+template <bool F16>
 __global__ void __launch_bounds__(256)
     k_router_logits(const __nv_bfloat16* __restrict__ xb, const __nv_bfloat16* __restrict__ w, float* __restrict__ logits,
                     int rows, int e1, float beta) {
@@ -272,8 +252,15 @@ __global__ void __launch_bounds__(256)
         const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-          acc[r] = fmaf(__uint_as_float(ww[t] << 16), __uint_as_float(xw[t] << 16), acc[r]);
-          acc[r] = fmaf(__uint_as_float(ww[t] & 0xffff0000u), __uint_as_float(xw[t] & 0xffff0000u), acc[r]);
+          float x0, x1;
+          if (F16) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xw[t]));
+            x0 = f.x, x1 = f.y;
+          } else {
+            x0 = __uint_as_float(xw[t] << 16), x1 = __uint_as_float(xw[t] & 0xffff0000u);
+          }
+          acc[r] = fmaf(__uint_as_float(ww[t] << 16), x0, acc[r]);
+          acc[r] = fmaf(__uint_as_float(ww[t] & 0xffff0000u), x1, acc[r]);
         }
       }
     }
@@ -320,16 +307,17 @@ __global__ void __launch_bounds__(256) k_offsets(const int* __restrict__ counts,
 static cudaError_t configure_all() {
   cudaError_t e;
   if ((e = drb_carveout(k_offsets)) != cudaSuccess) return e;
-  if ((e = drb_carveout(k_router_logits)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_router_logits<false>)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_router_logits<true>)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_count)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_permute)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_combine)) != cudaSuccess) return e;
-  if ((e = drb_carveout(k_pf_gate_up)) != cudaSuccess) return e;
-  if ((e = drb_carveout(k_pf_down)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_group)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_dequant_q8)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_f32_to_bf16)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_swiglu_rows)) != cudaSuccess) return e;
-  return drb_carveout(k_rmsnorm);
+  if ((e = drb_carveout(k_rmsnorm<true>)) != cudaSuccess) return e;
+  return drb_carveout(k_rmsnorm<false>);
 }
 
 }  // namespace pf
@@ -337,7 +325,7 @@ static cudaError_t configure_all() {
 // Reference: kernels/drama.cu:750-753; src/ffi.rs:65. counts must be zeroed by the caller.
 extern "C" int dr_moe_count(const int* idx, int n, int* counts, cudaStream_t st) {
   if (n <= 0) return 0;
-  pf::k_count<<<(n + 255) / 256, 256, 0, st>>>(idx, n, counts);
+  pf::k_count<<<(n + 1023) / 1024, 256, 0, st>>>(idx, n, counts);
   return 0;
 }
 
@@ -356,7 +344,25 @@ extern "C" int drb_router_logits(const __nv_bfloat16* xb, const __nv_bfloat16* w
                                  float beta, cudaStream_t st) {
   if (h != pf::RL_K) return -1;
   if (rows <= 0 || e1 <= 0) return 0;
-  pf::k_router_logits<<<dim3((rows + pf::RL_RB - 1) / pf::RL_RB, pf::RL_SPLIT), 256, 0, st>>>(xb, w, logits, rows, e1, beta);
+  pf::k_router_logits<false><<<dim3((rows + pf::RL_RB - 1) / pf::RL_RB, pf::RL_SPLIT), 256, 0, st>>>(xb, w, logits, rows, e1, beta);
+  return 0;
+}
+
+// The two calls above for rows kept in fp16 (no counterpart in the reference, whose prefill rounds the normalised rows
+// to bf16: src/engine.rs:499): drb_rmsnorm_f16 writes the normalised rows as fp16 (clamped to +-65504),
+// drb_router_logits_f16 reads them. With drb_moe_prefill_block(x_f16 = 1) the whole block then works on rows with
+// eleven significant bits instead of eight.
+extern "C" int drb_rmsnorm_f16(const float* x, const float* w, __half* yh, int rows, int D, float eps, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  pf::k_rmsnorm<true><<<rows, 256, 0, st>>>(x, w, nullptr, reinterpret_cast<__nv_bfloat16*>(yh), D, eps);
+  return 0;
+}
+extern "C" int drb_router_logits_f16(const __half* xh, const __nv_bfloat16* w, float* logits, int rows, int e1, int h, float beta,
+                                     cudaStream_t st) {
+  if (h != pf::RL_K) return -1;
+  if (rows <= 0 || e1 <= 0) return 0;
+  pf::k_router_logits<true><<<dim3((rows + pf::RL_RB - 1) / pf::RL_RB, pf::RL_SPLIT), 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(xh), w, logits, rows, e1, beta);
   return 0;
 }
 
@@ -365,7 +371,7 @@ extern "C" int dr_moe_permute(const int* idx, int rows, int topk, const int* off
                               const __nv_bfloat16* x, __nv_bfloat16* xp, int H, cudaStream_t st) {
   if (H % 8 != 0) return -1;
   if (rows * topk <= 0) return 0;
-  pf::k_permute<<<rows * topk, 128, 0, st>>>(idx, topk, offsets, fill, slot_of, x, xp, H);
+  pf::k_permute<<<(rows * topk + 7) / 8, 256, 0, st>>>(idx, rows * topk, topk, offsets, fill, slot_of, x, xp, H);
   return 0;
 }
 
@@ -378,7 +384,8 @@ extern "C" int dr_moe_combine(float* x, const float* Y, const int* slot_of, cons
   return 0;
 }
 
-// act: scratch of 16 bits per (slot, j); this implementation keeps the SwiGLU intermediate there as fp16.
+// act: scratch of 16 bits per (slot, j); this implementation keeps the SwiGLU intermediate there as fp16
+// (values beyond +-65504 are clamped to that range).
 // Reference: kernels/drama.cu:961-968; src/ffi.rs:61-64. H = 2048 and I = 512 only, else -1.
 extern "C" int dr_moe_prefill(const uint8_t* gu_q, const __half2* gu_sm, const uint8_t* d_q, const __half2* d_sm,
                               const __nv_bfloat16* xp, const int* offsets, const int* counts, __nv_bfloat16* act, float* y,
@@ -387,22 +394,52 @@ extern "C" int dr_moe_prefill(const uint8_t* gu_q, const __half2* gu_sm, const u
   if (E <= 0) return 0;
   const DrbDevice& dev = drb_device(st);
   if (!dev.ready) return -2;
-  if (dev.prefill_mma) {
-    // tensor-core path: two persistent grouped GEMMs (moe_prefill_mma.cuh)
-    drb_launch(pfmma::k_grouped<0, 0>, dim3(pfmma::BLOCKS_PER_SM * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, gu_q, (const void*)gu_sm,
-               (const void*)xp, (void*)act, offsets, counts, E);
-    drb_launch(pfmma::k_grouped<1, 0>, dim3(pfmma::BLOCKS_PER_SM * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, d_q, (const void*)d_sm,
-               (const void*)act, (void*)y, offsets, counts, E);
-    return 0;
-  }
-  pf::k_pf_gate_up<<<dim3(E, I / 16), 256, 0, st>>>(gu_q, gu_sm, xp, offsets, counts, reinterpret_cast<__half*>(act));
-  pf::k_pf_down<<<dim3(E, H / 32), 256, 0, st>>>(d_q, d_sm, reinterpret_cast<const __half*>(act), offsets, counts, y);
+  const dim3 grid(pfmma::BLOCKS_PER_SM * dev.sms), block(pfmma::THREADS);
+  drb_launch(pfmma::k_grouped<0, 0, false>, grid, block, pfmma::SMEM_BYTES, st, false, gu_q, (const void*)gu_sm, (const void*)xp,
+             (void*)act, offsets, counts, E, pfmma::SharedExpert{}, (const int*)nullptr, 0);
+  drb_launch(pfmma::k_grouped<1, 0, false>, grid, block, pfmma::SMEM_BYTES, st, false, d_q, (const void*)d_sm, (const void*)act,
+             (void*)y, offsets, counts, E, pfmma::SharedExpert{}, (const int*)nullptr, 0);
   return 0;
 }
 
-// The same grouped GEMMs over block-FP8 experts (layouts as dr_moe_decode_fp8). Tensor-core path only: there is no
-// CUDA-core variant of it, so DRB_PREFILL=simt makes this call return -1.
-// Reference: kernels/drama.cu:971-1109; src/ffi.rs:52-55. H = 2048 and I = 512 only, else -1.
+// No counterpart in the reference. Count, exclusive scan and slot assignment of the (row, k) pairs in one launch:
+// counts[e_n], offsets[e_n], slot_of[rows * topk] (-1 for pairs whose expert lies outside [e_lo, e_lo + e_n)),
+// row_of[slot] = row. Replaces dr_moe_count + the host scan + dr_moe_permute of src/engine.rs:565-580 when the
+// grouped GEMM is drb_moe_prefill_block, which reads its rows through row_of. e_n <= 1024, else -1.
+extern "C" int drb_moe_group(const int* idx, int rows, int topk, int e_lo, int e_n, int* counts, int* offsets, int* slot_of,
+                             int* row_of, cudaStream_t st) {
+  if (e_n <= 0 || e_n > pf::GRP_MAX_E || topk <= 0) return -1;
+  drb_launch(pf::k_group, dim3(1), dim3(pf::GRP_THREADS), 0, st, false, idx, rows * topk, topk, e_lo, e_n, counts, offsets,
+             slot_of, row_of);
+  return 0;
+}
+
+// No counterpart in the reference. The routed experts AND the int8 shared expert of one prefill block in two
+// launches: dr_moe_prefill with (a) the operand rows read in place through row_of (xb holds the normalised rows in row
+// order, [rows, H], bf16 or with x_f16 != 0 fp16; nothing is permuted) and (b) the shared expert as one more expert that owns every row, its
+// int8 weights dequantised into the same tensor-core tiles (sh_act: fp16 scratch [rows, I]; sh_out: f32 [rows, H]).
+// The reference runs the shared expert through cuBLAS on weights dequantised to bf16 (src/engine.rs:351-355, 560-562);
+// here no library GEMM and no bf16 copy of the weights is involved. rows_sh = 0 skips the shared expert. Limits as dr_moe_prefill.
+extern "C" int drb_moe_prefill_block(const uint8_t* gu_q, const __half2* gu_sm, const uint8_t* d_q, const __half2* d_sm,
+                                     const int8_t* sgu_q, const __half* sgu_s, const int8_t* sd_q, const __half* sd_s,
+                                     const __nv_bfloat16* xb, const int* row_of, const int* offsets, const int* counts,
+                                     __nv_bfloat16* act, float* y, __nv_bfloat16* sh_act, float* sh_out, int rows_sh, int E,
+                                     int H, int I, int x_f16, cudaStream_t st) {
+  if (H != pf::H || I != pf::I) return -1;
+  if (E <= 0 && rows_sh <= 0) return 0;
+  const DrbDevice& dev = drb_device(st);
+  if (!dev.ready) return -2;
+  const dim3 grid(pfmma::BLOCKS_PER_SM * dev.sms), block(pfmma::THREADS);
+  const pfmma::SharedExpert s0{sgu_q, sgu_s, (const void*)xb, (void*)sh_act, rows_sh};
+  const pfmma::SharedExpert s1{sd_q, sd_s, (const void*)sh_act, (void*)sh_out, rows_sh};
+  drb_launch(pfmma::k_grouped<0, 0, true>, grid, block, pfmma::SMEM_BYTES, st, false, gu_q, (const void*)gu_sm, (const void*)xb,
+             (void*)act, offsets, counts, E, s0, row_of, x_f16);
+  drb_launch(pfmma::k_grouped<1, 0, true>, grid, block, pfmma::SMEM_BYTES, st, false, d_q, (const void*)d_sm, (const void*)act,
+             (void*)y, offsets, counts, E, s1, (const int*)nullptr, 1);
+  return 0;
+}
+
+// dr_moe_prefill over block-FP8 experts (include/dramakernels.h). Reference: kernels/drama.cu:971-1109; src/ffi.rs:52-55.
 extern "C" int dr_moe_prefill_fp8(const uint8_t* gu_w, const float* gu_s, const uint8_t* d_w, const float* d_s,
                                   const __nv_bfloat16* xp, const int* offsets, const int* counts, __nv_bfloat16* act, float* y,
                                   int E, int H, int I, cudaStream_t st) {
@@ -410,11 +447,11 @@ extern "C" int dr_moe_prefill_fp8(const uint8_t* gu_w, const float* gu_s, const 
   if (E <= 0) return 0;
   const DrbDevice& dev = drb_device(st);
   if (!dev.ready) return -2;
-  if (!dev.prefill_mma) return -1;
-  drb_launch(pfmma::k_grouped<0, 1>, dim3(pfmma::BLOCKS_PER_SM * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, gu_w, (const void*)gu_s,
-             (const void*)xp, (void*)act, offsets, counts, E);
-  drb_launch(pfmma::k_grouped<1, 1>, dim3(pfmma::BLOCKS_PER_SM * dev.sms), dim3(pfmma::THREADS), pfmma::SMEM_BYTES, st, false, d_w, (const void*)d_s,
-             (const void*)act, (void*)y, offsets, counts, E);
+  const dim3 grid(pfmma::BLOCKS_PER_SM * dev.sms), block(pfmma::THREADS);
+  drb_launch(pfmma::k_grouped<0, 1, false>, grid, block, pfmma::SMEM_BYTES, st, false, gu_w, (const void*)gu_s, (const void*)xp,
+             (void*)act, offsets, counts, E, pfmma::SharedExpert{}, (const int*)nullptr, 0);
+  drb_launch(pfmma::k_grouped<1, 1, false>, grid, block, pfmma::SMEM_BYTES, st, false, d_w, (const void*)d_s, (const void*)act,
+             (void*)y, offsets, counts, E, pfmma::SharedExpert{}, (const int*)nullptr, 0);
   return 0;
 }
 
@@ -446,6 +483,6 @@ extern "C" int dr_swiglu_rows(const float* h, __nv_bfloat16* y, int rows, int I,
 extern "C" int dr_rmsnorm(const float* x, const float* w, float* y, __nv_bfloat16* yb, int rows, int D, float eps,
                           cudaStream_t st) {
   if (rows <= 0) return 0;
-  pf::k_rmsnorm<<<rows, 256, 0, st>>>(x, w, y, yb, D, eps);
+  pf::k_rmsnorm<false><<<rows, 256, 0, st>>>(x, w, y, yb, D, eps);
   return 0;
 }

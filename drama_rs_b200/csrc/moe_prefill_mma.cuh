@@ -29,34 +29,25 @@
 namespace pfmma {
 
 constexpr int H = 2048, I = 512;
-#ifndef DRB_PF_PW
-#define DRB_PF_PW 8
-#endif
-constexpr int PRODUCER_WARPS = DRB_PF_PW;           // 8: two blocks per multiprocessor; 16: one block with twice the ring
-constexpr int BLOCKS_PER_SM = 16 / PRODUCER_WARPS;   // 4, 2 or 1
+constexpr int PRODUCER_WARPS = 8;                   // two blocks per multiprocessor
+constexpr int BLOCKS_PER_SM = 16 / PRODUCER_WARPS;
 constexpr int PRODUCERS = PRODUCER_WARPS * 32;
 constexpr int THREADS = PRODUCERS + 32;             // + the MMA-issuing warp
 constexpr int TILE_M = 128;
 constexpr int KC = 64;                              // K chunk = one swizzle atom of fp16 = one int4 scale group
-#ifndef DRB_PF_MAXN
-#define DRB_PF_MAXN 64
-#endif
-#ifndef DRB_PF_STAGES
-#define DRB_PF_STAGES 4
-#endif
-constexpr int MAX_N = DRB_PF_MAXN;                  // tokens per accumulator (one work item)
+constexpr int MAX_N = 64;                           // tokens per accumulator (one work item)
 constexpr int NG = 4;                               // token groups enumerated per expert; the last one loops on
 constexpr int A_BYTES = TILE_M * KC * 2;            // 16 KB
 constexpr int B_BYTES = MAX_N * KC * 2;             // 16 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;      // 24 KB; four stages: two blocks fit a multiprocessor
-constexpr int STAGES = DRB_PF_STAGES;
+constexpr int STAGES = 4;
 constexpr int CTL_BYTES = 1024;
 constexpr size_t SMEM_BYTES = CTL_BYTES + 1024 /* alignment slack */ + (size_t)STAGES * STAGE_BYTES;  // 98 KB
 constexpr int TMEM_COLS = MAX_N;
 constexpr int BPT = MAX_N * 8 / PRODUCERS;             // 16-byte B chunks per thread and K chunk
-constexpr int SPLIT = PRODUCERS / TILE_M;              // threads per tile row: 1, 2 or 4
-constexpr int NST = 8 / SPLIT;                         // 16-byte operand chunks a thread writes per K chunk: 8, 4 or 2
-static_assert(BPT >= 1 && (SPLIT == 1 || SPLIT == 2 || SPLIT == 4), "operand mapping");
+constexpr int SPLIT = PRODUCERS / TILE_M;              // threads per tile row: 2
+constexpr int NST = 8 / SPLIT;                         // 16-byte operand chunks a thread writes per K chunk: 4
+static_assert(BPT >= 1 && SPLIT == 2, "operand mapping");
 
 struct Ctl {
   uint64_t full[STAGES];   // a stage has been filled (one arrival per producer warp)
@@ -161,17 +152,46 @@ DRB_DEV float pow2_normaliser(float s) {
   return __uint_as_float((uint32_t)(254 - (e ? e : 1)) << 23);
 }
 
+// Two floats -> packed fp16 (lo, hi), round to nearest, clamped to the largest finite fp16: the operands of the
+// tensor-core path are fp16, whose range ends at 65504 where bf16 and fp32 carry on. An outlier beyond it then
+// degrades (it is clamped) instead of turning a token's whole output row into NaN through an infinity.
+DRB_DEV uint32_t f2h2_sat(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+DRB_DEV __half f2h_sat(float v) {
+  unsigned short h;
+  asm("cvt.rn.satfinite.f16.f32 %0, %1;" : "=h"(h) : "f"(v));
+  return __ushort_as_half(h);
+}
+
 // Eight bf16 activations (k ascending) -> fp16 in k order.
 DRB_DEV uint4 bf16x8_to_f16_nat(const uint4& v) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
   uint4 o;
   uint32_t* op = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __half2 h = __floats2half2_rn(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
-    op[i] = *reinterpret_cast<const uint32_t*>(&h);
-  }
+  for (int i = 0; i < 4; ++i) op[i] = f2h2_sat(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
   return o;
+}
+
+// Sixteen int8 weights (k ascending) times one fp16 scale -> sixteen fp16 in k order. 0x6400 | (b ^ 0x80) is the
+// half 1024 + 128 + b; subtracting 1152 is exact, the product rounds once.
+DRB_DEV void dequant16_i8(const uint4& v, __half2 s2, uint4& lo, uint4& hi) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  const __half2 k1152 = __half2half2(__ushort_as_half((unsigned short)0x6480));
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t u = w[i] ^ 0x80808080u;
+    const uint32_t a = prmt(u, 0x64646464u, 0x4140u), b = prmt(u, 0x64646464u, 0x4342u);
+    const __half2 pa = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&a), k1152), s2);
+    const __half2 pb = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&b), k1152), s2);
+    o[2 * i] = *reinterpret_cast<const uint32_t*>(&pa), o[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&pb);
+  }
+  lo = make_uint4(o[0], o[1], o[2], o[3]);
+  hi = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
 // Eight bf16 activations (k ascending) -> fp16 in the same (0,4,1,5,2,6,3,7) order.
@@ -183,10 +203,7 @@ DRB_DEV uint4 bf16x8_to_f16_perm(const uint4& v) {
   uint4 o;
   uint32_t* op = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __half2 h = __floats2half2_rn(f[i], f[i + 4]);
-    op[i] = *reinterpret_cast<const uint32_t*>(&h);
-  }
+  for (int i = 0; i < 4; ++i) op[i] = f2h2_sat(f[i], f[i + 4]);
   return o;
 }
 
@@ -201,19 +218,31 @@ DRB_DEV uint4 f16x8_perm(const uint4& v) {
 }
 
 
+// The int8 shared expert, run by the same launch as one more "expert" that owns every row (SH = true). Its work
+// items (one per 64-token group and 128-row tile) come first: they are the largest.
+struct SharedExpert {
+  const int8_t* q;  // gate/up: [2I, H]; down: [H, I]
+  const __half* s;  // one scale per 128 inputs: [rows of q, K / 128]
+  const void* src;  // gate/up: the normalised rows, bf16 [rows, H], in row order; down: fp16 [rows, I]
+  void* dst;        // gate/up: fp16 [rows, I]; down: f32 [rows, H]
+  int rows;
+};
+
 // GEMM = 0: gate/up (+ SwiGLU, fp16 out);  GEMM = 1: down (fp32 out).
 // FMT = 0: int4 experts: Q [E, R, K/2] nibbles, SM [E, R, K/64] (scale, min);  R = 2I, K = H for gate/up;  R = H, K = I for down.
 // FMT = 1: block-FP8 experts: Q [E, R, K] E4M3 bytes, SM = f32 scales [E, R/128, K/128]. A row block's scales are
 //   brought into fp16 range by the power of two that normalises the block's first scale (the weights times the
 //   scaled scale round once to fp16); the epilogue multiplies the row's result by the inverse power, exactly.
-//   src: gate/up: xp bf16 [slots, H];  down: act fp16 [slots, I]
+//   src: gate/up: xp bf16 [slots, H] (or, with row_of, the unpermuted rows [rows, H] and row_of[slot]; fp16 rows when
+//        src_f16 is set: three more significant bits than bf16, which the 1e-3 bar against fp32 rows needs);  down: act fp16 [slots, I]
 //   dst: gate/up: act fp16 [slots, I]; down: y f32 [slots, H]
 // Warps 0-7 convert operands into the stage ring and run the epilogue; warp 8 issues the MMAs. They meet only
 // on mbarriers: full[s] (8 warp arrivals), empty[s] and done (tcgen05.commit), tfree (accumulator drained).
-template <int GEMM, int FMT = 0>
+template <int GEMM, int FMT = 0, bool SH = false>
 __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
     k_grouped(const uint8_t* __restrict__ Q, const void* __restrict__ SMv, const void* __restrict__ src, void* __restrict__ dst,
-              const int* __restrict__ offsets, const int* __restrict__ counts, int E) {
+              const int* __restrict__ offsets, const int* __restrict__ counts, int E, SharedExpert sh,
+              const int* __restrict__ row_of, int src_f16) {
   const __half2* SM = static_cast<const __half2*>(SMv);  // FMT 0
   const float* SF = static_cast<const float*>(SMv);      // FMT 1
   constexpr int K = GEMM == 0 ? H : I;
@@ -247,15 +276,37 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
   unsigned chunk_no = 0;  // chunks so far: selects stage and mbarrier phase (same sequence in every warp)
   unsigned acc_no = 0;    // accumulators so far: phase of `done` and `tfree`
 
+  // Work items, walked in the same order by every warp: the shared expert's (token group, tile) pairs, then the routed
+  // experts' (expert, token group, tile) triples; the last enumerated group of a routed expert also takes whatever
+  // lies beyond NG * MAX_N tokens.
+  const int sh_items = SH ? ((sh.rows + MAX_N - 1) / MAX_N) * MT : 0;
+  const int total_items = sh_items + E * NG * MT;
+  struct Item {
+    bool valid, shared, single;
+    int e, mt, cnt, nfirst;
+  };
+  auto decode = [&](int item) {
+    Item it;
+    it.shared = SH && item < sh_items;
+    if (it.shared) {
+      it.mt = item % MT, it.nfirst = (item / MT) * MAX_N, it.cnt = sh.rows, it.e = 0, it.single = true, it.valid = true;
+    } else {
+      const int i2 = item - sh_items;
+      const int g = (i2 / MT) % NG;
+      it.mt = i2 % MT, it.e = i2 / (MT * NG), it.cnt = counts[it.e], it.nfirst = g * MAX_N, it.single = g != NG - 1;
+      it.valid = it.nfirst < it.cnt;
+    }
+    return it;
+  };
+
   if (warp == PRODUCER_WARPS) {
     // ================= MMA warp =================
-    for (int item = blockIdx.x; item < E * NG * MT; item += gridDim.x) {
-      const int g = (item / MT) % NG, e = item / (MT * NG);
-      const int cnt = counts[e];
-      if (g * MAX_N >= cnt) continue;
-      for (int n0 = g * MAX_N; n0 < cnt; n0 += MAX_N) {
-        if (n0 > g * MAX_N && g != NG - 1) break;
-        const int N = (min(MAX_N, cnt - n0) + 15) & ~15;
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+      const Item it = decode(item);
+      if (!it.valid) continue;
+      for (int n0 = it.nfirst; n0 < it.cnt; n0 += MAX_N) {
+        if (n0 > it.nfirst && it.single) break;
+        const int N = (min(MAX_N, it.cnt - n0) + 15) & ~15;
         const uint32_t idesc = instr_desc(N);
         // the previous accumulator must have been read out
         if (acc_no > 0 && !dead) dead = !mbar_wait(&ctl.tfree, (acc_no - 1) & 1, DRB_ERR_TMEM);
@@ -279,7 +330,7 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
     }
   } else {
     // ================= producer / epilogue warps =================
-    // This thread's share of the A tile: tile row t / 2, 32 of the chunk's 64 nibbles -> four 16-byte chunks.
+    // This thread's share of the A tile: tile row t / 2, 32 of the chunk's 64 weights -> four 16-byte operand chunks.
     const int arow = threadIdx.x / SPLIT, ahalf = threadIdx.x % SPLIT;
     uint32_t a_off[NST];
 #pragma unroll
@@ -290,31 +341,47 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
     for (int i = 0; i < BPT; ++i) b_off[i] = A_BYTES + swz_off((threadIdx.x + i * PRODUCERS) >> 3, threadIdx.x & 7);
     const int q4 = warp & 3;       // tensor-memory lane quarter this warp may read
     const int r = q4 * 32 + lane;  // tile row in the epilogue
+    constexpr int CB_R = FMT == 0 ? KC / 2 : KC;  // bytes of one K chunk of a routed weight row; this thread takes half of them
+    constexpr int CB_S = KC;                      // the same of a shared-expert (int8) row
+    constexpr int NL_R = CB_R / SPLIT / 16, NL_S = CB_S / SPLIT / 16;  // 16-byte pieces this thread loads per chunk: 1 or 2
+    constexpr int NLX = SH ? (NL_S > NL_R ? NL_S : NL_R) : NL_R;
+    static_assert(NL_R >= 1 && NL_S >= 1, "a thread loads whole 16-byte pieces");
 
-    for (int item = blockIdx.x; item < E * NG * MT; item += gridDim.x) {
-      const int mt = item % MT, g = (item / MT) % NG, e = item / (MT * NG);
-      const int cnt = counts[e];
-      if (g * MAX_N >= cnt) continue;
-      const int off = offsets[e];
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+      const Item it = decode(item);
+      if (!it.valid) continue;
+      const bool shd = it.shared;
+      const int mt = it.mt, e = it.e;
+      const int off = shd ? 0 : offsets[e];
       // weight row of tile row r: gate/up interleaves gate j (even r) with up j (odd r)
       const int wrow = GEMM == 0 ? (arow & 1) * I + mt * (TILE_M / 2) + (arow >> 1) : mt * TILE_M + arow;
-      constexpr int CB = FMT == 0 ? KC / 2 : KC;  // bytes of one K chunk of a weight row; this thread takes half of them
-      const uint8_t* qrow = Q + ((size_t)e * R + wrow) * (FMT == 0 ? K / 2 : K) + ahalf * (CB / SPLIT);
+      const int cb = shd ? CB_S : CB_R;
+      const uint8_t* qrow = shd ? reinterpret_cast<const uint8_t*>(sh.q) + (size_t)wrow * K + ahalf * (CB_S / SPLIT)
+                                : Q + ((size_t)e * R + wrow) * (FMT == 0 ? K / 2 : K) + ahalf * (CB_R / SPLIT);
       const __half2* smrow = SM + ((size_t)e * R + wrow) * (K / 64);
       const float* sfrow = SF + ((size_t)e * (R / 128) + (wrow >> 7)) * (K / 128);  // FMT 1: this row block's scales
-      const float norm = FMT == 1 ? pow2_normaliser(__ldg(sfrow)) : 1.f;
+      const __half* ssrow = sh.s + (size_t)wrow * (K / 128);                        // shared expert: this row's scales
+      const float norm = (FMT == 1 && !shd) ? pow2_normaliser(__ldg(sfrow)) : 1.f;
+      const unsigned char* asrc = static_cast<const unsigned char*>(shd ? sh.src : src);
+      void* adst = shd ? sh.dst : dst;
+      const int nl = shd ? NL_S : NL_R;
 
-      // token group g; the last enumerated group also takes whatever lies beyond NG * MAX_N tokens
-      for (int n0 = g * MAX_N; n0 < cnt; n0 += MAX_N) {
-        if (n0 > g * MAX_N && g != NG - 1) break;
-        const int nt = min(MAX_N, cnt - n0);
+      for (int n0 = it.nfirst; n0 < it.cnt; n0 += MAX_N) {
+        if (n0 > it.nfirst && it.single) break;
+        const int nt = min(MAX_N, it.cnt - n0);
         const int N = (nt + 15) & ~15;
         // activation rows of this thread's B chunks (nullptr beyond the group)
         const unsigned char* bsrc[BPT];
 #pragma unroll
         for (int i = 0; i < BPT; ++i) {
           const int n = (threadIdx.x + i * PRODUCERS) >> 3;
-          bsrc[i] = n < nt ? static_cast<const unsigned char*>(src) + ((size_t)(off + n0 + n) * K) * ESZ + (threadIdx.x & 7) * 16 : nullptr;
+          // row_of (gate/up of the routed experts only): slot -> row of src, so that no permuted copy of the rows is needed
+          bsrc[i] = nullptr;
+          if (n < nt) {
+            const int slot = off + n0 + n;
+            const int row = (GEMM == 0 && !shd && row_of) ? __ldg(row_of + slot) : slot;
+            bsrc[i] = asrc + ((size_t)row * K) * ESZ + (threadIdx.x & 7) * 16;
+          }
         }
         auto load_b = [&](int kc, int i) -> uint4 {
           if (!bsrc[i]) return make_uint4(0u, 0u, 0u, 0u);
@@ -322,36 +389,31 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
           return GEMM == 0 ? __ldg(p) : __ldcg(p);
         };
         // weights two chunks ahead, activations one chunk ahead, all in registers
-        // this thread's CB / SPLIT raw bytes of chunk kc as NL pieces of 16 bytes (one piece of 8 bytes when that is all)
-        constexpr int RAWB = CB / SPLIT;
-        constexpr int NL = RAWB >= 16 ? RAWB / 16 : 1;
         auto load_w = [&](int kc, int piece) -> uint4 {
-          if (RAWB == 8) {
-            const uint2 v = __ldg(reinterpret_cast<const uint2*>(qrow + (size_t)kc * CB));
-            return make_uint4(v.x, v.y, 0u, 0u);
-          }
-          return __ldg(reinterpret_cast<const uint4*>(qrow + (size_t)kc * CB + 16 * piece));
+          return __ldg(reinterpret_cast<const uint4*>(qrow + (size_t)kc * cb + 16 * piece));
         };
-        uint4 q0[NL], q1[NL];
+        uint4 q0[NLX], q1[NLX];
 #pragma unroll
-        for (int l = 0; l < NL; ++l) q0[l] = load_w(0, l), q1[l] = NKC > 1 ? load_w(1, l) : q0[l];
-        __half2 sm0 = FMT == 0 ? __ldg(smrow) : __half2();
-        __half2 sm1 = FMT == 0 ? (NKC > 1 ? __ldg(smrow + 1) : sm0) : __half2();
+        for (int l = 0; l < NLX; ++l)
+          if (l < nl) q0[l] = load_w(0, l), q1[l] = NKC > 1 ? load_w(1, l) : q0[l];
+        __half2 sm0 = (FMT == 0 && !shd) ? __ldg(smrow) : __half2();
+        __half2 sm1 = (FMT == 0 && !shd) ? (NKC > 1 ? __ldg(smrow + 1) : sm0) : __half2();
         uint4 bn[BPT];
 #pragma unroll
         for (int i = 0; i < BPT; ++i) bn[i] = load_b(0, i);
         for (int kc = 0; kc < NKC; ++kc, ++chunk_no) {
           const int s = chunk_no % STAGES;
           unsigned char* st = stages + (size_t)s * STAGE_BYTES;
-          uint4 qv[NL];
+          uint4 qv[NLX];
 #pragma unroll
-          for (int l = 0; l < NL; ++l) qv[l] = q0[l], q0[l] = q1[l];
+          for (int l = 0; l < NLX; ++l) qv[l] = q0[l], q0[l] = q1[l];
           const __half2 smv = sm0;
           sm0 = sm1;
           if (kc + 2 < NKC) {
 #pragma unroll
-            for (int l = 0; l < NL; ++l) q1[l] = load_w(kc + 2, l);
-            if (FMT == 0) sm1 = __ldg(smrow + kc + 2);
+            for (int l = 0; l < NLX; ++l)
+              if (l < nl) q1[l] = load_w(kc + 2, l);
+            if (FMT == 0 && !shd) sm1 = __ldg(smrow + kc + 2);
           }
           uint4 bv[BPT];
 #pragma unroll
@@ -362,18 +424,30 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
           }
           // the MMAs that read this stage STAGES chunks ago must have completed
           if (chunk_no >= STAGES && !dead) dead = !mbar_wait(&ctl.empty[s], ((chunk_no / STAGES) - 1) & 1, DRB_ERR_TMEM);
-          if (FMT == 0) {
+          bool natural;  // element order of the operand chunks: k ascending, or (0,4,1,5,2,6,3,7) within each eight
+          if (SH && shd) {
+            natural = true;
+            const __half2 s2 = __half2half2(__ldg(ssrow + (kc >> 1)));  // one scale per 128 inputs = two chunks
+#pragma unroll
+            for (int l = 0; l < NL_S; ++l) {
+              uint4 o0, o1;
+              dequant16_i8(qv[l], s2, o0, o1);
+              *reinterpret_cast<uint4*>(st + a_off[2 * l]) = o0, *reinterpret_cast<uint4*>(st + a_off[2 * l + 1]) = o1;
+            }
+          } else if (FMT == 0) {
+            natural = false;
             const __half2 s2 = __half2half2(__low2half(smv)), m2 = __half2half2(__high2half(smv));
 #pragma unroll
-            for (int l = 0; l < NL; ++l) {
+            for (int l = 0; l < NL_R; ++l) {
               const uint32_t w[4] = {qv[l].x, qv[l].y, qv[l].z, qv[l].w};
 #pragma unroll
-              for (int j = 0; j < NST / NL; ++j) *reinterpret_cast<uint4*>(st + a_off[l * (NST / NL) + j]) = dequant8(w[j], s2, m2);
+              for (int j = 0; j < NST / NL_R; ++j) *reinterpret_cast<uint4*>(st + a_off[l * (NST / NL_R) + j]) = dequant8(w[j], s2, m2);
             }
           } else {
+            natural = true;
             const __half2 s2 = __float2half2_rn(__ldg(sfrow + (kc >> 1)) * norm);  // one scale per 128 inputs = two chunks
 #pragma unroll
-            for (int l = 0; l < NL; ++l) {
+            for (int l = 0; l < NL_R; ++l) {
               uint4 o0, o1;
               dequant16_fp8(qv[l], s2, o0, o1);
               *reinterpret_cast<uint4*>(st + a_off[2 * l]) = o0, *reinterpret_cast<uint4*>(st + a_off[2 * l + 1]) = o1;
@@ -383,8 +457,9 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
           for (int i = 0; i < BPT; ++i)
             if (bsrc[i]) {
               uint4 o;
-              if (FMT == 0) o = GEMM == 0 ? bf16x8_to_f16_perm(bv[i]) : f16x8_perm(bv[i]);
-              else o = GEMM == 0 ? bf16x8_to_f16_nat(bv[i]) : bv[i];  // E4M3 pairs unpack in k order
+              const bool from_bf16 = GEMM == 0 && !src_f16;  // the gate/up rows arrive as bf16 (the reference's ABI) or as fp16
+              if (!natural) o = from_bf16 ? bf16x8_to_f16_perm(bv[i]) : f16x8_perm(bv[i]);
+              else o = from_bf16 ? bf16x8_to_f16_nat(bv[i]) : bv[i];
               *reinterpret_cast<uint4*>(st + b_off[i]) = o;
             }
           fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
@@ -397,7 +472,7 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
         tc_fence_after();
         // FMT 1: undo the power of two that normalised the scales of this tile row's 128-row block
         float unnorm = 1.f;
-        if (FMT == 1) {
+        if (FMT == 1 && !shd) {
           const int erow = GEMM == 0 ? (r & 1) * I + mt * (TILE_M / 2) + (r >> 1) : mt * TILE_M + r;
           unnorm = 1.f / pow2_normaliser(__ldg(SF + ((size_t)e * (R / 128) + (erow >> 7)) * (K / 128)));
         }
@@ -409,16 +484,16 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
             for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * unnorm);
           }
           if (GEMM == 0) {
-            __half* act = static_cast<__half*>(dst);
+            __half* act = static_cast<__half*>(adst);
             const int j = mt * (TILE_M / 2) + (r >> 1);
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const float mine = __uint_as_float(v[i]);
               const float other = __shfl_xor_sync(0xffffffffu, mine, 1);  // even lane: gate, odd lane: up
-              if ((lane & 1) == 0 && c0 + i < nt) act[(size_t)(off + n0 + c0 + i) * I + j] = __float2half_rn(silu_f(mine) * other);
+              if ((lane & 1) == 0 && c0 + i < nt) act[(size_t)(off + n0 + c0 + i) * I + j] = f2h_sat(silu_f(mine) * other);
             }
           } else {
-            float* y = static_cast<float*>(dst);
+            float* y = static_cast<float*>(adst);
 #pragma unroll
             for (int i = 0; i < 16; ++i)
               if (c0 + i < nt) y[(size_t)(off + n0 + c0 + i) * H + mt * TILE_M + r] = __uint_as_float(v[i]);
@@ -435,16 +510,20 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
   if (warp == PRODUCER_WARPS) tmem_dealloc(tmem, TMEM_COLS);
 }
 
+template <typename Kn>
+static cudaError_t configure_one(Kn kernel) {
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+  return e != cudaSuccess ? e : drb_carveout(kernel);
+}
+
 static cudaError_t configure_all() {
   cudaError_t e;
-  if ((e = cudaFuncSetAttribute(k_grouped<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES)) != cudaSuccess) return e;
-  if ((e = cudaFuncSetAttribute(k_grouped<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES)) != cudaSuccess) return e;
-  if ((e = cudaFuncSetAttribute(k_grouped<0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES)) != cudaSuccess) return e;
-  if ((e = cudaFuncSetAttribute(k_grouped<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES)) != cudaSuccess) return e;
-  if ((e = drb_carveout(k_grouped<0, 0>)) != cudaSuccess) return e;
-  if ((e = drb_carveout(k_grouped<0, 1>)) != cudaSuccess) return e;
-  if ((e = drb_carveout(k_grouped<1, 1>)) != cudaSuccess) return e;
-  return drb_carveout(k_grouped<1, 0>);
+  if ((e = configure_one(k_grouped<0, 0, false>)) != cudaSuccess) return e;
+  if ((e = configure_one(k_grouped<1, 0, false>)) != cudaSuccess) return e;
+  if ((e = configure_one(k_grouped<0, 0, true>)) != cudaSuccess) return e;
+  if ((e = configure_one(k_grouped<1, 0, true>)) != cudaSuccess) return e;
+  if ((e = configure_one(k_grouped<0, 1, false>)) != cudaSuccess) return e;
+  return configure_one(k_grouped<1, 1, false>);
 }
 
 }  // namespace pfmma

@@ -202,123 +202,10 @@ __global__ void __launch_bounds__(THREADS)
   if (threadIdx.x == 0) sgate[r] = __ldcg(l + E);
 }
 
-// Decode router. Block b owns rows [b*R, b*R + R) of the [E+1, 2048] bf16 matrix, fetched with one
-// bulk copy issued before the dependency wait. After the wait every block normalises x itself,
-// computes its logits, and the last block to arrive (atomic counter, left at zero) runs the tail.
 constexpr int K = 2048;
-constexpr int ROWS_PER_BLOCK = 2;
-
-struct Smem {
-  __align__(16) unsigned char w[ROWS_PER_BLOCK * K * 2];
-  uint64_t full;
-  float part[ROWS_PER_BLOCK][8];
-  float red[32];
-  float inv_rms;
-  int last;
-  TopkSmem tk;
-};
-
-__global__ void __launch_bounds__(THREADS)
-    k_router_topk(const __nv_bfloat16* __restrict__ W, const float* __restrict__ x, const float* __restrict__ nw, float eps,
-                  float* logits, int E, int topk, int* __restrict__ idx, float* __restrict__ wts,
-                  float* __restrict__ sgate, unsigned* counter, const char* gu_q, const char* gu_sm, const char* d_q,
-                  const char* d_sm, size_t gu_q_b, size_t gu_sm_b, size_t d_q_b, size_t d_sm_b) {
-  __shared__ Smem sm;
-  DRB_TRACE_POINT(0, 0);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int row0 = blockIdx.x * ROWS_PER_BLOCK;
-  const int nrows = min(ROWS_PER_BLOCK, E + 1 - row0);
-  if (threadIdx.x == 0) {
-    mbar_init(&sm.full, 1);
-    mbar_fence_init();
-    mbar_expect_tx(&sm.full, (unsigned)(nrows * K * 2));
-    bulk_g2s(sm.w, W + (size_t)row0 * K, (unsigned)(nrows * K * 2), &sm.full);
-  }
-  __syncthreads();
-  pdl_launch_dependents();  // the gate/up kernel may start fetching the shared expert's rows right away
-  pdl_wait();               // x is the previous kernel's output
-  DRB_TRACE_POINT(1, 0);
-
-  // RMSNorm scale, recomputed by every block (8 KB of x from L2).
-  const float4* x4 = reinterpret_cast<const float4*>(x);
-  const float4 xa = __ldcg(x4 + threadIdx.x * 2), xb = __ldcg(x4 + threadIdx.x * 2 + 1);  // k = 8*t .. 8*t+7
-  float inv = 1.f;
-  if (nw) {
-    float ss = xa.x * xa.x + xa.y * xa.y + xa.z * xa.z + xa.w * xa.w + xb.x * xb.x + xb.y * xb.y + xb.z * xb.z + xb.w * xb.w;
-    ss = warp_sum(ss);
-    if (lane == 0) sm.red[warp] = ss;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      float t = 0.f;
-      for (int w = 0; w < 8; ++w) t += sm.red[w];
-      sm.inv_rms = rsqrtf(t / K + eps);
-    }
-    __syncthreads();
-    inv = sm.inv_rms;
-  }
-  unsigned long long xp[4];
-  {
-    float4 a = xa, b = xb;
-    if (nw) {
-      const float4 wa = reinterpret_cast<const float4*>(nw)[threadIdx.x * 2], wb = reinterpret_cast<const float4*>(nw)[threadIdx.x * 2 + 1];
-      a = make_float4(a.x * inv * wa.x, a.y * inv * wa.y, a.z * inv * wa.z, a.w * inv * wa.w);
-      b = make_float4(b.x * inv * wb.x, b.y * inv * wb.y, b.z * inv * wb.z, b.w * inv * wb.w);
-    }
-    xp[0] = pack2(a.x, a.y), xp[1] = pack2(a.z, a.w), xp[2] = pack2(b.x, b.y), xp[3] = pack2(b.z, b.w);
-  }
-  DRB_TRACE_POINT(2, 0);
-  mbar_wait(&sm.full, 0, DRB_ERR_FULL_WAIT);
-  DRB_TRACE_POINT(3, 0);
-  // Each thread owns one 16-byte chunk (8 weights) of every row of the block.
-#pragma unroll
-  for (int r = 0; r < ROWS_PER_BLOCK; ++r) {
-    float d = 0.f;
-    if (r < nrows) {
-      const uint4 v = *reinterpret_cast<const uint4*>(sm.w + (size_t)r * K * 2 + threadIdx.x * 16);
-      float p0, p1;
-      unpack2(dot8_bf16(v, xp, 0ull), p0, p1);
-      d = p0 + p1;
-    }
-    d = warp_sum(d);
-    if (lane == 0) sm.part[r][warp] = d;
-  }
-  __syncthreads();
-  if ((int)threadIdx.x < nrows) {
-    float t = 0.f;
-    for (int w = 0; w < 8; ++w) t += sm.part[threadIdx.x][w];
-    __stcg(logits + row0 + threadIdx.x, t);
-  }
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) sm.last = atomicAdd(counter, 1u) == gridDim.x - 1;
-  __syncthreads();
-  DRB_TRACE_POINT(4, 0);
-  if (!sm.last) return;
-  __threadfence();
-  DRB_TRACE_ANY(5, 0);
-  const int e = threadIdx.x;
-  const float v = e < E ? __ldcg(logits + e) : -INFINITY;
-  softmax_topk(v, E, topk, idx, wts, sm.tk);
-  if (threadIdx.x == 0) {
-    sgate[0] = __ldcg(logits + E);
-    *counter = 0u;
-  }
-  DRB_TRACE_ANY(6, 0);
-  // Optional: pull exactly the chosen experts into L2 (one bulk prefetch per region and expert).
-  if (gu_q && threadIdx.x < 32) {
-    __syncwarp();
-    for (int i = threadIdx.x; i < topk * 4; i += 32) {
-      const int k = i >> 2, which = i & 3;
-      const size_t ex = (size_t)idx[k];
-      const char* base = which == 0 ? gu_q : which == 1 ? gu_sm : which == 2 ? d_q : d_sm;
-      const size_t nb = which == 0 ? gu_q_b : which == 1 ? gu_sm_b : which == 2 ? d_q_b : d_sm_b;
-      if (base) prefetch_share(base + ex * nb, nb, 0, 1);
-    }
-  }
-}
 
 // ------------------------------------------------------------------------------------------
-// Cluster variant of the decode router: ONE thread-block cluster of 8 blocks. Block c owns rows
+// Decode router: ONE thread-block cluster of 8 blocks. Block c owns rows
 // [33 c, 33 c + 33) of the [E+1, 2048] matrix and pulls them into shared memory with one bulk copy
 // before the dependency wait; after the wait it normalises x, computes its logits and stores them
 // straight into block 0's shared memory (distributed shared memory). One cluster barrier later block 0
@@ -472,9 +359,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 }  // namespace cl
 
 static cudaError_t configure_all() {
-  cudaError_t e = drb_carveout(k_router_topk);
+  cudaError_t e = drb_carveout(cl::k_router_cluster);
   if (e != cudaSuccess) return e;
-  if ((e = drb_carveout(cl::k_router_cluster)) != cudaSuccess) return e;
   if ((e = cudaFuncSetAttribute(cl::k_router_cluster, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cl::SMEM_BYTES)) != cudaSuccess) return e;
   return drb_carveout(k_moe_topk);
 }
@@ -489,27 +375,23 @@ extern "C" int dr_router_topk(const __nv_bfloat16* W, const float* x, const floa
   if (K != 2048 || E > 256 || E < 1 || topk > 32 || topk < 1 || topk > E) return -1;
   const DrbDevice& dev = drb_device(st);
   if (!dev.ready) return -2;
-  if (dev.router_cluster) {
-    // One cluster of 8 blocks, launched with the programmatic-dependency attribute as well.
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(router::cl::CLUSTER);
-    cfg.blockDim = dim3(router::THREADS);
-    cfg.dynamicSmemBytes = router::cl::SMEM_BYTES;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = router::cl::CLUSTER, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = dev.pdl ? 2 : 1;
-    cudaLaunchKernelEx(&cfg, router::cl::k_router_cluster, W, x, nw, eps, logits, E, topk, idx, wts, sgate, gu_q, gu_sm, d_q,
-                       d_sm, gu_q_b, gu_sm_b, d_q_b, d_sm_b);
-    return 0;
-  }
-  const int grid = (E + 1 + router::ROWS_PER_BLOCK - 1) / router::ROWS_PER_BLOCK;
-  drb_launch(router::k_router_topk, dim3(grid), dim3(router::THREADS), 0, st, dev.pdl, W, x, nw, eps, logits, E, topk, idx,
-             wts, sgate, counter, gu_q, gu_sm, d_q, d_sm, gu_q_b, gu_sm_b, d_q_b, d_sm_b);
+  // One cluster of 8 blocks, launched with the programmatic-dependency attribute as well. The counter word of the
+  // ABI is never touched (it stays zero, as the caller expects): nothing here needs a last-block election.
+  (void)counter;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(router::cl::CLUSTER);
+  cfg.blockDim = dim3(router::THREADS);
+  cfg.dynamicSmemBytes = router::cl::SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = router::cl::CLUSTER, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dev.pdl ? 2 : 1;
+  cudaLaunchKernelEx(&cfg, router::cl::k_router_cluster, W, x, nw, eps, logits, E, topk, idx, wts, sgate, gu_q, gu_sm, d_q,
+                     d_sm, gu_q_b, gu_sm_b, d_q_b, d_sm_b);
   return 0;
 }
 

@@ -10,6 +10,7 @@
 #include <cublas_v2.h>
 #include <stdlib.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -32,8 +33,8 @@ namespace pfmma { static cudaError_t configure_all(); }
 namespace rt {
 
 constexpr int MAX_DEVICES = 32;
-constexpr int GRID_SYNC_WORDS = 1024;
 static DrbDevice g_dev[MAX_DEVICES];
+static std::atomic<bool> g_ready[MAX_DEVICES];  // g_dev[d] is complete (release / acquire)
 static const DrbDevice g_unready = {};
 static std::mutex g_mu;
 static cudaError_t g_setup_error = cudaSuccess;
@@ -43,19 +44,9 @@ static cudaError_t setup(int d) {
   cudaError_t e;
   int sms = 0;
   if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d)) != cudaSuccess) return e;
-  if (const char* v = getenv("DRB_SMS")) {
-    const int o = atoi(v);
-    if (o > 0 && o < sms) sms = o;
-  }
   dv.sms = sms;
   const char* p = getenv("DRB_PDL");
   dv.pdl = !(p && p[0] == '0');
-  const char* pv = getenv("DRB_PREFILL");
-  dv.prefill_mma = !(pv && pv[0] == 's');
-  const char* rv = getenv("DRB_ROUTER");
-  dv.router_cluster = !(rv && rv[0] == 'g');
-  const char* dw = getenv("DRB_DOWN_WARMUP");
-  dv.down_warmup = dw && dw[0] == '1';  // measured 0.3 us per layer slower than leaving the rows to the down kernel
   if ((e = gemv::configure_all()) != cudaSuccess) return e;
   if ((e = router::configure_all()) != cudaSuccess) return e;
   if ((e = pf::configure_all()) != cudaSuccess) return e;
@@ -63,10 +54,9 @@ static cudaError_t setup(int d) {
   if ((e = moe::f8::configure_all()) != cudaSuccess) return e;
   if ((e = stack::configure_all()) != cudaSuccess) return e;
   if ((e = pfmma::configure_all()) != cudaSuccess) return e;
-  if ((e = cudaMalloc(&dv.grid_sync, GRID_SYNC_WORDS * sizeof(unsigned))) != cudaSuccess) return e;
-  if ((e = cudaMemset(dv.grid_sync, 0, GRID_SYNC_WORDS * sizeof(unsigned))) != cudaSuccess) return e;
   dv.ready = true;
   g_dev[d] = dv;
+  g_ready[d].store(true, std::memory_order_release);
   return cudaSuccess;
 }
 
@@ -78,7 +68,7 @@ static cudaError_t ensure() {
   if (e != cudaSuccess) return e;
   if (d < 0 || d >= MAX_DEVICES) return cudaErrorInvalidDevice;
   std::lock_guard<std::mutex> lock(g_mu);
-  if (g_dev[d].ready) return cudaSuccess;
+  if (g_ready[d].load(std::memory_order_acquire)) return cudaSuccess;
   e = setup(d);
   g_setup_error = e;
   return e;
@@ -89,7 +79,7 @@ static cudaError_t ensure() {
 const DrbDevice& drb_device(cudaStream_t st) {
   int d = 0;
   if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= rt::MAX_DEVICES) return rt::g_unready;
-  if (rt::g_dev[d].ready) return rt::g_dev[d];
+  if (rt::g_ready[d].load(std::memory_order_acquire)) return rt::g_dev[d];
   cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
   if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return rt::g_unready;
   if (rt::ensure() != cudaSuccess) return rt::g_unready;
@@ -178,7 +168,7 @@ DRB_API int drb_device_error(unsigned* out) {
   return (int)cudaMemcpyToSymbol(g_drb_error, &zero, sizeof(unsigned));
 }
 
-// Blocks the persistent kernels launch on the current device (multiprocessor count unless overridden).
+// Blocks the persistent kernels launch on the current device (the multiprocessor count).
 DRB_API int drb_grid_blocks(void) {
   if (rt::ensure() != cudaSuccess) return -1;
   int d = 0;

@@ -5,9 +5,12 @@ region to the op before it for L2 prefetch (the last wraps to the first), and is
 into a graph that `step` replays — src/engine.rs:136-150 (`Op`), 674-708 (`record_step`),
 946-1042 (router + moe_decode per layer, x == res == y), 1047-1066 (`step`).
 
-Prefill: `moe_prefill` is src/engine.rs:544-604: cuBLAS router logits, dr_moe_topk, shared
-expert through dequant + cuBLAS, count, counts to the host, host exclusive scan, permute,
-grouped expert kernel, combine.
+Prefill: `MoePrefill` has two forms. `reference_calls=True` is src/engine.rs:544-604 call for call:
+cuBLAS router logits, dr_moe_topk, shared expert through dequant + cuBLAS, count, counts to the
+host, host exclusive scan, permute, grouped expert kernel, combine. The default is this library's
+own sequence of seven launches with no library GEMM and no host round trip: rmsnorm, router logits
+in a fixed order, top-k, one grouping kernel, the two grouped tensor-core GEMMs (which also run the
+int8 shared expert and read their rows in place), combine.
 """
 
 from __future__ import annotations
@@ -42,11 +45,12 @@ class MoeDecoder:
     """Batch-1 decode over a stack of MoE layers: x <- x + moe_l(rmsnorm(x)) for each layer."""
 
     def __init__(self, layers: list[MoeLayer], topk: int = 8, eps: float = 1e-6, st: Stream | None = None,
-                 chained: bool = False, trace_routing: bool = False, fp8: list | None = None) -> None:
+                 chained: bool = False, trace_routing: bool = False, fp8: list | None = None, lib=None) -> None:
         """chained (not in the reference): the layers run drb_moe_decode_chained, whose down kernel also produces the
         next layer's routing, so only the first layer launches dr_router_topk. trace_routing copies every layer's
-        idx to `idx_trace` (tests)."""
-        self.l = ffi.lib()
+        idx to `idx_trace` (tests). lib: another library with the same ABI (ffi.bind) to issue the launches to; buffers
+        and streams still come from this one."""
+        self.l = lib or ffi.lib()
         self.st = st or Stream()
         self.layers = layers
         self.topk, self.eps = topk, eps
@@ -177,33 +181,41 @@ class MoePrefill:
     counts/offsets/fill/slot_of, xp/ap/yp in expert-sorted order, and one bf16 weight buffer for
     the dequantised int8 matrices."""
 
-    def __init__(self, layer: MoeLayer, max_rows: int, topk: int = 8, eps: float = 1e-6, st: Stream | None = None) -> None:
+    def __init__(self, layer: MoeLayer, max_rows: int, topk: int = 8, eps: float = 1e-6, st: Stream | None = None,
+                 reference_calls: bool = False) -> None:
         self.l = ffi.lib()
         self.st = st or Stream()
         self.layer, self.topk, self.eps, self.max_rows = layer, topk, eps, max_rows
+        self.reference_calls = reference_calls
+        # own sequence: the normalised rows stay in fp16 (eleven significant bits; the reference's prefill rounds them to bf16)
+        self.rows_f16 = not reference_calls
         h, i, e = layer.hidden, layer.inter, layer.experts
         n = max_rows
         self.blas = C.c_void_p()
-        check(self.l.dr_cublas_create(C.byref(self.blas), self.st.raw), "cublas_create")
+        if reference_calls:
+            check(self.l.dr_cublas_create(C.byref(self.blas), self.st.raw), "cublas_create")
+        else:
+            check(self.l.drb_init(), "init")
         self.x = DevBuf(n * h * 4)
         self.hn_b = DevBuf(n * h * 2)
         self.rlog = DevBuf(n * (e + 1) * 4)
         self.idx = DevBuf(n * topk * 4)
         self.wts = DevBuf(n * topk * 4)
         self.sgate = DevBuf(n * 4)
-        self.shh = DevBuf(n * 2 * i * 4)
+        self.shh = DevBuf(n * 2 * i * 4) if reference_calls else None
         self.sh_act_b = DevBuf(n * i * 2)
         self.sh_out = DevBuf(n * h * 4)
         self.counts = DevBuf(e * 4)
         self.offsets = DevBuf(e * 4)
         self.fill = DevBuf(e * 4)
         self.slot_of = DevBuf(n * topk * 4)
-        self.xp = DevBuf(n * topk * h * 2)
+        self.row_of = DevBuf(n * topk * 4)
+        self.xp = DevBuf(n * topk * h * 2) if reference_calls else None
         self.ap = DevBuf(n * topk * i * 2)
         self.yp = DevBuf(n * topk * h * 4)
-        self.wbuf = DevBuf(2 * i * h * 2)
-        self.device_scan = False  # True: offsets by drb_moe_offsets on the device instead of the reference's host scan
-        self.invariant_router = False  # True: router logits by drb_router_logits (independent of the batch size) instead of cuBLAS
+        self.wbuf = DevBuf(2 * i * h * 2) if reference_calls else None
+        self.device_scan = False  # reference calls only: offsets by drb_moe_offsets on the device instead of the host scan
+        self.invariant_router = not reference_calls  # router logits by drb_router_logits (independent of the batch size) instead of cuBLAS
         self.logit_bias: DevBuf | None = None  # [n, E + 1] f32 rows the router GEMM accumulates onto (not in the reference)
 
     def gemm_q8(self, a, w, c, m: int, beta: float) -> None:
@@ -228,21 +240,53 @@ class MoePrefill:
         self.run_device(n)
         return self.x.download(np.float32, n * h, self.st).reshape(n, h)
 
-    def run_device(self, n: int) -> None:
-        """The block on the n rows already in self.x (device), in place; call for call the reference's sequence.
-        With a logit bias the router GEMM accumulates onto the bias rows (beta = 1) instead of overwriting."""
+    def route_device(self, n: int) -> None:
+        """rmsnorm -> hn_b, router logits, top-k, on the n rows in self.x."""
         l, st, layer = self.l, self.st.raw, self.layer
-        h, e, topk, i = layer.hidden, layer.experts, self.topk, layer.inter
-        launched(l.dr_rmsnorm(self.x.at(0), layer.post_norm.at(0), NULL, self.hn_b.at(0), n, h, self.eps, st), "rmsnorm")
+        h, e, topk = layer.hidden, layer.experts, self.topk
+        if self.rows_f16:
+            launched(l.drb_rmsnorm_f16(self.x.at(0), layer.post_norm.at(0), self.hn_b.at(0), n, h, self.eps, st), "rmsnorm_f16")
+        else:
+            launched(l.dr_rmsnorm(self.x.at(0), layer.post_norm.at(0), NULL, self.hn_b.at(0), n, h, self.eps, st), "rmsnorm")
         beta = 0.0
         if self.logit_bias is not None:
             check(l.dr_d2d(self.rlog.at(0), self.logit_bias.at(0), n * (e + 1) * 4, st), "d2d")
             beta = 1.0
-        if self.invariant_router:
+        if self.rows_f16:
+            launched(l.drb_router_logits_f16(self.hn_b.at(0), layer.router.at(0), self.rlog.at(0), n, e + 1, h, beta, st), "router_logits_f16")
+        elif self.invariant_router:
             launched(l.drb_router_logits(self.hn_b.at(0), layer.router.at(0), self.rlog.at(0), n, e + 1, h, beta, st), "router_logits")
         else:
             check(l.dr_gemm(self.blas, self.hn_b.at(0), layer.router.at(0), self.rlog.at(0), n, e + 1, h, beta), "gemm")
         launched(l.dr_moe_topk(self.rlog.at(0), n, e, topk, e + 1, self.idx.at(0), self.wts.at(0), self.sgate.at(0), st), "moe_topk")
+
+    def run_device(self, n: int) -> None:
+        """The block on the n rows already in self.x (device), in place. With a logit bias the router logits are
+        accumulated onto the bias rows (beta = 1) instead of overwriting them."""
+        if self.reference_calls:
+            return self.run_device_reference_calls(n)
+        l, st, layer = self.l, self.st.raw, self.layer
+        h, e, topk, i = layer.hidden, layer.experts, self.topk, layer.inter
+        self.route_device(n)
+        launched(l.drb_moe_group(self.idx.at(0), n, topk, 0, e, self.counts.at(0), self.offsets.at(0), self.slot_of.at(0),
+                                 self.row_of.at(0), st), "moe_group")
+        gq, gs = layer.gate_up.expert(0)
+        dq, ds = layer.down.expert(0)
+        sgq, sgs = layer.shared_gate_up.rows(0)
+        sdq, sds = layer.shared_down.rows(0)
+        launched(
+            l.drb_moe_prefill_block(gq, gs, dq, ds, sgq, sgs, sdq, sds, self.hn_b.at(0), self.row_of.at(0), self.offsets.at(0),
+                                    self.counts.at(0), self.ap.at(0), self.yp.at(0), self.sh_act_b.at(0), self.sh_out.at(0), n, e, h, i,
+                                    1 if self.rows_f16 else 0, st), "moe_prefill_block")
+        launched(
+            l.dr_moe_combine(self.x.at(0), self.yp.at(0), self.slot_of.at(0), self.wts.at(0), self.sgate.at(0),
+                             self.sh_out.at(0), n, topk, h, st), "moe_combine")
+
+    def run_device_reference_calls(self, n: int) -> None:
+        """Call for call the reference's sequence (src/engine.rs:544-604)."""
+        l, st, layer = self.l, self.st.raw, self.layer
+        h, e, topk, i = layer.hidden, layer.experts, self.topk, layer.inter
+        self.route_device(n)
         # Shared expert.
         self.gemm_q8(self.hn_b.at(0), layer.shared_gate_up, self.shh.at(0), n, 0.0)
         launched(l.dr_swiglu_rows(self.shh.at(0), self.sh_act_b.at(0), n, i, st), "swiglu")
@@ -268,6 +312,7 @@ class MoePrefill:
         launched(
             l.dr_moe_combine(self.x.at(0), self.yp.at(0), self.slot_of.at(0), self.wts.at(0), self.sgate.at(0),
                              self.sh_out.at(0), n, topk, h, st), "moe_combine")
+
 
 class MoeStackDecoder:
     """The same stack as MoeDecoder through drb_moe_stack_decode: one persistent kernel per step."""

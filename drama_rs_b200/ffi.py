@@ -61,6 +61,10 @@ SIGNATURES: dict[str, tuple] = {
     "drb_moe_stack_workspace_bytes": (I32, []),
     "drb_moe_stack_decode": (I32, [P, I32, P, P, I32, I32, I32, I32, F32, P, P, P]),
     "drb_moe_offsets": (I32, [P, I32, P, P]),
+    "drb_moe_group": (I32, [P, I32, I32, I32, I32, P, P, P, P, P]),
+    "drb_moe_prefill_block": (I32, [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I32, I32, I32, I32, I32, P]),
+    "drb_rmsnorm_f16": (I32, [P, P, P, I32, I32, F32, P]),
+    "drb_router_logits_f16": (I32, [P, P, P, I32, I32, I32, F32, P]),
     "drb_router_logits": (I32, [P, P, P, I32, I32, I32, F32, P]),
     "drb_moe_decode_chained": (I32, [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I32, I32, I32, P, F32, P, P, I32, P, P, I32, P]),
     "drb_moe_chain_workspace_bytes": (SZ, []),
@@ -72,6 +76,19 @@ SIGNATURES: dict[str, tuple] = {
 }
 
 _lib = None
+
+
+def bind(path: str) -> C.CDLL:
+    """Loads another library that exports (a subset of) the same ABI, for example the reference's own kernels built
+    as a checker, and applies the signatures of the symbols it has. Used by tests and benchmarks only."""
+    l = C.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        try:
+            fn = getattr(l, name)
+        except AttributeError:
+            continue
+        fn.restype, fn.argtypes = res, args
+    return l
 
 
 def lib() -> C.CDLL:

@@ -10,11 +10,13 @@ from drama_rs_b200.engine import MoeDecoder, MoePrefill, MoeStackDecoder
 from drama_rs_b200.gpu import DevBuf, Stream, launched
 from drama_rs_b200.model import MoeLayer
 from oracle import moe_oracle as orc
-from tests.helpers import NULL, assert_parity, device_error_word
+from tests.helpers import MAX_ABS, NULL, REL_L2, assert_parity, device_error_word, parity
 
 pytestmark = pytest.mark.gpu
 
 SHAPE = synth.MoeShape()
+# the reference's own kernels/drama.cu built unchanged as a checker (oracle/build.py); absent when no checkout was at hand
+REF_LIB = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "libdrama_ref.so")
 
 
 @pytest.fixture(scope="module")
@@ -223,6 +225,51 @@ def test_moe_stack_persistent_kernel(st, layers, golden_dir):
     assert device_error_word() == 0
 
 
+def test_moe_stack_40_layers_against_the_oracle(st, layers):
+    """The benchmark's decode step at its real depth: 40 layers (two seeded layers alternating, so the stack is 40
+    pointers) in one persistent kernel against the fp64 oracle, every layer's routing bit-exact. The per-layer entry
+    points are held to the same bar on the same stack."""
+    pairs = [layers(s) for s in (0, 1)] * 20
+    x = synth.make_x(21, 1, 2048)[0]
+    ref = x.astype(np.float64)[None]
+    ref_idx, margins = [], []
+    for host, _ in pairs:
+        ref, ridx, _, _, logits = orc.moe_layer(host, ref, 8, 1e-6, np.float64)
+        ref_idx.append(ridx[0])
+        margins.append(float(orc.route_margin(logits, 256, 8)[0]))
+    ref_idx = np.stack(ref_idx)
+    # a margin below ~1e-6 of probability is within fp32 rounding of the logits themselves: such a layer's routing is
+    # not decidable in single precision (none occurs on this seed; the assertion documents the premise)
+    assert min(margins) > 1e-6, min(margins)
+    scale = float(np.abs(ref).max())
+    sd = MoeStackDecoder([d for _, d in pairs], st=st)
+    sd.capture()
+    sd.set_x(x)
+    y = sd.step()
+    assert device_error_word() == 0
+    idx, _ = sd.routing()
+    assert np.array_equal(idx, ref_idx), np.nonzero((idx != ref_idx).any(axis=1))[0]
+    # one layer is held to 4e-6 of the largest output (the fp32 noise of the reference block); over 40 layers of an
+    # fp32 hidden state that compounds, so the stack is held to 1e-5 and the reference's own fp32 kernels are run on
+    # the same stack to show where the floor lies
+    bar = max(1e-2, 1e-5 * scale)
+    a, r = assert_parity(y, ref[0], "40-layer persistent stack", max_abs=bar)
+    dec = MoeDecoder([d for _, d in pairs], st=st, trace_routing=True)
+    dec.capture()
+    dec.set_x(x)
+    y2 = dec.step()
+    assert np.array_equal(dec.routing_trace(), ref_idx)
+    a2, r2 = assert_parity(y2, ref[0], "40-layer stack, per-layer entry points", max_abs=bar)
+    note = ""
+    if os.path.exists(REF_LIB):
+        rdec = MoeDecoder([d for _, d in pairs], st=st, lib=ffi.bind(REF_LIB))
+        rdec.set_x(x)
+        a3, r3 = parity(rdec.step_eager(), ref[0])
+        note = f"; the reference's fp32 kernels max-abs {a3:.3e} rel-L2 {r3:.3e}"
+    print(f"40 layers, |x| {scale:.3e}: persistent max-abs {a:.3e} rel-L2 {r:.3e}; per-layer max-abs {a2:.3e} rel-L2 {r2:.3e}{note}; smallest routing margin {min(margins):.2e}")
+    assert device_error_word() == 0
+
+
 def test_moe_prefill_grouped_kernel_direct(st, layers):
     """dr_moe_prefill alone on hand-made groups: one expert with more tokens than one accumulator holds (300),
     empty experts, groups of 1, 16 and 17 tokens. Each output row against the fp64 expert on the same bf16 row."""
@@ -255,67 +302,86 @@ def test_moe_prefill_grouped_kernel_direct(st, layers):
 
 
 def test_router_logits_do_not_depend_on_the_batch(st, layers):
-    """drb_router_logits: a row's logits are bit-identical whether it is computed alone, in a batch of 7 or of 300
-    (what lets expert-parallel ranks with different row counts route identically), and agree with cuBLAS."""
+    """drb_router_logits / drb_router_logits_f16: a row's logits are bit-identical whether it is computed alone, in a
+    batch of 7 or of 300 (what lets expert-parallel ranks with different row counts route identically), and agree
+    with cuBLAS on the same bf16 rows."""
     host, dev = layers(2)
     x = synth.make_x(8, 300, 2048)
-    runs = {}
-    for name, sl in (("all", slice(0, 300)), ("seven", slice(100, 107)), ("one", slice(103, 104))):
-        pre = MoePrefill(dev, 300, st=st)
-        pre.invariant_router = True
-        pre.run(x[sl])
-        n = sl.stop - sl.start
-        runs[name] = (pre.rlog.download(np.float32, n * 257, st).reshape(n, 257), pre.idx.download(np.int32, n * 8, st).reshape(n, 8))
-    assert np.array_equal(runs["all"][0][100:107].view(np.uint32), runs["seven"][0].view(np.uint32))
-    assert np.array_equal(runs["all"][0][103:104].view(np.uint32), runs["one"][0].view(np.uint32))
-    assert np.array_equal(runs["all"][1][100:107], runs["seven"][1])
-    blas = MoePrefill(dev, 300, st=st)
+    for rows_f16 in (True, False):
+        runs = {}
+        for name, sl in (("all", slice(0, 300)), ("seven", slice(100, 107)), ("one", slice(103, 104))):
+            pre = MoePrefill(dev, 300, st=st)
+            pre.rows_f16 = rows_f16
+            pre.run(x[sl])
+            n = sl.stop - sl.start
+            runs[name] = (pre.rlog.download(np.float32, n * 257, st).reshape(n, 257), pre.idx.download(np.int32, n * 8, st).reshape(n, 8))
+        assert np.array_equal(runs["all"][0][100:107].view(np.uint32), runs["seven"][0].view(np.uint32))
+        assert np.array_equal(runs["all"][0][103:104].view(np.uint32), runs["one"][0].view(np.uint32))
+        assert np.array_equal(runs["all"][1][100:107], runs["seven"][1])
+        xh = orc.rmsnorm(x, host["post_norm"], 1e-6)
+        xh = xh.astype(np.float16).astype(np.float32) if rows_f16 else orc.round_bf16(xh)
+        ref = orc.router_logits(host, xh.astype(np.float64), np.float64)
+        # the device's RMSNorm sums in another order, so a few normalised values round to the neighbouring 16-bit value
+        assert np.abs(ref - runs["all"][0]).max() <= (3e-4 if rows_f16 else 2e-3) * np.abs(ref).max()
+    blas = MoePrefill(dev, 300, st=st, reference_calls=True)
     blas.run(x)
     lb = blas.rlog.download(np.float32, 300 * 257, st).reshape(300, 257)
     assert np.abs(lb - runs["all"][0]).max() <= 1e-5 * np.abs(lb).max()
-    xh = orc.round_bf16(orc.rmsnorm(x, host["post_norm"], 1e-6))
-    ref = orc.router_logits(host, xh.astype(np.float64), np.float64)
-    # the device's RMSNorm sums in another order, so a few normalised values round to the neighbouring bf16
-    assert np.abs(ref - runs["all"][0]).max() <= 2e-3 * np.abs(ref).max()
     assert ffi.lib().drb_router_logits(NULL, NULL, NULL, 4, 257, 1024, 0.0, st.raw) == -1
+    assert ffi.lib().drb_router_logits_f16(NULL, NULL, NULL, 4, 257, 1024, 0.0, st.raw) == -1
+
+
+def prefill_bar(ref):
+    """The prefill bar: relative L2 1e-3, and max-abs 1e-2 scaled to the outputs where they are large. The grouped
+    GEMMs run on the tensor cores with fp16 operands (11 significant bits where the decode path's integer dot
+    products are exact), so the absolute error is 2^-11 of the largest output, not the decode path's 4e-6."""
+    return dict(max_abs=max(MAX_ABS, 2.0 ** -11 * float(np.abs(ref).max())), rel_l2=REL_L2)
+
+
+# Relative L2 of the reference call sequence: the shared expert runs through cuBLAS on weights dequantised to bf16 and
+# a bf16 intermediate, exactly as the reference's prefill does (src/engine.rs:351-355, 560-562); that rounding sets it.
+REL_PREFILL_CUBLAS = 4e-3
 
 
 def test_moe_prefill_golden_rows40(st, layers, golden_dir):
+    """40 rows through the prefill block: this library's own sequence (grouping kernel, grouped tensor-core GEMMs that
+    also run the int8 shared expert, no library GEMM) held to the layer bar; the reference's call sequence (shared
+    expert through cuBLAS on bf16-dequantised weights) to the looser figure that rounding sets."""
     g = np.load(os.path.join(golden_dir, "moe_rows40_seed2.npz"))
     host, dev = layers(2)
     x = synth.make_x(2, 40, 2048)
-    pre = MoePrefill(dev, 64, st=st)
-    y = pre.run(x)
-    idx = pre.idx.download(np.int32, 40 * 8, st).reshape(40, 8)
-    # The prefill ABI carries the normalised rows in bf16 (src/engine.rs:499, 554), so routing is decided on
-    # bf16-rounded activations: compare with the oracle fed the same rows, and with the reference's fp32-input
-    # routing wherever the two oracles agree.
-    xh = orc.round_bf16(orc.rmsnorm(x, host["post_norm"], 1e-6))
-    out, oidx, _, _, logits = orc.moe_block(host, xh.astype(np.float64), 8, np.float64)
-    safe = orc.route_margin(logits, 256, 8) > 1e-6
-    assert safe.all() and np.array_equal(idx, oidx)
-    same = (oidx == g["idx"]).all(axis=1)
-    assert same.mean() >= 0.9 and np.array_equal(idx[same], g["idx"][same])
     ref = x.astype(np.float64) + g["out_hf64"]
-    a, r = assert_parity(y[same], ref[same], "prefill 40 rows vs the reference (fp32 inputs)", max_abs=np.inf, rel_l2=REL_PREFILL)
-    assert_parity(y - x, out, "prefill 40 rows vs bf16-input oracle", max_abs=np.inf, rel_l2=REL_PREFILL)
-    assert device_error_word() == 0
+    for reference_calls in (False, True):
+        # the reference's prefill rounds the normalised rows to bf16, this library's own sequence keeps fp16: the oracle
+        # is fed the rows as the sequence sees them, so routing is compared on equal terms
+        xh = orc.rmsnorm(x, host["post_norm"], 1e-6)
+        xh = orc.round_bf16(xh) if reference_calls else xh.astype(np.float16).astype(np.float32)
+        out, oidx, _, _, logits = orc.moe_block(host, xh.astype(np.float64), 8, np.float64)
+        safe = orc.route_margin(logits, 256, 8) > 1e-6
+        same = (oidx == g["idx"]).all(axis=1)
+        pre = MoePrefill(dev, 64, st=st, reference_calls=reference_calls)
+        y = pre.run(x)
+        idx = pre.idx.download(np.int32, 40 * 8, st).reshape(40, 8)
+        assert safe.all() and np.array_equal(idx, oidx)
+        assert same.mean() >= 0.9 and np.array_equal(idx[same], g["idx"][same])
+        what = "reference call sequence" if reference_calls else "own sequence"
+        bar = dict(max_abs=np.inf, rel_l2=REL_PREFILL_CUBLAS) if reference_calls else prefill_bar(out)
+        a, r = assert_parity(y - x, out, f"prefill 40 rows, {what}, vs the oracle on the same 16-bit rows", **bar)
+        a2, r2 = parity(y[same], ref[same])
+        print(f"{what}: vs same-rows oracle max-abs {a:.3e} rel-L2 {r:.3e}; vs the reference block on fp32 rows max-abs {a2:.3e} rel-L2 {r2:.3e}")
+        # the bar of the layer against the reference block itself (fp32 rows, fp64 arithmetic): relative L2 1e-3
+        assert r2 <= (REL_PREFILL_CUBLAS if reference_calls else REL_L2)
+        assert device_error_word() == 0
 
 
-# Relative L2 of the prefill output. The shared expert runs through cuBLAS on weights dequantised to bf16 and
-# a bf16 intermediate, exactly as the reference's prefill does (src/engine.rs:351-355, 560-562); that rounding,
-# not the routed int4 path, sets this figure.
-REL_PREFILL = 4e-3
-
-
-def test_moe_prefill_device_scan_and_graph(st, layers):
-    """With the offsets computed on the device the whole prefill block is one captured graph; its result equals
-    the reference-style sequence with the host scan."""
+def test_moe_prefill_reference_calls_device_scan_and_graph(st, layers):
+    """Reference call sequence: with the offsets computed on the device the whole block is one captured graph; its
+    result equals the sequence with the host scan. Own sequence: a captured graph equals the eager launches."""
     from drama_rs_b200.gpu import Graph
 
     host, dev = layers(2)
     x = synth.make_x(5, 64, 2048)
-    pre = MoePrefill(dev, 64, st=st)
+    pre = MoePrefill(dev, 64, st=st, reference_calls=True)
     y_host_scan = pre.run(x)
     pre.device_scan = True
     y_dev_scan = pre.run(x)
@@ -325,7 +391,69 @@ def test_moe_prefill_device_scan_and_graph(st, layers):
     g.launch(st)
     y_graph = pre.x.download(np.float32, 64 * 2048, st).reshape(64, 2048)
     assert np.array_equal(y_graph, y_host_scan)
+    own = MoePrefill(dev, 64, st=st)
+    y_own = own.run(x)
+    g2 = Graph(st, lambda: own.run_device(64))
+    for _ in range(2):
+        own.x.upload(x, st)
+        g2.launch(st)
+        assert np.array_equal(own.x.download(np.float32, 64 * 2048, st).reshape(64, 2048), y_own)
+    assert parity(y_own, y_host_scan)[1] <= 5e-3  # the two sequences differ by the rounding of rows and shared-expert weights to bf16
     assert device_error_word() == 0
+
+
+def test_moe_group_matches_count_scan_permute(st, layers):
+    """drb_moe_group against numpy: counts, exclusive scan, a valid slot assignment (every expert's slots are its
+    range, each used once), row_of inverse of slot_of; an expert-parallel slice (e_lo, e_n) marks foreign pairs -1."""
+    l = ffi.lib()
+    rng = np.random.Generator(np.random.PCG64(5))
+    for rows, topk, e, e_lo, e_n in ((300, 8, 256, 0, 256), (1, 8, 256, 0, 256), (77, 4, 64, 16, 32), (513, 8, 1024, 0, 1024)):
+        idx = np.stack([rng.permutation(e)[:topk] for _ in range(rows)]).astype(np.int32)
+        didx = DevBuf.from_array(idx, st)
+        dc, do, ds, dr = DevBuf(e_n * 4), DevBuf(e_n * 4), DevBuf(rows * topk * 4), DevBuf(rows * topk * 4)
+        dr.fill(0xFF, st)
+        launched(l.drb_moe_group(didx.at(0), rows, topk, e_lo, e_n, dc.at(0), do.at(0), ds.at(0), dr.at(0), st.raw), "moe_group")
+        counts, offsets = dc.download(np.int32, e_n, st), do.download(np.int32, e_n, st)
+        slot_of, row_of = ds.download(np.int32, rows * topk, st), dr.download(np.int32, rows * topk, st)
+        local = idx.reshape(-1) - e_lo
+        mine = (local >= 0) & (local < e_n)
+        assert np.array_equal(counts, np.bincount(local[mine], minlength=e_n))
+        assert np.array_equal(offsets, np.cumsum(counts) - counts)
+        assert (slot_of[~mine] == -1).all()
+        s = slot_of[mine]
+        assert np.array_equal(np.sort(s), np.arange(mine.sum()))
+        assert ((s >= offsets[local[mine]]) & (s < offsets[local[mine]] + counts[local[mine]])).all()
+        assert np.array_equal(row_of[s], np.nonzero(mine)[0] // topk)
+    assert l.drb_moe_group(didx.at(0), 1, 8, 0, 2048, dc.at(0), do.at(0), ds.at(0), dr.at(0), st.raw) == -1
+
+
+def test_moe_prefill_outliers_beyond_fp16_range_stay_finite(st, layers):
+    """The tensor-core operands are fp16: a row with values above 65504 is clamped, not turned into infinities."""
+    host, dev = layers(2)
+    x = synth.make_x(9, 8, 2048)
+    pre = MoePrefill(dev, 8, st=st)
+    y0 = pre.run(x)
+    # overwrite the normalised rows with outliers of 7e4 and -9e4 and run everything behind the routing
+    l = ffi.lib()
+    pre.x.upload(x, st)
+    pre.route_device(8)
+    pre.rows_f16 = False  # bf16 rows can hold such values; the fp16 operands they are converted to cannot
+    pre.route_device(8)
+    hb = synth.bf16_bits_to_f32(pre.hn_b.download(np.uint16, 8 * 2048, st)).reshape(8, 2048)
+    hb[3, 100] = 7e4
+    hb[3, 101] = -9e4
+    pre.hn_b.upload(synth.f32_to_bf16_bits(hb), st)
+    launched(l.drb_moe_group(pre.idx.at(0), 8, 8, 0, 256, pre.counts.at(0), pre.offsets.at(0), pre.slot_of.at(0), pre.row_of.at(0), st.raw), "group")
+    gq, gs = dev.gate_up.expert(0)
+    dq, ds = dev.down.expert(0)
+    sgq, sgs = dev.shared_gate_up.rows(0)
+    sdq, sds = dev.shared_down.rows(0)
+    launched(l.drb_moe_prefill_block(gq, gs, dq, ds, sgq, sgs, sdq, sds, pre.hn_b.at(0), pre.row_of.at(0), pre.offsets.at(0), pre.counts.at(0),
+                                     pre.ap.at(0), pre.yp.at(0), pre.sh_act_b.at(0), pre.sh_out.at(0), 8, 256, 2048, 512, 0, st.raw), "block")
+    sh = pre.sh_out.download(np.float32, 8 * 2048, st)
+    yp = pre.yp.download(np.float32, 64 * 2048, st)
+    assert np.isfinite(sh).all() and np.isfinite(yp).all()
+    assert np.isfinite(y0).all() and device_error_word() == 0
 
 
 def test_moe_prefill_zipf_300(st, layers):
@@ -334,7 +462,7 @@ def test_moe_prefill_zipf_300(st, layers):
     bias = synth.zipf_router_bias(33, 256, 1.1)
     pre = MoePrefill(dev, 300, st=st)
     y = pre.run(x, logit_bias=bias)
-    xh = orc.round_bf16(orc.rmsnorm(x, host["post_norm"], 1e-6))
+    xh = orc.rmsnorm(x, host["post_norm"], 1e-6).astype(np.float16).astype(np.float32)  # the rows as the own sequence keeps them
     out, idx, wts, sgate, logits = orc.moe_block(host, xh.astype(np.float64), 8, np.float64, logit_bias=bias)
     got_idx = pre.idx.download(np.int32, 300 * 8, st).reshape(300, 8)
     margin = orc.route_margin(logits, 256, 8)
@@ -342,5 +470,5 @@ def test_moe_prefill_zipf_300(st, layers):
     assert np.array_equal(got_idx[safe], idx[safe]) and safe.mean() > 0.99
     counts = pre.counts.download(np.int32, 256, st)
     assert counts.sum() == 2400 and np.array_equal(counts, orc.moe_count(got_idx, 256))
-    assert_parity((y - x)[safe], out[safe], "prefill zipf 300", max_abs=np.inf, rel_l2=REL_PREFILL)
+    assert_parity((y - x)[safe], out[safe], "prefill zipf 300", **prefill_bar(out[safe]))
     assert device_error_word() == 0
