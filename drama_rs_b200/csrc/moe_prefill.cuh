@@ -69,20 +69,31 @@ __global__ void __launch_bounds__(256)
 // rows is ever written. e_lo / e_n restrict the grouping to experts [e_lo, e_lo + e_n) (an expert-parallel rank's
 // slice; pairs of other experts get slot -1); local expert ids are e - e_lo.
 constexpr int GRP_THREADS = 1024, GRP_MAX_E = 1024;
+// With cap > 0 the pairs are what an expert-parallel rank received: `world` blocks of blk_rows rows of row_ints
+// 32-bit words each; block b holds cap row slots followed by the cap expert ids of those rows (one int each, the
+// region padded to whole rows). Pair j = (block j / cap, slot j % cap); its id is read from the block's id region,
+// row_of[slot] is the row's index in the buffer (in rows), pair_of[slot] = j. cap = 0: idx is a plain array,
+// row_of[slot] = pair / topk, pair_of is not written.
 __global__ void __launch_bounds__(GRP_THREADS)
     k_group(const int* __restrict__ idx, int pairs, int topk, int e_lo, int e_n, int* __restrict__ counts,
-            int* __restrict__ offsets, int* __restrict__ slot_of, int* __restrict__ row_of) {
+            int* __restrict__ offsets, int* __restrict__ slot_of, int* __restrict__ row_of, int* __restrict__ pair_of,
+            int cap, int blk_rows, int row_ints) {
   pdl_wait();
   __shared__ int cnt[GRP_MAX_E];
   __shared__ int offs[GRP_MAX_E];
   __shared__ int warp_tot[GRP_THREADS / 32];
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  auto expert_of = [&](int p) {
+    if (cap <= 0) return __ldg(idx + p);
+    const int b = p / cap, i = p - b * cap;
+    return __ldcg(idx + ((size_t)b * blk_rows + cap) * row_ints + i);
+  };
   for (int i = t; i < e_n; i += GRP_THREADS) cnt[i] = 0;
   __syncthreads();
   // rank of every pair among its expert's pairs (the order inside an expert is arbitrary: every slot is computed
   // independently and the combine step sums in a fixed order)
   for (int p = t; p < pairs; p += GRP_THREADS) {
-    const int e = __ldg(idx + p) - e_lo;
+    const int e = expert_of(p) - e_lo;
     slot_of[p] = (e >= 0 && e < e_n) ? atomicAdd(&cnt[e], 1) : -1;
   }
   __syncthreads();
@@ -114,13 +125,70 @@ __global__ void __launch_bounds__(GRP_THREADS)
   }
   __syncthreads();
   for (int p = t; p < pairs; p += GRP_THREADS) {
-    const int e = __ldg(idx + p) - e_lo;
+    const int e = expert_of(p) - e_lo;
     if (e >= 0 && e < e_n) {
       const int slot = offs[e] + slot_of[p];
       slot_of[p] = slot;
-      row_of[slot] = p / topk;
+      if (cap <= 0) {
+        row_of[slot] = p / topk;
+      } else {
+        const int b = p / cap;
+        row_of[slot] = b * blk_rows + (p - b * cap);
+        pair_of[slot] = p;
+      }
     }
   }
+}
+
+// Expert-parallel dispatch, sender side, step 1 (one block): every (row, k) pair gets a slot in the block of the rank
+// that owns its expert. send is `world` blocks of blk_rows rows of row_ints words (layout as in k_group); the pair's
+// local expert id goes to the block's id region, unused slots get the id `per` (one past the owner's last expert:
+// the owner's grouping skips them). slot_of[pair] = owner * cap + slot (what the combine step indexes the returned
+// results with), dst_row[pair] = the row of `send` that the pair's row must be copied to (-1: dropped).
+// A pair that finds its block full is dropped, its slot_of points at a valid slot of the block, and *overflow is set:
+// the step's result is then void and the caller must repeat it with a larger capacity. Nothing waits or faults.
+__global__ void __launch_bounds__(GRP_THREADS)
+    k_ep_plan(const int* __restrict__ idx, int pairs, int per, int world, int cap, int blk_rows, int row_ints,
+              int* __restrict__ send, int* __restrict__ slot_of, int* __restrict__ dst_row, unsigned* __restrict__ overflow) {
+  pdl_wait();
+  __shared__ int cnt[64];
+  const int t = threadIdx.x;
+  if (t < 64) cnt[t] = 0;
+  __syncthreads();
+  for (int p = t; p < pairs; p += GRP_THREADS) {
+    const int e = __ldg(idx + p);
+    const int o = e / per;
+    const int r = atomicAdd(&cnt[o], 1);
+    if (r < cap) {
+      send[((size_t)o * blk_rows + cap) * row_ints + r] = e - o * per;
+      slot_of[p] = o * cap + r;
+      dst_row[p] = o * blk_rows + r;
+    } else {
+      atomicExch(overflow, 1u);
+      slot_of[p] = o * cap;
+      dst_row[p] = -1;
+    }
+  }
+  __syncthreads();
+  for (int j = t; j < world * cap; j += GRP_THREADS) {
+    const int o = j / cap, r = j - o * cap;
+    if (r >= cnt[o]) send[((size_t)o * blk_rows + cap) * row_ints + r] = per;
+  }
+}
+
+// Step 2: one warp per pair copies its row (row_bytes each, 16-byte accesses) to its place in the send buffer.
+__global__ void __launch_bounds__(256)
+    k_ep_scatter(const unsigned char* __restrict__ rows, int pairs, int topk, const int* __restrict__ dst_row,
+                 unsigned char* __restrict__ send, int row_bytes) {
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int p = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (p >= pairs) return;
+  const int d = __ldg(dst_row + p);
+  if (d < 0) return;
+  const uint4* src = reinterpret_cast<const uint4*>(rows + (size_t)(p / topk) * row_bytes);
+  uint4* dst = reinterpret_cast<uint4*>(send + (size_t)d * row_bytes);
+  for (int c = lane; c < row_bytes / 16; c += 32) dst[c] = __ldg(src + c);
 }
 
 // x[r] += sigmoid(sgate[r]) * shared[r] + sum_k w[r,k] * Y[slot_of[r,k]], k ascending (fixed order, so
@@ -313,6 +381,8 @@ static cudaError_t configure_all() {
   if ((e = drb_carveout(k_permute)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_combine)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_group)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_ep_plan)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_ep_scatter)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_dequant_q8)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_f32_to_bf16)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_swiglu_rows)) != cudaSuccess) return e;
@@ -396,9 +466,9 @@ extern "C" int dr_moe_prefill(const uint8_t* gu_q, const __half2* gu_sm, const u
   if (!dev.ready) return -2;
   const dim3 grid(pfmma::BLOCKS_PER_SM * dev.sms), block(pfmma::THREADS);
   drb_launch(pfmma::k_grouped<0, 0, false>, grid, block, pfmma::SMEM_BYTES, st, false, gu_q, (const void*)gu_sm, (const void*)xp,
-             (void*)act, offsets, counts, E, pfmma::SharedExpert{}, (const int*)nullptr, 0);
+             (void*)act, offsets, counts, E, pfmma::SharedExpert{}, (const int*)nullptr, 0, (const int*)nullptr);
   drb_launch(pfmma::k_grouped<1, 0, false>, grid, block, pfmma::SMEM_BYTES, st, false, d_q, (const void*)d_sm, (const void*)act,
-             (void*)y, offsets, counts, E, pfmma::SharedExpert{}, (const int*)nullptr, 0);
+             (void*)y, offsets, counts, E, pfmma::SharedExpert{}, (const int*)nullptr, 0, (const int*)nullptr);
   return 0;
 }
 
@@ -410,7 +480,38 @@ extern "C" int drb_moe_group(const int* idx, int rows, int topk, int e_lo, int e
                              int* row_of, cudaStream_t st) {
   if (e_n <= 0 || e_n > pf::GRP_MAX_E || topk <= 0) return -1;
   drb_launch(pf::k_group, dim3(1), dim3(pf::GRP_THREADS), 0, st, false, idx, rows * topk, topk, e_lo, e_n, counts, offsets,
-             slot_of, row_of);
+             slot_of, row_of, (int*)nullptr, 0, 0, 0);
+  return 0;
+}
+
+// Expert parallelism (no counterpart in the reference, which is single-GPU). Rows travel between ranks in a buffer of
+// `world` blocks; a block is blk_rows = cap + ceil(4 cap / row_bytes) rows of row_bytes bytes: cap row slots, then the
+// cap local expert ids of those rows (int32), padded to whole rows. One collective moves rows and ids together.
+//   drb_ep_pack    sender: places this rank's (row, k) pairs (idx [rows, topk], experts per rank `per`) into `send`,
+//                  slot_of [rows * topk] = owner * cap + slot for the combine step, dst_row [rows * topk] scratch.
+//                  *overflow (device word, zeroed by the caller) is set when a block was full: the result is void then.
+//   drb_ep_group   owner: groups the received world * cap pairs by local expert: counts / offsets [per],
+//                  slot_of [world * cap] scratch, row_of [slot] = row of `recv` (operand gather of the grouped GEMM),
+//                  pair_of [slot] = position of the pair in receive order (where the result row goes).
+// row_bytes % 16 == 0, world <= 64, per <= 1024; -1 otherwise.
+extern "C" int drb_ep_block_rows(int cap, int row_bytes) { return cap + (4 * cap + row_bytes - 1) / row_bytes; }
+extern "C" int drb_ep_pack(const void* rows, const int* idx, int n_rows, int topk, int per, int world, int cap, int row_bytes,
+                           void* send, int* slot_of, int* dst_row, unsigned* overflow, cudaStream_t st) {
+  if (row_bytes % 16 != 0 || world <= 0 || world > 64 || per <= 0 || cap <= 0 || topk <= 0) return -1;
+  const int pairs = n_rows * topk;
+  const int blk_rows = drb_ep_block_rows(cap, row_bytes);
+  drb_launch(pf::k_ep_plan, dim3(1), dim3(pf::GRP_THREADS), 0, st, false, idx, pairs, per, world, cap, blk_rows, row_bytes / 4,
+             (int*)send, slot_of, dst_row, overflow);
+  if (pairs > 0)
+    drb_launch(pf::k_ep_scatter, dim3((pairs + 7) / 8), dim3(256), 0, st, false, (const unsigned char*)rows, pairs, topk,
+               (const int*)dst_row, (unsigned char*)send, row_bytes);
+  return 0;
+}
+extern "C" int drb_ep_group(const void* recv, int world, int cap, int row_bytes, int per, int* counts, int* offsets, int* slot_of,
+                            int* row_of, int* pair_of, cudaStream_t st) {
+  if (row_bytes % 16 != 0 || world <= 0 || per <= 0 || per > pf::GRP_MAX_E || cap <= 0) return -1;
+  drb_launch(pf::k_group, dim3(1), dim3(pf::GRP_THREADS), 0, st, false, (const int*)recv, world * cap, 1, 0, per, counts, offsets,
+             slot_of, row_of, pair_of, cap, drb_ep_block_rows(cap, row_bytes), row_bytes / 4);
   return 0;
 }
 
@@ -419,23 +520,29 @@ extern "C" int drb_moe_group(const int* idx, int rows, int topk, int e_lo, int e
 // order, [rows, H], bf16 or with x_f16 != 0 fp16; nothing is permuted) and (b) the shared expert as one more expert that owns every row, its
 // int8 weights dequantised into the same tensor-core tiles (sh_act: fp16 scratch [rows, I]; sh_out: f32 [rows, H]).
 // The reference runs the shared expert through cuBLAS on weights dequantised to bf16 (src/engine.rs:351-355, 560-562);
-// here no library GEMM and no bf16 copy of the weights is involved. rows_sh = 0 skips the shared expert. Limits as dr_moe_prefill.
+// here no library GEMM and no bf16 copy of the weights is involved. rows_sh = 0 skips the shared expert, E = 0 the
+// routed ones. y_row_of (or NULL): slot -> row of y for the routed results. Limits as dr_moe_prefill.
+// Every pointer of a part that runs must be a valid device address; with E = 0 or rows_sh = 0 the arrays of the part
+// that does not run are not used, but must still be valid addresses (any buffer will do, NULL will not): the compiler
+// may issue a load ahead of the branch that decides whether its value is needed. row_of and y_row_of may be NULL.
 extern "C" int drb_moe_prefill_block(const uint8_t* gu_q, const __half2* gu_sm, const uint8_t* d_q, const __half2* d_sm,
                                      const int8_t* sgu_q, const __half* sgu_s, const int8_t* sd_q, const __half* sd_s,
                                      const __nv_bfloat16* xb, const int* row_of, const int* offsets, const int* counts,
                                      __nv_bfloat16* act, float* y, __nv_bfloat16* sh_act, float* sh_out, int rows_sh, int E,
-                                     int H, int I, int x_f16, cudaStream_t st) {
+                                     int H, int I, int x_f16, const int* y_row_of, cudaStream_t st) {
   if (H != pf::H || I != pf::I) return -1;
   if (E <= 0 && rows_sh <= 0) return 0;
+  if (!gu_q || !gu_sm || !d_q || !d_sm || !sgu_q || !sgu_s || !sd_q || !sd_s || !xb || !offsets || !counts || !act || !y || !sh_act || !sh_out)
+    return -1;
   const DrbDevice& dev = drb_device(st);
   if (!dev.ready) return -2;
   const dim3 grid(pfmma::BLOCKS_PER_SM * dev.sms), block(pfmma::THREADS);
   const pfmma::SharedExpert s0{sgu_q, sgu_s, (const void*)xb, (void*)sh_act, rows_sh};
   const pfmma::SharedExpert s1{sd_q, sd_s, (const void*)sh_act, (void*)sh_out, rows_sh};
   drb_launch(pfmma::k_grouped<0, 0, true>, grid, block, pfmma::SMEM_BYTES, st, false, gu_q, (const void*)gu_sm, (const void*)xb,
-             (void*)act, offsets, counts, E, s0, row_of, x_f16);
+             (void*)act, offsets, counts, E, s0, row_of, x_f16, (const int*)nullptr);
   drb_launch(pfmma::k_grouped<1, 0, true>, grid, block, pfmma::SMEM_BYTES, st, false, d_q, (const void*)d_sm, (const void*)act,
-             (void*)y, offsets, counts, E, s1, (const int*)nullptr, 1);
+             (void*)y, offsets, counts, E, s1, (const int*)nullptr, 1, y_row_of);
   return 0;
 }
 
@@ -449,9 +556,9 @@ extern "C" int dr_moe_prefill_fp8(const uint8_t* gu_w, const float* gu_s, const 
   if (!dev.ready) return -2;
   const dim3 grid(pfmma::BLOCKS_PER_SM * dev.sms), block(pfmma::THREADS);
   drb_launch(pfmma::k_grouped<0, 1, false>, grid, block, pfmma::SMEM_BYTES, st, false, gu_w, (const void*)gu_s, (const void*)xp,
-             (void*)act, offsets, counts, E, pfmma::SharedExpert{}, (const int*)nullptr, 0);
+             (void*)act, offsets, counts, E, pfmma::SharedExpert{}, (const int*)nullptr, 0, (const int*)nullptr);
   drb_launch(pfmma::k_grouped<1, 1, false>, grid, block, pfmma::SMEM_BYTES, st, false, d_w, (const void*)d_s, (const void*)act,
-             (void*)y, offsets, counts, E, pfmma::SharedExpert{}, (const int*)nullptr, 0);
+             (void*)y, offsets, counts, E, pfmma::SharedExpert{}, (const int*)nullptr, 0, (const int*)nullptr);
   return 0;
 }
 

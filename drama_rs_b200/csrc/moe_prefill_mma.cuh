@@ -242,7 +242,7 @@ template <int GEMM, int FMT = 0, bool SH = false>
 __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
     k_grouped(const uint8_t* __restrict__ Q, const void* __restrict__ SMv, const void* __restrict__ src, void* __restrict__ dst,
               const int* __restrict__ offsets, const int* __restrict__ counts, int E, SharedExpert sh,
-              const int* __restrict__ row_of, int src_f16) {
+              const int* __restrict__ row_of, int src_f16, const int* __restrict__ dst_row_of) {
   const __half2* SM = static_cast<const __half2*>(SMv);  // FMT 0
   const float* SF = static_cast<const float*>(SMv);      // FMT 1
   constexpr int K = GEMM == 0 ? H : I;
@@ -496,7 +496,13 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
             float* y = static_cast<float*>(adst);
 #pragma unroll
             for (int i = 0; i < 16; ++i)
-              if (c0 + i < nt) y[(size_t)(off + n0 + c0 + i) * H + mt * TILE_M + r] = __uint_as_float(v[i]);
+              if (c0 + i < nt) {
+                // dst_row_of (down projection of the routed experts only): slot -> row of y, so that the results land where
+                // their consumer wants them (an expert-parallel rank: in the order the rows arrived)
+                const int slot = off + n0 + c0 + i;
+                const int row = (!shd && dst_row_of) ? __ldg(dst_row_of + slot) : slot;
+                y[(size_t)row * H + mt * TILE_M + r] = __uint_as_float(v[i]);
+              }
           }
         }
         tc_fence_before();

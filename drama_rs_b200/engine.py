@@ -277,7 +277,7 @@ class MoePrefill:
         launched(
             l.drb_moe_prefill_block(gq, gs, dq, ds, sgq, sgs, sdq, sds, self.hn_b.at(0), self.row_of.at(0), self.offsets.at(0),
                                     self.counts.at(0), self.ap.at(0), self.yp.at(0), self.sh_act_b.at(0), self.sh_out.at(0), n, e, h, i,
-                                    1 if self.rows_f16 else 0, st), "moe_prefill_block")
+                                    1 if self.rows_f16 else 0, NULL, st), "moe_prefill_block")
         launched(
             l.dr_moe_combine(self.x.at(0), self.yp.at(0), self.slot_of.at(0), self.wts.at(0), self.sgate.at(0),
                              self.sh_out.at(0), n, topk, h, st), "moe_combine")

@@ -62,7 +62,10 @@ SIGNATURES: dict[str, tuple] = {
     "drb_moe_stack_decode": (I32, [P, I32, P, P, I32, I32, I32, I32, F32, P, P, P]),
     "drb_moe_offsets": (I32, [P, I32, P, P]),
     "drb_moe_group": (I32, [P, I32, I32, I32, I32, P, P, P, P, P]),
-    "drb_moe_prefill_block": (I32, [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I32, I32, I32, I32, I32, P]),
+    "drb_moe_prefill_block": (I32, [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I32, I32, I32, I32, I32, P, P]),
+    "drb_ep_block_rows": (I32, [I32, I32]),
+    "drb_ep_pack": (I32, [P, P, I32, I32, I32, I32, I32, I32, P, P, P, P, P]),
+    "drb_ep_group": (I32, [P, I32, I32, I32, I32, P, P, P, P, P, P]),
     "drb_rmsnorm_f16": (I32, [P, P, P, I32, I32, F32, P]),
     "drb_router_logits_f16": (I32, [P, P, P, I32, I32, I32, F32, P]),
     "drb_router_logits": (I32, [P, P, P, I32, I32, I32, F32, P]),

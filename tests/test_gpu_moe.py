@@ -449,7 +449,7 @@ def test_moe_prefill_outliers_beyond_fp16_range_stay_finite(st, layers):
     sgq, sgs = dev.shared_gate_up.rows(0)
     sdq, sds = dev.shared_down.rows(0)
     launched(l.drb_moe_prefill_block(gq, gs, dq, ds, sgq, sgs, sdq, sds, pre.hn_b.at(0), pre.row_of.at(0), pre.offsets.at(0), pre.counts.at(0),
-                                     pre.ap.at(0), pre.yp.at(0), pre.sh_act_b.at(0), pre.sh_out.at(0), 8, 256, 2048, 512, 0, st.raw), "block")
+                                     pre.ap.at(0), pre.yp.at(0), pre.sh_act_b.at(0), pre.sh_out.at(0), 8, 256, 2048, 512, 0, NULL, st.raw), "block")
     sh = pre.sh_out.download(np.float32, 8 * 2048, st)
     yp = pre.yp.download(np.float32, 64 * 2048, st)
     assert np.isfinite(sh).all() and np.isfinite(yp).all()
