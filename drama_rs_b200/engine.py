@@ -182,8 +182,9 @@ class MoePrefill:
     the dequantised int8 matrices."""
 
     def __init__(self, layer: MoeLayer, max_rows: int, topk: int = 8, eps: float = 1e-6, st: Stream | None = None,
-                 reference_calls: bool = False) -> None:
-        self.l = ffi.lib()
+                 reference_calls: bool = False, lib=None) -> None:
+        """lib: another library with the same ABI (ffi.bind) to issue the launches to (reference_calls only)."""
+        self.l = lib or ffi.lib()
         self.st = st or Stream()
         self.layer, self.topk, self.eps, self.max_rows = layer, topk, eps, max_rows
         self.reference_calls = reference_calls
