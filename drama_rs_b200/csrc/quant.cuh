@@ -1,8 +1,12 @@
 // Checkpoint quantisers on the GPU: the reference's converter (tools/convert.py) turns bf16/fp8 expert weights
 // into the int4 / int8 layouts the kernels stream. These two kernels restate its per-group procedures operation by
 // operation in IEEE fp32 (no fused multiply-add, round-to-nearest division, fp16 rounding of scale and min), so that
-// codes and scales come out as the reference writes them; only the order of the 64-term error sums differs (a warp
-// butterfly here), which can change the pick between two candidates whose errors agree to the last bits.
+// codes and scales come out as the reference writes them. That includes the ORDER of the 64-term sums that decide
+// between two clipping candidates: eight running sums over the inputs 8 i + j (i ascending), then
+// ((r0 + r1) + (r2 + r3)) + ((r4 + r5) + (r6 + r7)): the order of the CPU restatement of the converter, which
+// reproduces the converter's own output on the committed fixture bit for bit. (The converter's sums are a library's
+// vectorised reduction whose exact order depends on the host's vector width; where two candidates' errors agree to
+// the last bit, its pick is not defined by its source.)
 //
 //   drb_quant_q4: tools/convert.py:44-89 (`quant_q4_groups`: 24-step clipping search, least-squares refit) and
 //                 92-101 (`quant_q4`: packing, low nibble = even k). One warp per group of 64 inputs.
@@ -21,10 +25,20 @@ __constant__ float c_shrink[STEPS] = {1.0f,        0.97916669f, 0.95833331f, 0.9
 
 DRB_DEV float half_round(float v) { return __half2float(__float2half_rn(v)); }
 
-DRB_DEV float warp_sum_all(float v) {
+// Sum of the group's 64 values in the converter's order; lane l passes inputs 2l (a) and 2l + 1 (b), every lane
+// gets the total. Running sum j collects inputs j, 8 + j, 16 + j, ...: those of lanes j / 2, j / 2 + 4, ...
+DRB_DEV float sum64(float a, float b) {
+  const int p = threadIdx.x & 3;
+  float r0 = __shfl_sync(0xffffffffu, a, p), r1 = __shfl_sync(0xffffffffu, b, p);  // running sums 2p and 2p + 1
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
+  for (int i = 1; i < 8; ++i) {
+    r0 = __fadd_rn(r0, __shfl_sync(0xffffffffu, a, p + 4 * i));
+    r1 = __fadd_rn(r1, __shfl_sync(0xffffffffu, b, p + 4 * i));
+  }
+  const float pr = __fadd_rn(r0, r1);                                       // r[2p] + r[2p + 1]
+  const float q = __fadd_rn(__shfl_sync(0xffffffffu, pr, 0), __shfl_sync(0xffffffffu, pr, 1));  // (r0 + r1) + (r2 + r3)
+  const float h = __fadd_rn(__shfl_sync(0xffffffffu, pr, 2), __shfl_sync(0xffffffffu, pr, 3));  // (r4 + r5) + (r6 + r7)
+  return __fadd_rn(q, h);
 }
 
 // Lane l holds inputs 2l and 2l + 1 of the group.
@@ -53,15 +67,15 @@ __global__ void __launch_bounds__(256) k_quant_q4(const float* __restrict__ w, s
     const float q1 = fminf(fmaxf(rintf(__fdiv_rn(__fsub_rn(v.y, lo_h), scale_h)), 0.f), 15.f);
     const float d0 = __fsub_rn(__fadd_rn(__fmul_rn(q0, scale_h), lo_h), v.x);
     const float d1 = __fsub_rn(__fadd_rn(__fmul_rn(q1, scale_h), lo_h), v.y);
-    const float err = warp_sum_all(__fadd_rn(__fmul_rn(d0, d0), __fmul_rn(d1, d1)));
+    const float err = sum64(__fmul_rn(d0, d0), __fmul_rn(d1, d1));
     if (i == 0 || err < best_err) best_err = err, best_scale = scale_h, best_lo = lo_h, bq0 = q0, bq1 = q1;
   }
   // One least-squares refinement of (scale, min) given the codes.
   const float n = 64.f;
-  const float sq = warp_sum_all(__fadd_rn(bq0, bq1));
-  const float sqq = warp_sum_all(__fadd_rn(__fmul_rn(bq0, bq0), __fmul_rn(bq1, bq1)));
-  const float sw = warp_sum_all(__fadd_rn(v.x, v.y));
-  const float sqw = warp_sum_all(__fadd_rn(__fmul_rn(bq0, v.x), __fmul_rn(bq1, v.y)));
+  const float sq = sum64(bq0, bq1);
+  const float sqq = sum64(__fmul_rn(bq0, bq0), __fmul_rn(bq1, bq1));
+  const float sw = sum64(v.x, v.y);
+  const float sqw = sum64(__fmul_rn(bq0, v.x), __fmul_rn(bq1, v.y));
   const float det = __fsub_rn(__fmul_rn(n, sqq), __fmul_rn(sq, sq));
   const bool ok = fabsf(det) > 1e-6f;
   const float ls_scale = ok ? __fdiv_rn(__fsub_rn(__fmul_rn(n, sqw), __fmul_rn(sq, sw)), det) : best_scale;
@@ -69,7 +83,7 @@ __global__ void __launch_bounds__(256) k_quant_q4(const float* __restrict__ w, s
   const float ls_scale_h = half_round(ls_scale), ls_min_h = half_round(ls_min);
   const float e0 = __fsub_rn(__fadd_rn(__fmul_rn(bq0, ls_scale_h), ls_min_h), v.x);
   const float e1 = __fsub_rn(__fadd_rn(__fmul_rn(bq1, ls_scale_h), ls_min_h), v.y);
-  const float ls_err = warp_sum_all(__fadd_rn(__fmul_rn(e0, e0), __fmul_rn(e1, e1)));
+  const float ls_err = sum64(__fmul_rn(e0, e0), __fmul_rn(e1, e1));
   if (ls_err < best_err && ok && ls_scale_h > 0.f) best_scale = ls_scale_h, best_lo = ls_min_h;
   q[g * 32 + lane] = (uint8_t)((unsigned)bq0 | ((unsigned)bq1 << 4));
   if (lane == 0) sm[g] = __halves2half2(__float2half_rn(best_scale), __float2half_rn(best_lo));

@@ -22,19 +22,45 @@ struct TensorInfo {
   size_t begin = 0, end = 0;
 };
 
+inline size_t dtype_bytes(const std::string& dtype) {
+  if (dtype == "U8" || dtype == "I8" || dtype == "BOOL" || dtype == "F8_E4M3" || dtype == "F8_E5M2") return 1;
+  if (dtype == "F16" || dtype == "BF16" || dtype == "I16" || dtype == "U16") return 2;
+  if (dtype == "F32" || dtype == "I32" || dtype == "U32") return 4;
+  if (dtype == "F64" || dtype == "I64" || dtype == "U64") return 8;
+  return 0;
+}
+
+// Every tensor of the header is validated before anything is read: its byte range must lie inside the file, in order,
+// and be exactly as long as its shape and dtype say. A truncated or malformed file is refused here, on the host; what
+// reaches the device always has the size the kernels assume.
 class SafeTensors {
  public:
   explicit SafeTensors(const std::string& path) : path_(path) {
-    std::ifstream f(path, std::ios::binary);
+    std::ifstream f(path, std::ios::binary | std::ios::ate);
     if (!f) throw std::runtime_error("cannot open " + path);
+    const uint64_t file_size = (uint64_t)f.tellg();
+    f.seekg(0);
     uint64_t n = 0;
     f.read(reinterpret_cast<char*>(&n), 8);
-    if (!f || n == 0 || n > (1u << 26)) throw std::runtime_error(path + ": bad safetensors header length");
+    if (!f || n == 0 || n > (1u << 26) || 8 + n > file_size) throw std::runtime_error(path + ": bad safetensors header length");
     std::string js(n, '\0');
     f.read(js.data(), (std::streamsize)n);
     if (!f) throw std::runtime_error(path + ": truncated header");
     data0_ = 8 + n;
     parse(js);
+    const uint64_t data_bytes = file_size - data0_;
+    for (const auto& kv : tensors_) {
+      const TensorInfo& t = kv.second;
+      const size_t esz = dtype_bytes(t.dtype);
+      if (esz == 0) throw std::runtime_error(path + ": " + kv.first + ": unknown dtype " + t.dtype);
+      uint64_t count = 1;
+      for (size_t d : t.shape) {
+        if (d != 0 && count > (uint64_t(1) << 48) / d) throw std::runtime_error(path + ": " + kv.first + ": shape overflows");
+        count *= d;
+      }
+      if (t.begin > t.end || t.end > data_bytes) throw std::runtime_error(path + ": " + kv.first + ": data range outside the file (truncated?)");
+      if (t.end - t.begin != count * esz) throw std::runtime_error(path + ": " + kv.first + ": data size does not match shape and dtype");
+    }
   }
 
   const TensorInfo& info(const std::string& name) const {
@@ -55,49 +81,66 @@ class SafeTensors {
 
  private:
   // The header is flat enough for a hand scanner: top-level keys map to objects with three known members.
+  // Every access is bounded: running off the end of the header is a parse error, never a read past the string.
   void parse(const std::string& s) {
     size_t p = 0;
-    auto skip = [&] { while (p < s.size() && (s[p] == ' ' || s[p] == '\n' || s[p] == '\t' || s[p] == ',' || s[p] == ':')) ++p; };
+    auto fail = [&]() -> void { throw std::runtime_error(path_ + ": header parse error"); };
+    auto at = [&]() -> char {
+      if (p >= s.size()) fail();
+      return s[p];
+    };
+    auto skip = [&] { while (p < s.size() && (s[p] == ' ' || s[p] == '\n' || s[p] == '\t' || s[p] == '\r' || s[p] == ',' || s[p] == ':')) ++p; };
     auto str = [&] {
-      if (s[p] != '"') throw std::runtime_error(path_ + ": header parse error");
-      size_t q = ++p;
-      while (p < s.size() && s[p] != '"') p += (s[p] == '\\') ? 2 : 1;
+      if (at() != '"') fail();
+      const size_t q = ++p;
+      while (at() != '"') {
+        p += (s[p] == '\\') ? 2 : 1;
+        if (p > s.size()) fail();
+      }
       std::string out = s.substr(q, p - q);
       ++p;
       return out;
     };
     auto numbers = [&] {
       std::vector<size_t> out;
-      if (s[p] != '[') throw std::runtime_error(path_ + ": header parse error");
+      if (at() != '[') fail();
       ++p;
       for (;;) {
         skip();
-        if (s[p] == ']') { ++p; return out; }
+        if (at() == ']') { ++p; return out; }
+        if (s[p] < '0' || s[p] > '9') fail();
         size_t v = 0;
-        while (p < s.size() && s[p] >= '0' && s[p] <= '9') v = v * 10 + (size_t)(s[p++] - '0');
+        while (p < s.size() && s[p] >= '0' && s[p] <= '9') {
+          if (v > (~size_t(0) - 9) / 10) fail();
+          v = v * 10 + (size_t)(s[p++] - '0');
+        }
         out.push_back(v);
       }
     };
     skip();
-    if (s[p] != '{') throw std::runtime_error(path_ + ": header parse error");
+    if (at() != '{') fail();
     ++p;
     for (;;) {
       skip();
       if (p >= s.size() || s[p] == '}') return;
       const std::string name = str();
       skip();
-      if (s[p] != '{') throw std::runtime_error(path_ + ": header parse error");
+      if (at() != '{') fail();
       ++p;
       TensorInfo t;
       for (;;) {
         skip();
-        if (s[p] == '}') { ++p; break; }
+        if (at() == '}') { ++p; break; }
         const std::string key = str();
         skip();
         if (key == "dtype") t.dtype = str();
         else if (key == "shape") t.shape = numbers();
-        else if (key == "data_offsets") { auto v = numbers(); t.begin = v.at(0), t.end = v.at(1); }
-        else if (s[p] == '"') str();  // "__metadata__": {"k": "v"}
+        else if (key == "data_offsets") {
+          auto v = numbers();
+          if (v.size() != 2) fail();
+          t.begin = v[0], t.end = v[1];
+        }
+        else if (at() == '"') str();  // "__metadata__": {"k": "v"}
         else throw std::runtime_error(path_ + ": unexpected header member " + key);
       }
       if (name != "__metadata__") tensors_[name] = std::move(t);
@@ -108,6 +151,16 @@ class SafeTensors {
   size_t data0_ = 0;
   std::map<std::string, TensorInfo> tensors_;
 };
+
+// CRC-32 (IEEE, reflected) of a tensor's bytes: what `--inspect` prints so that a host-side check can compare values.
+inline uint32_t crc32_bytes(const std::vector<char>& v) {
+  uint32_t c = 0xFFFFFFFFu;
+  for (char ch : v) {
+    c ^= (uint8_t)ch;
+    for (int k = 0; k < 8; ++k) c = (c >> 1) ^ (0xEDB88320u & (0u - (c & 1u)));
+  }
+  return ~c;
+}
 
 inline DevBuf upload_checked(const SafeTensors& f, const std::string& name, const char* dtype, const std::vector<size_t>& shape,
                              const Stream& st) {

@@ -1,5 +1,5 @@
 // Command-line driver of the C++ host: batch-1 decode through a stack of MoE layers.
-//   moe_decode_main --inspect layer00.safetensors      (no GPU: prints the MoE tensors' dtypes and shapes)
+//   moe_decode_main --inspect layer00.safetensors      (no GPU: prints the MoE tensors' dtypes, shapes, sizes and CRC-32s)
 //   moe_decode_main --x x.f32 --out-eager a.f32 --out-graph b.f32 [--steps N] [--topk 8] [--eps 1e-6] layer00.safetensors ...
 // Runs one eager step from x, then captures the step and replays it `steps` times from x again; writes the hidden
 // state after the eager step and after the last replay, and prints the per-step time of the replays.
@@ -42,7 +42,7 @@ int main(int argc, char** argv) try {
         const drama::TensorInfo& t = f.info(name);
         std::cout << name << " " << t.dtype;
         for (size_t d : t.shape) std::cout << " " << d;
-        std::cout << " bytes=" << (t.end - t.begin) << "\n";
+        std::cout << " bytes=" << (t.end - t.begin) << " crc32=" << drama::crc32_bytes(f.read(name)) << "\n";
       }
       return 0;
     }

@@ -26,14 +26,10 @@ def test_inspect_reads_safetensors_header(tmp_path):
     t = synth.make_layer(11, SHAPE)
     path = str(tmp_path / "layer00.safetensors")
     save_layer_safetensors(t, path)
-    out = subprocess.run([_binary(), "--inspect", path], capture_output=True, text=True, check=True).stdout.splitlines()
-    seen = {}
-    for line in out:
-        name, dtype, *rest = line.split()
-        seen[name] = (dtype, [int(v) for v in rest[:-1]], int(rest[-1].split("=")[1]))
+    seen = _inspect(path)
     names = {"uint8": "U8", "int8": "I8", "float16": "F16", "float32": "F32", "uint16": "BF16"}
     for k in LAYER_TENSORS:
-        dtype, shape, nbytes = seen[k]
+        dtype, shape, nbytes, _ = seen[k]
         assert dtype == names[t[k].dtype.name], k
         assert shape == list(t[k].shape), k
         assert nbytes == t[k].nbytes, k
@@ -47,6 +43,70 @@ def test_inspect_rejects_missing_tensor(tmp_path):
     save_file({"moe.router": torch.zeros(4, 4)}, path)
     r = subprocess.run([_binary(), "--inspect", path], capture_output=True, text=True)
     assert r.returncode == 1 and "missing tensor" in r.stderr
+
+
+def _inspect(path):
+    out = subprocess.run([_binary(), "--inspect", path], capture_output=True, text=True, check=True).stdout.splitlines()
+    seen = {}
+    for line in out:
+        name, dtype, *rest = line.split()
+        seen[name] = (dtype, [int(v) for v in rest[:-2]], int(rest[-2].split("=")[1]), int(rest[-1].split("=")[1]))
+    return seen
+
+
+def test_cpp_loader_reads_the_converter_written_layer():
+    """The layer file written by the reference's own converter (tests/golden/ckpt_tiny): the C++ loader sees the same
+    dtypes, shapes and bytes (CRC-32) as the Python loader."""
+    import zlib
+
+    from drama_rs_b200.model import load_layer_safetensors
+
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ckpt_tiny", "layer00.safetensors")
+    seen = _inspect(path)
+    t = load_layer_safetensors(path)
+    names = {"uint8": "U8", "int8": "I8", "float16": "F16", "float32": "F32", "uint16": "BF16"}
+    for k in LAYER_TENSORS:
+        dtype, shape, nbytes, crc = seen[k]
+        assert dtype == names[t[k].dtype.name] and shape == list(t[k].shape) and nbytes == t[k].nbytes, k
+        assert crc == zlib.crc32(np.ascontiguousarray(t[k]).tobytes()), k
+
+
+def test_cpp_loader_refuses_truncated_and_inconsistent_files(tmp_path):
+    """A file cut short, a tensor whose byte range does not match its shape, offsets in the wrong order and a header
+    that ends inside an array are all refused on the host with an error, before anything could reach the device."""
+    import json
+    import struct
+
+    t = synth.make_layer(11, synth.MoeShape(experts=2))
+    good = str(tmp_path / "good.safetensors")
+    save_layer_safetensors(t, good)
+    raw = open(good, "rb").read()
+    n = struct.unpack("<Q", raw[:8])[0]
+    header = json.loads(raw[8:8 + n])
+
+    def write(name, hdr, body):
+        js = json.dumps(hdr, separators=(",", ":")).encode() if isinstance(hdr, dict) else hdr
+        p = str(tmp_path / name)
+        with open(p, "wb") as f:
+            f.write(struct.pack("<Q", len(js)) + js + body)
+        return p
+
+    cases = {}
+    cases["truncated"] = write("truncated.safetensors", header, raw[8 + n:-4096])
+    h2 = json.loads(json.dumps(header))
+    h2["moe.down.q4"]["shape"][0] += 1  # right offsets, wrong shape
+    cases["size"] = write("size.safetensors", h2, raw[8 + n:])
+    h3 = json.loads(json.dumps(header))
+    b, e = h3["post_norm"]["data_offsets"]
+    h3["post_norm"]["data_offsets"] = [e, b]
+    cases["order"] = write("order.safetensors", h3, raw[8 + n:])
+    js = json.dumps(header, separators=(",", ":")).encode()
+    cut = js[: js.index(b'"shape":[') + 12]  # the header ends inside an array
+    cases["header"] = write("header.safetensors", cut, raw[8 + n:])
+    for what, p in cases.items():
+        r = subprocess.run([_binary(), "--inspect", p], capture_output=True, text=True, timeout=20)
+        assert r.returncode == 1 and "moe_decode_main:" in r.stderr, (what, r.stderr)
+    assert subprocess.run([_binary(), "--inspect", good], capture_output=True, text=True).returncode == 0
 
 
 @pytest.mark.gpu

@@ -37,12 +37,10 @@ def test_gpu_quantisers_match_reference_converter():
     launched(l.drb_quant_q4(dw.at(0), C.c_size_t(groups), dq.at(0), dsm.at(0), st.raw), "quant_q4")
     q = dq.download(np.uint8, groups * 32, st).reshape(g["q4"].shape)
     sm = dsm.download(np.float16, groups * 2, st).reshape(g["sm"].shape)
-    same = (q == g["q4"]).reshape(groups, 32).all(axis=1) & (sm.view(np.uint16) == g["sm"].view(np.uint16)).reshape(groups, 2).all(axis=1)
-    # the error sums run in a different order: a pick between two candidates of equal error may differ, nothing else
-    assert same.mean() >= 0.99, same.mean()
-    e_ref = ((qo.dequant_q4(g["q4"], g["sm"]) - w) ** 2).reshape(groups, 64).sum(1)
-    e_gpu = ((qo.dequant_q4(q, sm) - w) ** 2).reshape(groups, 64).sum(1)
-    assert (e_gpu <= e_ref * (1 + 1e-5) + 1e-12).all()
+    # bit for bit the converter's output: codes, scales and mins of every group (the 64-term sums that pick between
+    # clipping candidates run in the converter's order)
+    assert np.array_equal(q, g["q4"])
+    assert np.array_equal(sm.view(np.uint16), g["sm"].view(np.uint16))
     w8 = np.ascontiguousarray(g["w8"], dtype=np.float32)
     g8 = w8.size // 128
     dw8, dq8, ds8 = DevBuf.from_array(w8, st), DevBuf(w8.size), DevBuf(g8 * 2)
