@@ -20,49 +20,6 @@
 // The library is one translation unit, so the definition lives here.
 __device__ unsigned int g_drb_error = 0;
 
-// Optional timing probes for development builds (-DDRB_TRACE): block 0 records the global timer at
-// numbered points of a kernel into g_drb_trace. Compiled out of the product build.
-#ifdef DRB_TRACE
-__device__ unsigned long long g_drb_trace[64];
-__device__ unsigned long long g_drb_trace_blk[256 * 16];
-#define DRB_TRACE_BLK(i, tid)                                                     \
-  do {                                                                            \
-    if (threadIdx.x == (tid) && blockIdx.x < 256) {                               \
-      unsigned long long t_;                                                      \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                      \
-      g_drb_trace_blk[blockIdx.x * 16 + (i)] = t_;                                \
-    }                                                                             \
-  } while (0)
-#define DRB_TRACE_POINT(i, tid)                                                   \
-  do {                                                                            \
-    if (blockIdx.x == 0 && threadIdx.x == (tid)) {                                \
-      unsigned long long t_;                                                      \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                      \
-      g_drb_trace[(i)] = t_;                                                      \
-    }                                                                             \
-  } while (0)
-#define DRB_TRACE_ANY(i, tid)                                                     \
-  do {                                                                            \
-    if (threadIdx.x == (tid)) {                                                   \
-      unsigned long long t_;                                                      \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                      \
-      g_drb_trace[(i)] = t_;                                                      \
-    }                                                                             \
-  } while (0)
-#elif defined(DRB_TRACE_MODE) && DRB_TRACE_MODE == 1
-#define DRB_TRACE_POINT(i, tid) do { if (threadIdx.x == (tid)) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); } } while (0)
-#define DRB_TRACE_ANY(i, tid) ((void)0)
-#define DRB_TRACE_BLK(i, tid) DRB_TRACE_POINT(i, tid)
-#elif defined(DRB_TRACE_MODE) && DRB_TRACE_MODE == 2
-#define DRB_TRACE_POINT(i, tid) asm volatile("" ::: "memory")
-#define DRB_TRACE_ANY(i, tid) ((void)0)
-#define DRB_TRACE_BLK(i, tid) ((void)0)
-#else
-#define DRB_TRACE_POINT(i, tid) ((void)0)
-#define DRB_TRACE_ANY(i, tid) ((void)0)
-#define DRB_TRACE_BLK(i, tid) ((void)0)
-#endif
-
 enum DrbError : unsigned int {
   DRB_OK = 0,
   DRB_ERR_FULL_WAIT = 1,   // a consumer gave up waiting for a bulk copy to land
@@ -116,9 +73,6 @@ DRB_DEV void mbar_init(uint64_t* bar, unsigned count) {
 DRB_DEV void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 
 DRB_DEV void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
-#ifdef DRB_STACK_SKELETON
-  return;
-#endif
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 
@@ -138,10 +92,10 @@ DRB_DEV bool mbar_try_wait(uint64_t* bar, unsigned parity) {
   return ok != 0;
 }
 
-// Bounded wait: about a second of polling at most, then the error word is set and the caller
-// continues with whatever is in shared memory.
-DRB_DEV bool mbar_wait(uint64_t* bar, unsigned parity, unsigned err_code) {
-  for (unsigned it = 0; it < (1u << 22); ++it) {
+// Bounded wait: `limit` polls (by default about a second's worth), then the error word is set and the
+// caller continues with whatever is in shared memory.
+DRB_DEV bool mbar_wait(uint64_t* bar, unsigned parity, unsigned err_code, unsigned limit = 1u << 22) {
+  for (unsigned it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (it > 64) __nanosleep(it > 4096 ? 256 : 32);
   }
@@ -151,9 +105,6 @@ DRB_DEV bool mbar_wait(uint64_t* bar, unsigned parity, unsigned err_code) {
 
 // Global -> shared bulk copy. dst, src 16-byte aligned; bytes a multiple of 16.
 DRB_DEV void bulk_g2s(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
-#ifdef DRB_STACK_SKELETON
-  return;
-#endif
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                    smem_u32(dst)),
                "l"(src), "r"(bytes), "r"(smem_u32(bar))
@@ -303,7 +254,7 @@ DRB_DEV unsigned long long dot8_bf16(const uint4& v, const unsigned long long* x
 // kernel as block fixed point: x_k = delta * n_k with |n_k| <= 2^20 and delta = max|x| * 2^-20 over
 // the slice, n_k split into three signed limbs n = l0 + 128 l1 + 16384 l2 (l0, l1 in [-64, 63]).
 // A weight word then costs one dp4a per limb, four multiply-adds each, accumulated exactly in
-// int32; the three sums are recombined in integer and converted to fp32 once per 16-byte chunk.
+// int32; the three sums are recombined and converted to fp32 once per 16-byte chunk.
 // Quantisation error of an activation is at most delta / 2 = 2^-21 of the slice's largest value
 // (fp32 itself carries 2^-24 of each value), and nothing is rounded during accumulation.
 
@@ -437,7 +388,12 @@ DRB_DEV void qact_load(QAct<16, false>& a, const unsigned char* blk) {
   a.delta = *reinterpret_cast<const float*>(blk + 48);
 }
 
+// 32 int4 products: |sum| <= 32 * 15 * 2^20 < 2^29, the integer recombination cannot overflow.
 DRB_DEV float recombine(int a0, int a1, int a2) { return (float)(a0 + (a1 << 7) + (a2 << 14)); }
+// int8 weights: 32 products of magnitude up to 128 * 2^20 reach 2^32 (a constant slice against weights of one
+// sign does it), so the top limb's sum joins in fp32. |a0| + |a1 << 7| < 2^26 stays an integer sum; a2 is below
+// 2^19 and exact as a float; the one rounding is 2^-24 of the result, as every fp32 sum has.
+DRB_DEV float recombine_wide(int a0, int a1, int a2) { return fmaf((float)a2, 16384.f, (float)(a0 + (a1 << 7))); }
 
 // sum_k q_k n_k over one 16-byte chunk of int4 weights (32 nibbles, k ascending) against words
 // [w0, w0 + 8) of an even/odd-ordered slice. Multiply by delta (and the group scale) afterwards.
@@ -466,7 +422,7 @@ DRB_DEV float dot16_q8_i(const uint4& v, const QAct<N, false>& a, int w0) {
     a1 = dp4a_ss(w[i], a.l[1][w0 + i], a1);
     a2 = dp4a_ss(w[i], a.l[2][w0 + i], a2);
   }
-  return recombine(a0, a1, a2);
+  return recombine_wide(a0, a1, a2);
 }
 
 // The same for an even/odd-ordered slice: two weight words are first regrouped into their even and odd bytes.
@@ -482,7 +438,7 @@ DRB_DEV float dot32_q8_eo(const uint4& v0, const uint4& v1, const QAct<N, true>&
     a1 = dp4a_ss(ev, a.l[1][w0 + 2 * i], a1), a1 = dp4a_ss(od, a.l[1][w0 + 2 * i + 1], a1);
     a2 = dp4a_ss(ev, a.l[2][w0 + 2 * i], a2), a2 = dp4a_ss(od, a.l[2][w0 + 2 * i + 1], a2);
   }
-  return recombine(a0, a1, a2);
+  return recombine_wide(a0, a1, a2);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -3,7 +3,6 @@
 #include "common.cuh"
 #include "runtime.cuh"
 #include "gemv.cuh"
-#include "chain.cuh"
 #include "router.cuh"
 #include "moe_decode.cuh"
 #include "moe_decode_static.cuh"

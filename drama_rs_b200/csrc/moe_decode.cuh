@@ -56,10 +56,7 @@ constexpr int UNITS = 32;                                 // units (gate row + u
 constexpr int ROUTED_BLOCKS = TOPK * I / UNITS;           // 128
 constexpr int SHARED_BLOCKS = I / UNITS;                  // 16
 constexpr int GRID = ROUTED_BLOCKS + SHARED_BLOCKS;       // 144
-#ifndef DRB_GU_PARTS
-#define DRB_GU_PARTS 4
-#endif
-constexpr int QUARTERS = DRB_GU_PARTS, QU = UNITS / QUARTERS;  // the block's rows arrive in parts of QU units, one mbarrier each
+constexpr int QUARTERS = 4, QU = UNITS / QUARTERS;  // the block's rows arrive in parts of QU units, one mbarrier each
 constexpr int QROW = H / 2;                               // 1024 bytes of nibbles per routed row
 constexpr int SMROW = (H / 64) * 4;                       // 128 bytes of (scale, min) per routed row
 constexpr int SSROW = (H / 128) * 2;                      // 32 bytes of scales per shared-expert row
@@ -128,19 +125,10 @@ DRB_DEV void quant_block16_halfwarps(float v, unsigned char* dst, int lane) {
 // [32 (b - 128), +32) of the shared expert (64 int8 rows, 130 KB; they do not depend on the routing and are requested
 // before the dependency wait, so these larger blocks finish first). The rows arrive in four parts of 8 units with one
 // mbarrier each; warp w computes units w and w + 16, i.e. parts w / 8 and 2 + w / 8.
-// CH = true (chained sequence): with have_prev the routing and the hidden state are read from this block's replica in
-// the workspace instead of idx and x.
-template <bool CH>
 __global__ void __launch_bounds__(THREADS, 1)
     k_moe_gate_up(const uint8_t* __restrict__ Q, const __half2* __restrict__ SM, const int8_t* __restrict__ shq,
                   const __half* __restrict__ shs, const float* __restrict__ x, const int* __restrict__ idx,
-                  unsigned char* __restrict__ actq, const float* __restrict__ nw, float eps, float* __restrict__ ws,
-                  int have_prev, const uint8_t* __restrict__ DQ, const __half2* __restrict__ DSM,
-                  const int8_t* __restrict__ dshq, const char* pf, size_t pf_bytes) {
-  if (CH && have_prev) {
-    idx = reinterpret_cast<const int*>(ws + chainws::OFF_ROUTE + (blockIdx.x % chainws::ROUTE_REPS) * chainws::ROUTE_STRIDE);
-    x = ws + chainws::OFF_YREP + (blockIdx.x % chainws::VEC_REPS) * chainws::HID;
-  }
+                  unsigned char* __restrict__ actq, const float* __restrict__ nw, float eps) {
   extern __shared__ __align__(128) unsigned char dyn[];
   Ctl& ctl = *reinterpret_cast<Ctl*>(dyn);
   unsigned char* qx = dyn + CTL_BYTES;
@@ -149,7 +137,6 @@ __global__ void __launch_bounds__(THREADS, 1)
   const int b = blockIdx.x;
   const bool shared = b >= ROUTED_BLOCKS;
   const int j0 = shared ? (b - ROUTED_BLOCKS) * UNITS : (b % (I / UNITS)) * UNITS;  // first unit
-  DRB_TRACE_POINT(10, 0);
 
   if (threadIdx.x == 0) {
     for (int q = 0; q < QUARTERS; ++q) mbar_init(&ctl.full[q], 1);
@@ -159,7 +146,6 @@ __global__ void __launch_bounds__(THREADS, 1)
 
   if (warp == CW) {
     // ---------------- producer warp: lane 4 q + c requests copy c (gate rows, up rows, gate scales, up scales) of part q
-    if (lane == 31) prefetch_share(pf, pf_bytes, blockIdx.x, gridDim.x);  // constants of a later kernel (chained: the next router)
     const int q = lane >> 2, c = lane & 3;
     const bool issuing = q < QUARTERS;
     if (shared) {
@@ -176,7 +162,6 @@ __global__ void __launch_bounds__(THREADS, 1)
       pdl_wait();
     } else {
       pdl_wait();  // idx is the router's output
-      DRB_TRACE_POINT(11, CW * 32);
       if (issuing && c == 0) mbar_expect_tx(&ctl.full[q], (unsigned)(2 * QU * (QROW + SMROW)));
       __syncwarp();
       if (issuing) {
@@ -190,19 +175,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         else bulk_g2s(st + (size_t)2 * UNITS * QROW + (UNITS + l0) * SMROW, smp + ((size_t)I + u0) * SMROW, QU * SMROW, &ctl.full[q]);
       }
     }
-    DRB_TRACE_POINT(12, CW * 32);
     pdl_launch_dependents();  // never before the wait: the down kernel's prologue reads the router's idx
-    // The down kernel cannot start while this one holds the registers, so its weights are warmed into L2 from
-    // here: once this block's own rows have landed (the warm-up must not compete with them), each of the first
-    // 17 lanes asks for this block's 1/gridDim share of one region of the down projection.
-    if (DQ) {
-      if (lane < QUARTERS) mbar_wait(&ctl.full[lane], 0, DRB_ERR_FULL_WAIT);
-      __syncwarp();
-      constexpr size_t DQ_BYTES = (size_t)H * (I / 2), DSM_BYTES = (size_t)H * (I / 64) * 4, DSH_BYTES = (size_t)H * I;
-      if (lane < TOPK) prefetch_share(reinterpret_cast<const char*>(DQ) + (size_t)__ldcg(idx + lane) * DQ_BYTES, DQ_BYTES, blockIdx.x, gridDim.x);
-      else if (lane < 2 * TOPK) prefetch_share(reinterpret_cast<const char*>(DSM) + (size_t)__ldcg(idx + lane - TOPK) * DSM_BYTES, DSM_BYTES, blockIdx.x, gridDim.x);
-      else if (lane == 2 * TOPK) prefetch_share(reinterpret_cast<const char*>(dshq), DSH_BYTES, blockIdx.x, gridDim.x);
-    }
     return;
   }
 
@@ -211,14 +184,7 @@ __global__ void __launch_bounds__(THREADS, 1)
   const float4 wv = nw ? reinterpret_cast<const float4*>(nw)[threadIdx.x] : make_float4(1.f, 1.f, 1.f, 1.f);
   pdl_wait();               // x is the previous kernel's output
   pdl_launch_dependents();
-  DRB_TRACE_POINT(13, 0);
   const float4 xv = __ldcg(reinterpret_cast<const float4*>(x) + threadIdx.x);
-#ifdef DRB_TRACE
-  {
-    asm volatile("" ::"f"(xv.x));
-    DRB_TRACE_POINT(18, 0);
-  }
-#endif
   float inv = 1.f;
   if (nw) {
     const float ss = warp_sum(xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w);
@@ -237,7 +203,6 @@ __global__ void __launch_bounds__(THREADS, 1)
   float X0, X1;
   qact_load(x0, X0, qx + (size_t)lane * QB32_BYTES);
   qact_load(x1, X1, qx + (size_t)(32 + lane) * QB32_BYTES);
-  DRB_TRACE_POINT(14, 0);
 
   // v[2i] = gate, v[2i + 1] = up partial sums of this warp's unit warp + 16 i
   float v[4];
@@ -284,7 +249,6 @@ __global__ void __launch_bounds__(THREADS, 1)
     if (shared) quant_block16_halfwarps(a, actq + ACTQ_SHARED + (size_t)(b - ROUTED_BLOCKS) * 2 * QB16_BYTES, lane);
     else quant_block32_warp(a, actq + (size_t)b * QB32_BYTES, lane);
   }
-  DRB_TRACE_POINT(17, 0);
 }
 
 }  // namespace gu
@@ -312,44 +276,16 @@ static_assert(RT == CW, "one shared-expert row per consumer warp");
 struct Ctl {
   uint64_t full;
   float part[TOPK + 1][RT];
-  float xs[RT];   // CHAIN: this block's new hidden values times the next layer's norm weight
-  float ysq[RT];  // CHAIN: their squares
   float wk[TOPK]; // the routing weights and the shared expert's gate, fetched once per block
   float sgate;
-  int last;       // CHAIN: this block was the last to add its shares
-  float tail[2];  // CHAIN: the shared gate's logit and the sum of squares, for the last block
-  int ridx[32];
-  float rwts[32];
 };
 static_assert(sizeof(Ctl) <= CTL_BYTES, "control block too large");
 
-// What a chained launch adds: the next layer's router matrix [e_next + 1, H] (bf16), its norm weight, and where
-// this block's partial logits go: partials[block][c], c < e_next + 1 the partial dot products of router row c with
-// (new hidden state * norm weight) over this block's rows, c = e_next + 1 the partial sum of squares.
-struct Chain {
-  const __nv_bfloat16* w;  // nullptr: last layer of the chain, nothing to prepare
-  const float* nw;
-  float* ws;               // the chain workspace (chain.cuh)
-  int e_next;
-  int have_prev;           // the routing is read from the workspace replicas instead of idx / wts / sgate
-  float eps;
-  int* idx_out;            // where the next layer's routing goes (the caller's idx / wts / sgate, and logits or nullptr)
-  float* wts_out;
-  float* sgate_out;
-  float* logits_out;
-};
-
-// CHAIN = true: the activations come from this block's replica in the workspace, the new hidden state is also
-// written to the workspace replicas, and (chain.w != nullptr) the block writes its share of the NEXT layer's router logits (the logits are linear in
-// the hidden state; the 1 / rms factor is applied by the kernel that sums the shares, router::k_router_tail).
-// The router rows are fetched before the dependency wait, so the next layer's routing costs no matrix read after
-// this kernel and no second pass over the hidden state.
-template <bool CHAIN>
 __global__ void __launch_bounds__(THREADS, 1)
     k_moe_down(const uint8_t* __restrict__ Q, const __half2* __restrict__ SM, const int8_t* __restrict__ shq,
                const __half* __restrict__ shs, const unsigned char* __restrict__ actq, const int* __restrict__ idx,
                const float* __restrict__ wts, const float* __restrict__ sgate, const float* res, float* y,
-               const char* pf, size_t pf_bytes, Chain chain) {
+               const char* pf, size_t pf_bytes) {
   extern __shared__ __align__(128) unsigned char dyn[];
   Ctl& ctl = *reinterpret_cast<Ctl*>(dyn);
   unsigned char* qa = dyn + CTL_BYTES;
@@ -358,23 +294,13 @@ __global__ void __launch_bounds__(THREADS, 1)
   const unsigned G = gridDim.x, b = blockIdx.x;
   const int n0 = (int)((long long)H * b / G), n1 = (int)((long long)H * (b + 1) / G);
   const int nr = n1 - n0;  // <= RT because the grid has at least MIN_GRID blocks
-  DRB_TRACE_POINT(20, 0);
-  const bool chain_out = CHAIN && chain.w != nullptr;
-  if (CHAIN) {
-    if (chain.have_prev) {
-      const float* rep = chain.ws + chainws::OFF_ROUTE + (b % chainws::ROUTE_REPS) * chainws::ROUTE_STRIDE;
-      idx = reinterpret_cast<const int*>(rep), wts = rep + 8, sgate = rep + 16;
-    }
-  }
 
   if (threadIdx.x == 0) {
     mbar_init(&ctl.full, 1);
     mbar_fence_init();
   }
   __syncthreads();
-#ifndef DRB_D_LATE
   pdl_launch_dependents();
-#endif
 
   if (warp == CW) {
     // ---------------- producer warp. This kernel is only ever launched behind k_moe_gate_up, which lets its
@@ -392,7 +318,6 @@ __global__ void __launch_bounds__(THREADS, 1)
         bulk_g2s(st + TOPK * EXPERT_BYTES, shq + (size_t)n0 * I, (unsigned)(nr * I), &ctl.full);
       }
     }
-    DRB_TRACE_POINT(21, CW * 32);
     if (lane == 0) prefetch_share(pf, pf_bytes, b, G);
     return;
   }
@@ -401,29 +326,7 @@ __global__ void __launch_bounds__(THREADS, 1)
   const int ke = warp & (TOPK - 1), rh = warp >> 3;
   // The shared expert's scales are constants: fetched before the dependency wait.
   const float ssc = warp < nr ? __half2float(__ldg(shs + (size_t)(n0 + warp) * (I / 128) + (lane >> 3))) : 0.f;
-  float wn[RT];     // CHAIN: router row threadIdx.x of the next layer, columns n0 .. n0 + nr
-  float nwn = 0.f;  // CHAIN: the next layer's norm weight of row n0 + threadIdx.x
-  if (CHAIN) {
-#pragma unroll
-    for (int i = 0; i < RT; ++i) wn[i] = 0.f;
-    if (chain_out) {
-      // a chained launch has exactly H / RT blocks: the block's 16 columns of a router row are 32 aligned bytes
-      if ((int)threadIdx.x <= chain.e_next) {
-        const uint4* wr = reinterpret_cast<const uint4*>(chain.w + (size_t)threadIdx.x * H + n0);
-        const uint4 a = __ldg(wr), c = __ldg(wr + 1);
-        const uint32_t w8[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) wn[2 * i] = __uint_as_float(w8[i] << 16), wn[2 * i + 1] = __uint_as_float(w8[i] & 0xffff0000u);
-      }
-      if ((int)threadIdx.x < nr) nwn = __ldg(chain.nw + n0 + threadIdx.x);
-    }
-    if (threadIdx.x < RT) ctl.xs[threadIdx.x] = 0.f, ctl.ysq[threadIdx.x] = 0.f;
-  }
   pdl_wait();  // the activations, and everything the caller wrote before
-#ifdef DRB_D_LATE
-  pdl_launch_dependents();
-#endif
-  DRB_TRACE_POINT(22, 0);
   // The block copies the 16 KB of activations once (read at L2: they were written while this block may already
   // have been resident, so nothing of them may come from this multiprocessor's L1), together with the routing
   // weights; then half-warps take alternate rows, lane & 15 = 16-byte chunk cc of the row, k in [32 cc, 32 cc + 32):
@@ -450,10 +353,8 @@ __global__ void __launch_bounds__(THREADS, 1)
   float wk[TOPK];
 #pragma unroll
   for (int k = 0; k < TOPK; ++k) wk[k] = ctl.wk[k];
-  DRB_TRACE_POINT(23, 0);
 
   mbar_wait(&ctl.full, 0, DRB_ERR_FULL_WAIT);
-  DRB_TRACE_POINT(24, 0);
   const unsigned char* eq = st + ke * EXPERT_BYTES;
   const unsigned char* esm = eq + RT * QROW;
   // This warp's four row pairs: pass p covers rows 2 (4 rh + p) + half.
@@ -495,91 +396,17 @@ __global__ void __launch_bounds__(THREADS, 1)
     for (int k = 0; k < TOPK; ++k) acc += wk[k] * ctl.part[k][lr];
     const float yn = __ldcg(res + n0 + lr) + sg * ctl.part[TOPK][lr] + acc;
     y[n0 + lr] = yn;
-    if (CHAIN) {
-      ctl.xs[lr] = yn * nwn, ctl.ysq[lr] = yn * yn;
-#pragma unroll
-      for (int c = 0; c < chainws::VEC_REPS; ++c) chain.ws[chainws::OFF_YREP + c * chainws::HID + n0 + lr] = yn;
-    }
   }
-  if (chain_out) {
-    named_sync<NT>();
-    unsigned long long* acc0 = reinterpret_cast<unsigned long long*>(chain.ws + chainws::OFF_ACC);
-    unsigned long long* accp = acc0 + (size_t)(b % chainws::ACC_REPS) * chainws::ACC_COLS;
-    unsigned* counter = reinterpret_cast<unsigned*>(chain.ws + chainws::OFF_COUNTER);
-    const int E = chain.e_next;
-    if ((int)threadIdx.x <= E) {
-      float acc = 0.f;
-#pragma unroll
-      for (int i = 0; i < RT; ++i) acc = fmaf(wn[i], ctl.xs[i], acc);
-      atomicAdd(accp + threadIdx.x, (unsigned long long)__double2ll_rn((double)acc * chainws::FX_LOGIT));
-    } else if ((int)threadIdx.x == E + 1) {
-      float acc = 0.f;
-#pragma unroll
-      for (int i = 0; i < RT; ++i) acc += ctl.ysq[i];
-      atomicAdd(accp + threadIdx.x, (unsigned long long)__double2ll_rn((double)acc * chainws::FX_SSQ));
-    }
-    DRB_TRACE_POINT(26, 0);
-    // The last block to arrive turns the totals into the next layer's routing.
-    __threadfence();
-    named_sync<NT>();
-    if (threadIdx.x == 0) ctl.last = atomicAdd(counter, 1u) == G - 1 ? 1 : 0;
-    named_sync<NT>();
-    if (!ctl.last || threadIdx.x >= 256) return;
-    __threadfence();
-    DRB_TRACE_ANY(51, 0);
-    const int e = threadIdx.x;
-    long long mine = 0, t = 0;
-#pragma unroll
-    for (int r = 0; r < chainws::ACC_REPS; ++r) mine += (long long)__ldcg(acc0 + r * chainws::ACC_COLS + e);
-#pragma unroll
-    for (int r = 0; r < chainws::ACC_REPS; ++r) acc0[r * chainws::ACC_COLS + e] = 0ull;
-    if (e < 2) {  // columns 256 and 257 exist only when E = 256; reading them is harmless otherwise
-#pragma unroll
-      for (int r = 0; r < chainws::ACC_REPS; ++r) t += (long long)__ldcg(acc0 + r * chainws::ACC_COLS + 256 + e);
-#pragma unroll
-      for (int r = 0; r < chainws::ACC_REPS; ++r) acc0[r * chainws::ACC_COLS + 256 + e] = 0ull;
-      if (256 + e == E) ctl.tail[0] = (float)((double)t * (1.0 / chainws::FX_LOGIT));
-      if (256 + e == E + 1) ctl.tail[1] = (float)((double)t * (1.0 / chainws::FX_SSQ));
-    }
-    if (e == E) ctl.tail[0] = (float)((double)mine * (1.0 / chainws::FX_LOGIT));
-    if (e == E + 1) ctl.tail[1] = (float)((double)mine * (1.0 / chainws::FX_SSQ));
-    if (e == 0) *counter = 0u;
-    asm volatile("bar.sync 2, 256;" ::: "memory");
-    const float inv = rsqrtf(ctl.tail[1] / (float)H + chain.eps);
-    const float v = e < E ? (float)((double)mine * (1.0 / chainws::FX_LOGIT)) * inv : -INFINITY;
-    const float sgn = ctl.tail[0] * inv;
-    if (chain.logits_out) {
-      if (e < E) chain.logits_out[e] = v;
-      if (e == 0) chain.logits_out[E] = sgn;
-    }
-    router::TopkSmem& tk = *reinterpret_cast<router::TopkSmem*>(st);  // the weight stage is free by now
-    router::softmax_topk<2>(v, E, TOPK, ctl.ridx, ctl.rwts, tk);
-    asm volatile("bar.sync 2, 256;" ::: "memory");
-    DRB_TRACE_ANY(53, 0);
-    if (e < TOPK) chain.idx_out[e] = ctl.ridx[e], chain.wts_out[e] = ctl.rwts[e];
-    if (e == 0) chain.sgate_out[0] = sgn;
-    {
-      float* rep = chain.ws + chainws::OFF_ROUTE + (size_t)(e >> 4) * chainws::ROUTE_STRIDE;
-      const int j = e & 15;
-      rep[j] = j < 8 ? __int_as_float(ctl.ridx[j]) : ctl.rwts[j - 8];
-      if (j == 0) rep[16] = sgn;
-    }
-  }
-  DRB_TRACE_POINT(25, 0);
 }
 
 }  // namespace dn
 
 static cudaError_t configure_all() {
-  cudaError_t e = cudaFuncSetAttribute(gu::k_moe_gate_up<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gu::SMEM_BYTES);
+  cudaError_t e = cudaFuncSetAttribute(gu::k_moe_gate_up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gu::SMEM_BYTES);
   if (e != cudaSuccess) return e;
-  if ((e = cudaFuncSetAttribute(gu::k_moe_gate_up<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gu::SMEM_BYTES)) != cudaSuccess) return e;
-  if ((e = drb_carveout(gu::k_moe_gate_up<true>)) != cudaSuccess) return e;
-  if ((e = cudaFuncSetAttribute(dn::k_moe_down<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dn::SMEM_BYTES)) != cudaSuccess) return e;
-  if ((e = cudaFuncSetAttribute(dn::k_moe_down<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dn::SMEM_BYTES)) != cudaSuccess) return e;
-  if ((e = drb_carveout(gu::k_moe_gate_up<false>)) != cudaSuccess) return e;
-  if ((e = drb_carveout(dn::k_moe_down<true>)) != cudaSuccess) return e;
-  return drb_carveout(dn::k_moe_down<false>);
+  if ((e = cudaFuncSetAttribute(dn::k_moe_down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dn::SMEM_BYTES)) != cudaSuccess) return e;
+  if ((e = drb_carveout(gu::k_moe_gate_up)) != cudaSuccess) return e;
+  return drb_carveout(dn::k_moe_down);
 }
 
 }  // namespace moe
@@ -598,48 +425,9 @@ extern "C" int dr_moe_decode(const uint8_t* gu_q, const __half2* gu_sm, const ui
   if (!dev.ready) return -2;
   const int g_gu = moe::gu::GRID;
   const int g_dn = dev.sms > moe::dn::MIN_GRID ? dev.sms : moe::dn::MIN_GRID;
-  drb_launch(moe::gu::k_moe_gate_up<false>, dim3(g_gu), dim3(moe::gu::THREADS), moe::gu::SMEM_BYTES, st, dev.pdl, gu_q, gu_sm,
-             sgu_q, sgu_s, x, idx, reinterpret_cast<unsigned char*>(act), nw, eps, (float*)nullptr, 0, (const uint8_t*)nullptr, d_sm, sd_q,
-             (const char*)nullptr, (size_t)0);
-  drb_launch(moe::dn::k_moe_down<false>, dim3(g_dn), dim3(moe::dn::THREADS), moe::dn::SMEM_BYTES, st, dev.pdl, d_q, d_sm, sd_q,
-             sd_s, reinterpret_cast<const unsigned char*>(act), idx, wts, sgate, res, y, pf, pf_bytes, moe::dn::Chain{});
+  drb_launch(moe::gu::k_moe_gate_up, dim3(g_gu), dim3(moe::gu::THREADS), moe::gu::SMEM_BYTES, st, dev.pdl, gu_q, gu_sm,
+             sgu_q, sgu_s, x, idx, reinterpret_cast<unsigned char*>(act), nw, eps);
+  drb_launch(moe::dn::k_moe_down, dim3(g_dn), dim3(moe::dn::THREADS), moe::dn::SMEM_BYTES, st, dev.pdl, d_q, d_sm, sd_q,
+             sd_s, reinterpret_cast<const unsigned char*>(act), idx, wts, sgate, res, y, pf, pf_bytes);
   return 0;
 }
-
-// No counterpart in the reference. dr_moe_decode as one link of a chain over consecutive MoE layers:
-//   * next_router != NULL: the down kernel also computes the NEXT layer's routing. Every block adds its share of
-//     next_router . (y * next_nw) and of sum(y^2) to fixed-point accumulators in the workspace (integer atomics: the
-//     totals do not depend on the order of arrival); the last block to arrive applies rsqrt(mean(y^2) + eps), runs
-//     softmax + top-k and OVERWRITES idx / wts / sgate (and logits, if given) with the next layer's routing, exactly
-//     what dr_router_topk(next_router, y, next_nw, ...) would write. The router rows are fetched while the kernel
-//     waits for its activations, so the next layer needs no router launch at all.
-//     next_router == NULL ends the chain (plain outputs only).
-//   * have_prev != 0: this layer's routing was produced by the previous chained call on the same workspace and x is
-//     that call's y: both are then read from the workspace's replicas (one per group of blocks) instead of
-//     idx / wts / sgate / x, which must still be passed and hold the same values.
-// workspace: drb_moe_chain_workspace_bytes() bytes, owned by the caller, zeroed once, private to one stream.
-// 8 <= e_next <= 256. Same limits and return codes as dr_moe_decode.
-extern "C" int drb_moe_decode_chained(const uint8_t* gu_q, const __half2* gu_sm, const uint8_t* d_q, const __half2* d_sm,
-                                      const int8_t* sgu_q, const __half* sgu_s, const int8_t* sd_q, const __half* sd_s,
-                                      const float* x, int* idx, float* wts, float* sgate, const float* res, float* act,
-                                      float* y, int H, int I, int topk, const float* nw, float eps,
-                                      const __nv_bfloat16* next_router, const float* next_nw, int e_next, float* logits,
-                                      float* workspace, int have_prev, cudaStream_t st) {
-  if (H != moe::H || I != moe::I || topk != moe::TOPK || !workspace) return -1;
-  if (next_router && (e_next < 8 || e_next > 256 || !next_nw)) return -1;
-  const DrbDevice& dev = drb_device(st);
-  if (!dev.ready) return -2;
-  const int g_gu = moe::gu::GRID;
-  const int g_dn = moe::dn::MIN_GRID;  // 16 rows per block: the block's columns of a router row are 32 aligned bytes
-  drb_launch(moe::gu::k_moe_gate_up<true>, dim3(g_gu), dim3(moe::gu::THREADS), moe::gu::SMEM_BYTES, st, dev.pdl, gu_q, gu_sm,
-             sgu_q, sgu_s, x, (const int*)idx, reinterpret_cast<unsigned char*>(act), nw, eps, workspace, have_prev,
-             (const uint8_t*)nullptr, d_sm, sd_q, reinterpret_cast<const char*>(next_router),
-             next_router ? (size_t)(e_next + 1) * moe::H * 2 : (size_t)0);
-  drb_launch(moe::dn::k_moe_down<true>, dim3(g_dn), dim3(moe::dn::THREADS), moe::dn::SMEM_BYTES, st, dev.pdl, d_q, d_sm, sd_q,
-             sd_s, reinterpret_cast<const unsigned char*>(act), (const int*)idx, (const float*)wts, (const float*)sgate, res, y,
-             (const char*)nullptr, (size_t)0,
-             moe::dn::Chain{next_router, next_nw, workspace, e_next, have_prev, eps, idx, wts, sgate, logits});
-  return 0;
-}
-
-extern "C" size_t drb_moe_chain_workspace_bytes(void) { return (size_t)chainws::TOTAL_FLOATS * sizeof(float); }

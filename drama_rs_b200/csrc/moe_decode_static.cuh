@@ -78,9 +78,9 @@ extern "C" int dr_moe_decode_static(const uint8_t* gu_q, const __half2* gu_sm, c
   const moe_static::PerDevice& pd = moe_static::g_dev[d];
   const int g_gu = moe::gu::GRID;
   const int g_dn = pd.sms > moe::dn::MIN_GRID ? pd.sms : moe::dn::MIN_GRID;
-  drb_launch(moe::gu::k_moe_gate_up<false>, dim3(g_gu), dim3(moe::gu::THREADS), moe::gu::SMEM_BYTES, st, pd.pdl, gu_q, gu_sm, sgu_q,
-             sgu_s, x, idx, reinterpret_cast<unsigned char*>(pd.act), nw, eps, (float*)nullptr, 0, (const uint8_t*)nullptr, d_sm, sd_q, (const char*)nullptr, (size_t)0);
-  drb_launch(moe::dn::k_moe_down<false>, dim3(g_dn), dim3(moe::dn::THREADS), moe::dn::SMEM_BYTES, st, pd.pdl, d_q, d_sm, sd_q, sd_s,
-             reinterpret_cast<const unsigned char*>(pd.act), idx, wts, sgate, res, y, pf, pf_bytes, moe::dn::Chain{nullptr, nullptr, nullptr, 0, 0});
+  drb_launch(moe::gu::k_moe_gate_up, dim3(g_gu), dim3(moe::gu::THREADS), moe::gu::SMEM_BYTES, st, pd.pdl, gu_q, gu_sm, sgu_q,
+             sgu_s, x, idx, reinterpret_cast<unsigned char*>(pd.act), nw, eps);
+  drb_launch(moe::dn::k_moe_down, dim3(g_dn), dim3(moe::dn::THREADS), moe::dn::SMEM_BYTES, st, pd.pdl, d_q, d_sm, sd_q, sd_s,
+             reinterpret_cast<const unsigned char*>(pd.act), idx, wts, sgate, res, y, pf, pf_bytes);
   return 0;
 }

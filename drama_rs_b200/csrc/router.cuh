@@ -94,7 +94,6 @@ DRB_DEV void softmax_topk_impl(float v, int E, int topk, int* __restrict__ idx, 
     if (w < nvalid) lo = min(lo, u);
   }
   const float m = ord_to_float(mo);
-  DRB_TRACE_ANY(40, 0);
   const float ex = e < E ? expf(v - m) : 0.f;
   const float ws = warp_sum(ex);
   if (lane == 0) sm.red[warp] = ws;
@@ -102,7 +101,6 @@ DRB_DEV void softmax_topk_impl(float v, int E, int topk, int* __restrict__ idx, 
   // the butterfly over the eight warp totals, written out: ((0+4)+(2+6)) + ((1+5)+(3+7))
   const float z = ((sm.red[0] + sm.red[4]) + (sm.red[2] + sm.red[6])) + ((sm.red[1] + sm.red[5]) + (sm.red[3] + sm.red[7]));
   const float p = e < E ? ex / z : -1.f;
-  DRB_TRACE_ANY(41, 0);
   const unsigned key = e < E ? __float_as_uint(p) + 1u : 0u;
   unsigned bound = 1u;  // every valid entry
   if (nvalid >= topk) bound = __float_as_uint(expf(ord_to_float(lo) - m) / z) + 1u;
@@ -112,7 +110,6 @@ DRB_DEV void softmax_topk_impl(float v, int E, int topk, int* __restrict__ idx, 
   const unsigned long long mine = ((unsigned long long)key << 32) | (unsigned)(~e);
   if (cand) sm.comp[warp * MAX_TOPK + __popc(bal & ((1u << lane) - 1u))] = mine;
   if (lane == 0) sm.cnt[warp] = __popc(bal);
-  DRB_TRACE_ANY(42, 0);
   topk_sync<BAR_ID>();
   // Warp 0 finishes alone. The survivors sit in (warp, lane) order, which is index order, so among equal keys
   // the earlier list position wins and 32-bit keys are all that has to travel.
@@ -164,7 +161,6 @@ DRB_DEV void softmax_topk_impl(float v, int E, int topk, int* __restrict__ idx, 
       }
     }
   }
-  DRB_TRACE_ANY(43, 0);
   __syncwarp();
   if (lane < topk) {
     float total = 0.f;
@@ -258,7 +254,6 @@ __global__ void __launch_bounds__(THREADS, 1)
   const unsigned rank = cluster_rank();
   const int row0 = rank * ROWS;
   const int nrows = max(0, min(ROWS, E + 1 - row0));
-  DRB_TRACE_POINT(0, 0);
   if (threadIdx.x == 0) {
     mbar_init(&ctl.full, 1);
     mbar_fence_init();
@@ -270,7 +265,6 @@ __global__ void __launch_bounds__(THREADS, 1)
   __syncthreads();
   pdl_launch_dependents();
   pdl_wait();  // x is the previous kernel's output
-  DRB_TRACE_POINT(1, 0);
 
   const float4 xa = __ldcg(reinterpret_cast<const float4*>(x) + threadIdx.x * 2), xb = __ldcg(reinterpret_cast<const float4*>(x) + threadIdx.x * 2 + 1);
   float inv = 1.f;
@@ -289,7 +283,6 @@ __global__ void __launch_bounds__(THREADS, 1)
   xs4[threadIdx.x * 2] = make_float4(xa.x * inv * wa.x, xa.y * inv * wa.y, xa.z * inv * wa.z, xa.w * inv * wa.w);
   xs4[threadIdx.x * 2 + 1] = make_float4(xb.x * inv * wb.x, xb.y * inv * wb.y, xb.z * inv * wb.z, xb.w * inv * wb.w);
   __syncthreads();
-  DRB_TRACE_POINT(2, 0);
   // Warp w takes rows w, w + 8, ...; lane l takes the 16-byte chunks l, l + 32, ... (8 weights each) of a row.
   unsigned long long xp[32];
 #pragma unroll
@@ -298,7 +291,6 @@ __global__ void __launch_bounds__(THREADS, 1)
     xp[4 * i] = pack2(a.x, a.y), xp[4 * i + 1] = pack2(a.z, a.w), xp[4 * i + 2] = pack2(b.x, b.y), xp[4 * i + 3] = pack2(b.z, b.w);
   }
   if (nrows > 0) mbar_wait(&ctl.full, 0, DRB_ERR_FULL_WAIT);
-  DRB_TRACE_POINT(3, 0);
   const uint32_t gather = map_to_rank(ctl.logits, 0);
   // Four rows at a time per warp (rows warp, warp + 8, ...): independent accumulators, one folded reduction.
   for (int rb = warp; rb < nrows; rb += 32) {
@@ -331,18 +323,15 @@ __global__ void __launch_bounds__(THREADS, 1)
     const int r = rb + 8 * (lane >> 3);  // lanes 0-7: row j = 0, 8-15: j = 1, 16-23: j = 2, 24-31: j = 3
     if ((lane & 7) == 0 && r < nrows) st_cluster_f32(gather + 4u * (unsigned)(row0 + r), sres);
   }
-  DRB_TRACE_POINT(4, 0);
   cluster_arrive();
   if (rank != 0) return;  // only block 0's shared memory is read from here on
   cluster_wait();
-  DRB_TRACE_POINT(5, 0);
   const int e = threadIdx.x;
   const float v = e < E ? ctl.logits[e] : -INFINITY;
   if (e < E) logits[e] = v;
   if (e == 0) logits[E] = ctl.logits[E];
   softmax_topk(v, E, topk, idx, wts, ctl.tk);
   if (threadIdx.x == 0) sgate[0] = ctl.logits[E];
-  DRB_TRACE_POINT(6, 0);
   if (gu_q && threadIdx.x < 32) {
     __syncwarp();
     // Pull exactly the chosen experts into L2: region `which` of expert idx[k], cut into bulk prefetches.

@@ -175,13 +175,3 @@ DRB_API int drb_grid_blocks(void) {
   cudaGetDevice(&d);
   return rt::g_dev[d].sms;
 }
-
-#ifdef DRB_TRACE
-// Development builds only: copies the timing probes out (nanoseconds of the global timer).
-DRB_API int drb_trace_read(unsigned long long* out, int n) {
-  return (int)cudaMemcpyFromSymbol(out, g_drb_trace, sizeof(unsigned long long) * (n < 64 ? n : 64));
-}
-DRB_API int drb_trace_blk_read(unsigned long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_drb_trace_blk, sizeof(unsigned long long) * 256 * 16);
-}
-#endif

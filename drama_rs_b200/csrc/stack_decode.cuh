@@ -87,17 +87,15 @@ constexpr int D_STAGE = TOPK * D_EXPERT + RT * I;  // 45,056
 // hand-over buffers
 constexpr int ACT_R_WORDS = 26;  // per routed block of 32 inputs: limbs [3][8] (even/odd order), delta, sum
 constexpr int ACT_S_WORDS = 14;  // per shared block of 16 inputs: limbs [3][4] (natural order), delta, pad
-// One replica of everything that crosses blocks. A cache line that every multiprocessor polls at the same
-// moment is served one request after the other, and the producer's store queues behind them, so the
-// producers write `reps` replicas and block b reads replica b % reps.
+// Everything that crosses blocks, as tagged words. (Replicating it so that fewer blocks poll the same cache
+// lines was measured and bought nothing: the polls are whole-line requests that L2 serves in a few hundred
+// nanoseconds whatever their number.)
 struct alignas(128) Copy {
   unsigned long long y[H];
   unsigned long long logits[MAX_E + 8];
   unsigned long long act_r[ROUTED_UB * ACT_R_WORDS];
   unsigned long long act_s[2 * SHARED_UB * ACT_S_WORDS];
 };
-constexpr int MAX_REPS = 32;
-constexpr int COPY_WORDS = (int)(sizeof(Copy) / sizeof(unsigned long long));
 static_assert(sizeof(Copy) % 128 == 0 && (sizeof(unsigned long long) * (H + MAX_E + 8)) % 16 == 0, "aligned sections");
 
 // shared memory map
@@ -147,32 +145,15 @@ DRB_DEV void ll_store(unsigned long long* p, uint32_t payload, uint32_t tag) {
   const unsigned long long v = ((unsigned long long)tag << 32) | payload;
   asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-// The same word into every replica (p points into replica 0).
-DRB_DEV void ll_store_all(unsigned long long* p, int reps, uint32_t payload, uint32_t tag) {
-  for (int r = 0; r < reps; ++r) ll_store(p + (size_t)r * COPY_WORDS, payload, tag);
-}
-#ifndef DRB_LL_LOAD
-#define DRB_LL_LOAD 0
-#endif
-#if DRB_LL_LOAD == 0
-#define DRB_LL_LD "ld.relaxed.gpu.global"
-#elif DRB_LL_LOAD == 1
-#define DRB_LL_LD "ld.global.cg"
-#else
-#define DRB_LL_LD "ld.volatile.global"
-#endif
 DRB_DEV void ll_load2(const unsigned long long* p, unsigned long long& a, unsigned long long& b) {
-  asm volatile(DRB_LL_LD ".v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+  asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
 }
 DRB_DEV unsigned long long ll_load1(const unsigned long long* p) {
   unsigned long long a;
-  asm volatile(DRB_LL_LD ".u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
   return a;
 }
 
-#ifndef DRB_POLL_SLEEP
-#define DRB_POLL_SLEEP 0
-#endif
 // What a poll does when its data has not arrived. A hand-over completes within a few round trips through L2 and a
 // sleeping warp wakes up late (measured: any sleep between retries costs more than a microsecond per layer), so
 // retries go out back to back; what keeps them cheap is that every poll asks for whole cache lines. Only a wait
@@ -184,22 +165,12 @@ DRB_DEV bool poll_failed(unsigned it, unsigned limit, volatile int* abort_flag) 
     *abort_flag = 1;
     return true;
   }
-  if (DRB_POLL_SLEEP > 0 || it > 8192) __nanosleep(it > 8192 ? 400 : DRB_POLL_SLEEP);
+  if (it > 8192) __nanosleep(400);
   if ((it & 1023u) == 1023u && (*abort_flag || *reinterpret_cast<volatile unsigned*>(&g_drb_error) != 0u)) {
     *abort_flag = 1;
     return true;
   }
   return false;
-}
-
-#ifndef DRB_POLL_STAGGER
-#define DRB_POLL_STAGGER 0  // clocks between the two requests a waiting thread keeps in flight (0: one request at a time)
-#endif
-DRB_DEV void poll_stagger() {
-  if (DRB_POLL_STAGGER > 0) {
-    const long long t0 = clock64();
-    while (clock64() - t0 < DRB_POLL_STAGGER) {}
-  }
 }
 
 // Waits for NV consecutive 16-byte pieces (two tagged words each) at p and returns their 2 NV payloads.
@@ -210,8 +181,8 @@ DRB_DEV void ll_poll(const unsigned long long* p, uint32_t tag, uint32_t (&out)[
 #pragma unroll
   for (int i = 0; i < 2 * NV; ++i) out[i] = 0u;
   if (*abort_flag) return;
-  unsigned long long ra[2 * NV], rb[2 * NV];
-  unsigned ma = 0u, mb = 0u;
+  unsigned long long ra[2 * NV];
+  unsigned ma = 0u;
   auto issue = [&](unsigned long long (&r)[2 * NV], unsigned& m) {
     m = need;
 #pragma unroll
@@ -229,37 +200,20 @@ DRB_DEV void ll_poll(const unsigned long long* p, uint32_t tag, uint32_t (&out)[
       }
   };
   issue(ra, ma);
-  if (DRB_POLL_STAGGER > 0) {
-    poll_stagger();
-    issue(rb, mb);
-  }
   for (unsigned it = 0;; ++it) {
     take(ra, ma);
     if (need == 0u) break;
     issue(ra, ma);
-    if (DRB_POLL_STAGGER > 0) {
-      take(rb, mb);
-      if (need == 0u) break;
-      issue(rb, mb);
-    }
     if (poll_failed(it, limit, abort_flag)) break;
   }
 }
 
 DRB_DEV uint32_t ll_poll1(const unsigned long long* p, uint32_t tag, unsigned limit, volatile int* abort_flag) {
   if (*abort_flag) return 0u;
-  unsigned long long a = ll_load1(p), b2 = 0ull;
-  if (DRB_POLL_STAGGER > 0) {
-    poll_stagger();
-    b2 = ll_load1(p);
-  }
+  unsigned long long a = ll_load1(p);
   for (unsigned it = 0;; ++it) {
     if ((uint32_t)(a >> 32) == tag) return (uint32_t)a;
     a = ll_load1(p);
-    if (DRB_POLL_STAGGER > 0) {
-      if ((uint32_t)(b2 >> 32) == tag) return (uint32_t)b2;
-      b2 = ll_load1(p);
-    }
     if (poll_failed(it, limit, abort_flag)) return 0u;
   }
 }
@@ -275,8 +229,8 @@ DRB_DEV void ll_poll_warp(const unsigned long long* p, uint32_t tag, uint32_t* p
   for (int i = 0; i < PER; ++i)
     if (lane + 32 * i < NP) need |= 1u << i;
   const bool skip = *abort_flag != 0;
-  unsigned long long ra[2 * PER], rb[2 * PER];
-  unsigned ma = 0u, mb = 0u;
+  unsigned long long ra[2 * PER];
+  unsigned ma = 0u;
   auto issue = [&](unsigned long long (&r)[2 * PER], unsigned& m) {
     m = need;
 #pragma unroll
@@ -295,19 +249,10 @@ DRB_DEV void ll_poll_warp(const unsigned long long* p, uint32_t tag, uint32_t* p
   };
   if (!skip) {
     issue(ra, ma);
-    if (DRB_POLL_STAGGER > 0) {
-      poll_stagger();
-      issue(rb, mb);
-    }
     for (unsigned it = 0;; ++it) {
       take(ra, ma);
       if (!__any_sync(0xffffffffu, need != 0u)) break;
       issue(ra, ma);
-      if (DRB_POLL_STAGGER > 0) {
-        take(rb, mb);
-        if (!__any_sync(0xffffffffu, need != 0u)) break;
-        issue(rb, mb);
-      }
       if (poll_failed(it, limit, abort_flag)) break;  // the same decision in every lane
     }
   }
@@ -319,9 +264,6 @@ DRB_DEV void ll_poll_warp(const unsigned long long* p, uint32_t tag, uint32_t* p
 
 // mbarrier wait that honours the abort flag; bounded like the polls, and without sleeping while the wait is short.
 DRB_DEV void wait_full(uint64_t* bar, unsigned parity, unsigned limit, volatile int* abort_flag) {
-#ifdef DRB_STACK_SKELETON
-  return;
-#endif
   if (*abort_flag) return;
   for (unsigned it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return;
@@ -335,8 +277,8 @@ DRB_DEV void wait_full(uint64_t* bar, unsigned parity, unsigned limit, volatile 
   }
 }
 
-// One warp turns 32 values (lane = input index) into the 26 tagged words of a routed activation block, in every replica.
-DRB_DEV void publish_block32(float v, unsigned long long* dst, int reps, uint32_t tag, int lane) {
+// One warp turns 32 values (lane = input index) into the 26 tagged words of a routed activation block.
+DRB_DEV void publish_block32(float v, unsigned long long* dst, uint32_t tag, int lane) {
   const float m = warp_max(fabsf(v));
   const float sum = warp_sum(v);
   const float delta = m > 0.f ? m * (1.f / 1048576.f) : 1.f;
@@ -352,12 +294,12 @@ DRB_DEV void publish_block32(float v, unsigned long long* dst, int reps, uint32_
   uint32_t w = prmt(prmt(t0, t1, sel), prmt(t2, t3, sel), 0x5410u);
   if (lane == 24) w = __float_as_uint(delta);
   if (lane == 25) w = __float_as_uint(sum);
-  if (lane < ACT_R_WORDS) ll_store_all(dst + lane, reps, w, tag);
+  if (lane < ACT_R_WORDS) ll_store(dst + lane, w, tag);
 }
 
 // Each half-warp turns 16 values (lane & 15 = input index) into the 14 tagged words of a shared-expert block
-// at dst + 14 * half, in every replica.
-DRB_DEV void publish_block16x2(float v, unsigned long long* dst, int reps, uint32_t tag, int lane) {
+// at dst + 14 * half.
+DRB_DEV void publish_block16x2(float v, unsigned long long* dst, uint32_t tag, int lane) {
   float m = fabsf(v);
 #pragma unroll
   for (int o = 1; o < 16; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
@@ -374,15 +316,15 @@ DRB_DEV void publish_block16x2(float v, unsigned long long* dst, int reps, uint3
   uint32_t w = prmt(prmt(t0, t1, sel), prmt(t2, t3, sel), 0x5410u);
   if (li == 12) w = __float_as_uint(delta);
   if (li == 13) w = 0u;
-  if (li < ACT_S_WORDS) ll_store_all(dst + h * ACT_S_WORDS + li, reps, w, tag);
+  if (li < ACT_S_WORDS) ll_store(dst + h * ACT_S_WORDS + li, w, tag);
 }
 
-#ifndef DRB_STACK_DOWN_AFTER
-#define DRB_STACK_DOWN_AFTER 3  // the down rows are requested once this part of the block's gate/up rows has landed (-1: at once)
-#endif
+// The down rows are requested once this part of the block's gate/up rows has landed: asked for at once they
+// compete with the gate/up rows for the memory queue, and the gate/up rows are needed first.
+constexpr int DOWN_AFTER_PART = 3;
 
 __global__ void __launch_bounds__(THREADS, 1)
-    k_moe_stack(const drb_moe_layer* __restrict__ layers, int n_layers, float* x, Copy* ws, int reps, int E, float eps,
+    k_moe_stack(const drb_moe_layer* __restrict__ layers, int n_layers, float* x, Copy* ws, int E, float eps,
                 int* __restrict__ idx_trace, float* __restrict__ wts_trace, unsigned poll_limit) {
   extern __shared__ __align__(128) unsigned char dyn[];
   Ctl& ctl = *reinterpret_cast<Ctl*>(dyn);
@@ -403,7 +345,7 @@ __global__ void __launch_bounds__(THREADS, 1)
   const int n0 = (int)((long long)H * b / G), n1 = (int)((long long)H * (b + 1) / G), nr = n1 - n0;  // down rows
   const int rrow0 = 2 * b, nrr = max(0, min(2, E + 1 - rrow0));                                     // router rows
   const bool needs_x = has_units || nrr > 0;
-  const Copy* mine = ws + (b % reps);  // the replica this block reads
+  const Copy* mine = ws;
 
   if (threadIdx.x == 0) {
     for (int q = 0; q < PARTS; ++q) mbar_init(&ctl.gfull[q], 1);
@@ -467,7 +409,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       bar_sync<256 + 32>(BAR_IDX);   // the routing of layer l is in ctl
       // The gate/up rows are what the layer waits for; the down rows are needed a hand-over later. Requested together
       // they share the memory system and delay the activations, so they follow once part of the gate/up rows is here.
-      if (DRB_STACK_DOWN_AFTER >= 0 && routed_blk) wait_full(&ctl.gfull[DRB_STACK_DOWN_AFTER < 0 ? 0 : DRB_STACK_DOWN_AFTER], (unsigned)l & 1u, poll_limit, abort_flag);
+      if (routed_blk) wait_full(&ctl.gfull[DOWN_AFTER_PART], (unsigned)l & 1u, poll_limit, abort_flag);
       issue_routed_dn(Lc);
       if (nrr > 0) {
         bar_sync<64 + 32>(BAR_RT);
@@ -515,7 +457,6 @@ __global__ void __launch_bounds__(THREADS, 1)
       pn_next = static_cast<const float*>(layers[l + 1].post_norm);
       sds_next = static_cast<const __half*>(layers[l + 1].sd_s);
     }
-    DRB_TRACE_POINT(0, 0); DRB_TRACE_BLK(0, 0);
 
     // ---- the hidden state: sum of squares and this block's two router rows in one pass, then the limb blocks.
     // The logits are linear in the hidden state, so the rows are multiplied with y * norm weight as it arrives and
@@ -530,8 +471,6 @@ __global__ void __launch_bounds__(THREADS, 1)
         ll_poll<2>(mine->y + 4 * t, tag - 1u, o, poll_limit, abort_flag);
         xv = make_float4(__uint_as_float(o[0]), __uint_as_float(o[1]), __uint_as_float(o[2]), __uint_as_float(o[3]));
       }
-      DRB_TRACE_POINT(1, 0); DRB_TRACE_BLK(1, 0);
-      DRB_TRACE_POINT(32 + warp, warp * 32 + 31);
       const float4 xw = make_float4(xv.x * wv.x, xv.y * wv.y, xv.z * wv.z, xv.w * wv.w);
       float v[4] = {xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w, 0.f, 0.f, 0.f};
       if (nrr > 0) {
@@ -558,20 +497,17 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
       for (int w = 0; w < CW; ++w) tot += ctl.red[0][w];
       const float inv = rsqrtf(tot / H + eps);
-      DRB_TRACE_POINT(2, 0); DRB_TRACE_BLK(2, 0);
       if (t < nrr) {
         float u = 0.f;
 #pragma unroll
         for (int w = 0; w < CW; ++w) u += ctl.red[1 + t][w];
-        ll_store_all(ws->logits + rrow0 + t, reps, __float_as_uint(u * inv), tag);
+        ll_store(ws->logits + rrow0 + t, __float_as_uint(u * inv), tag);
       }
-      DRB_TRACE_POINT(3, 0); DRB_TRACE_BLK(3, 0);
       if (warp < 2 && nrr > 0) bar_arrive<64 + 32>(BAR_RT);  // every warp read its part of the rows before the barrier above
       if (has_units) {
         quant_store_eo(qx, t, make_float4(xw.x * inv, xw.y * inv, xw.z * inv, xw.w * inv), true);
         bar_sync<NT>(BAR_CONS);
       }
-      DRB_TRACE_POINT(15, 0); DRB_TRACE_BLK(15, 0);
     }
 
     // ---- warps 0..7 of every block derive the routing from the E + 1 logits. A shared-expert block does its gate/up
@@ -594,7 +530,6 @@ __global__ void __launch_bounds__(THREADS, 1)
       const bool valid = t < E;
       float v = -INFINITY;
       if (valid) v = __uint_as_float(ll_poll1(mine->logits + t, tag, poll_limit, abort_flag));
-      DRB_TRACE_POINT(4, 0); DRB_TRACE_BLK(4, 0);
       const unsigned vb = __float_as_uint(v);
       const unsigned ord = (vb & 0x80000000u) ? ~vb : (vb | 0x80000000u);  // orders like the floats
       const unsigned wmax = __reduce_max_sync(0xffffffffu, ord);
@@ -663,7 +598,6 @@ __global__ void __launch_bounds__(THREADS, 1)
         }
       }
       __syncwarp();
-      DRB_TRACE_POINT(5, 0); DRB_TRACE_BLK(5, 0);
       // this block's gate/up rows: lane 4 q + c requests copy c (gate rows, up rows, gate scales, up scales) of part q
       if (routed_blk && lane < 4 * PARTS) {
         const int q = lane >> 2, c = lane & 3;
@@ -679,7 +613,6 @@ __global__ void __launch_bounds__(THREADS, 1)
         else bulk_g2s(gst + (size_t)2 * UNITS * QROW + (UNITS + l0) * SMROW, smp + ((size_t)I + u0) * SMROW, PU * SMROW, &ctl.gfull[q]);
       }
       bar_arrive<256 + 32>(BAR_IDX);  // the producer warp requests the down rows
-      DRB_TRACE_POINT(6, 0); DRB_TRACE_BLK(6, 0);
       {
         const float wsum = warp_sum(valid ? expf(v - m) : 0.f);
         if (lane == 0) tk.red[0] = wsum;
@@ -729,8 +662,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         // block waited for its rows (a shared block fetches them after it has published its own).
         if (i == 1 && routed_blk) fetch_shared_act(tag);
         wait_full(&ctl.gfull[u / PU], par, poll_limit, abort_flag);
-        if (i == 0) { DRB_TRACE_POINT(7, 0); DRB_TRACE_BLK(7, 0); }
-        if (shared_blk) {
+                if (shared_blk) {
           const uint4* gr = reinterpret_cast<const uint4*>(gst + (size_t)u * H);
           const uint4* ur = reinterpret_cast<const uint4*>(gst + (size_t)(UNITS + u) * H);
           const __half* gs = reinterpret_cast<const __half*>(gst + (size_t)2 * UNITS * H + (size_t)u * SSROW);
@@ -752,7 +684,6 @@ __global__ void __launch_bounds__(THREADS, 1)
         }
       }
       bar_arrive<THREADS>(BAR_GU);  // nothing of the stage is read after this point
-      DRB_TRACE_POINT(8, 0); DRB_TRACE_BLK(8, 0);
       // Fold the four per-lane sums into one reduction.
       const bool hi16 = lane & 16, hi8 = lane & 8;
       const float r0 = (hi16 ? v[2] : v[0]) + __shfl_xor_sync(0xffffffffu, hi16 ? v[0] : v[2], 16);
@@ -767,10 +698,9 @@ __global__ void __launch_bounds__(THREADS, 1)
       bar_sync<NT>(BAR_CONS);
       if (warp == 0) {
         const float a = ctl.actv[lane];
-        if (shared_blk) publish_block16x2(a, ws->act_s + (size_t)(b - ROUTED_UB) * 2 * ACT_S_WORDS, reps, tag, lane);
-        else publish_block32(a, ws->act_r + (size_t)b * ACT_R_WORDS, reps, tag, lane);
+        if (shared_blk) publish_block16x2(a, ws->act_s + (size_t)(b - ROUTED_UB) * 2 * ACT_S_WORDS, tag, lane);
+        else publish_block32(a, ws->act_r + (size_t)b * ACT_R_WORDS, tag, lane);
       }
-      DRB_TRACE_POINT(9, 0); DRB_TRACE_BLK(9, 0);
     } else {
       bar_arrive<THREADS>(BAR_GU);
     }
@@ -813,13 +743,10 @@ __global__ void __launch_bounds__(THREADS, 1)
         aq.delta = __uint_as_float(o[24]);
         A = __uint_as_float(o[25]);
       }
-      DRB_TRACE_POINT(11, 0); DRB_TRACE_BLK(11, 0);
-      DRB_TRACE_POINT(48 + warp, warp * 32 + 31);
       float v[4] = {0.f, 0.f, 0.f, 0.f};
       float s_sh = 0.f;
       if (nr > 0) {
         wait_full(&ctl.dfull_r, par, poll_limit, abort_flag);
-        DRB_TRACE_POINT(12, 0); DRB_TRACE_BLK(12, 0);
         const unsigned char* eq = dst + ke * D_EXPERT;
         const unsigned char* esm = eq + RT * DQROW;
 #pragma unroll
@@ -837,7 +764,6 @@ __global__ void __launch_bounds__(THREADS, 1)
         }
       }
       bar_arrive<THREADS>(BAR_DN);  // nothing of the stage is read after this point
-      DRB_TRACE_POINT(13, 0); DRB_TRACE_BLK(13, 0);
       {
         // Fold the four sums (each to be reduced over the 8 lanes of a row group) into one reduction.
         const bool hi4 = lane & 4, hi2 = lane & 2;
@@ -852,17 +778,15 @@ __global__ void __launch_bounds__(THREADS, 1)
       s_sh = warp_sum(s_sh);
       if (lane == 0 && warp < nr) ctl.part_s[warp] = s_sh;
       bar_sync<NT>(BAR_CONS);
-      DRB_TRACE_POINT(10, 0); DRB_TRACE_BLK(10, 0);
       if (t < nr) {
         float acc = 0.f;
 #pragma unroll
         for (int k = 0; k < TOPK; ++k) acc += ctl.wts[k] * (ctl.part[k][0][t] + ctl.part[k][1][t]);
         const float yn = xres + sigmoid_f(ctl.sgate) * ctl.part_s[t] + acc;
         xres = yn;
-        if (l + 1 < n_layers) ll_store_all(ws->y + n0 + t, reps, __float_as_uint(yn), tag);
+        if (l + 1 < n_layers) ll_store(ws->y + n0 + t, __float_as_uint(yn), tag);
         else x[n0 + t] = yn;
       }
-      DRB_TRACE_POINT(14, 0); DRB_TRACE_BLK(14, 0);
     }
   }
 }
@@ -873,13 +797,44 @@ static cudaError_t configure_all() {
   return drb_carveout(k_moe_stack);
 }
 
+// One block whose waits cannot be satisfied: nothing ever arrives at its mbarrier, nothing ever tags `word`. Each
+// wait gives up after `limit` polls, records its code and lets the kernel run to its end, which is what the host
+// observes through drb_device_error(). which = 1: the copy wait of the per-layer kernels (mbar_wait); 2: the copy wait
+// of the persistent kernel (wait_full); 3: its tagged-word polls, by one thread and then by whole warps, the later
+// ones returning at once because the block has already given up.
+__global__ void __launch_bounds__(64, 1) k_test_waits(int which, unsigned limit, const unsigned long long* word, unsigned* polls_after) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_word;
+  __shared__ uint32_t pay[2 * 32];
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    abort_word = 0;
+  }
+  __syncthreads();
+  volatile int* abort_flag = &abort_word;
+  if (which == 1) {
+    if (threadIdx.x == 0) mbar_wait(&bar, 0, DRB_ERR_FULL_WAIT, limit);
+  } else if (which == 2) {
+    if (threadIdx.x == 0) wait_full(&bar, 0, limit, abort_flag);
+    __syncthreads();
+    wait_full(&bar, 0, limit, abort_flag);  // every thread: returns at once, the block has given up
+  } else {
+    if (threadIdx.x == 0) ll_poll1(word, 1u, limit, abort_flag);
+    __syncthreads();
+    const long long t0 = clock64();
+    ll_poll_warp<32>(word, 1u, pay + 0, lane, limit, abort_flag);  // returns at once with zero payloads
+    if (threadIdx.x == 0 && polls_after) *polls_after = (unsigned)(clock64() - t0) + (pay[0] | pay[1]);
+  }
+}
+
 constexpr unsigned POLL_LIMIT = 1u << 20;  // about half a second of polling
-constexpr int REPS = 1;
 
 }  // namespace stack
 
 // Bytes of device workspace drb_moe_stack_decode needs (any contents; every call clears what it uses first).
-extern "C" int drb_moe_stack_workspace_bytes(void) { return (int)(sizeof(stack::Copy) * stack::MAX_REPS); }
+extern "C" int drb_moe_stack_workspace_bytes(void) { return (int)sizeof(stack::Copy); }
 
 // x <- x + moe_l(rmsnorm(x)) for l = 0 .. n_layers - 1, in place, in one cooperative kernel launch.
 // layers: device array of n_layers drb_moe_layer. workspace: drb_moe_stack_workspace_bytes() bytes of
@@ -895,13 +850,23 @@ extern "C" int drb_moe_stack_decode(const drb_moe_layer* layers, int n_layers, f
   if (dev.sms < stack::MIN_GRID || dev.sms > stack::MAX_GRID) return -1;
   if (n_layers == 0) return 0;
   stack::Copy* ws = static_cast<stack::Copy*>(workspace);
-  int reps = stack::REPS;
-  if (const char* v = getenv("DRB_STACK_REPS")) reps = atoi(v) > 0 && atoi(v) <= stack::MAX_REPS ? atoi(v) : reps;
   // tags restart at 1 with every launch, so whatever an earlier launch left must not look valid
-  cudaError_t err = cudaMemsetAsync(ws, 0, sizeof(stack::Copy) * reps, st);
+  cudaError_t err = cudaMemsetAsync(ws, 0, sizeof(stack::Copy), st);
   if (err != cudaSuccess) return (int)err;
   unsigned limit = stack::POLL_LIMIT;
-  void* args[] = {(void*)&layers, (void*)&n_layers, (void*)&x, (void*)&ws, (void*)&reps, (void*)&e, (void*)&eps, (void*)&idx_trace, (void*)&wts_trace, (void*)&limit};
+  void* args[] = {(void*)&layers, (void*)&n_layers, (void*)&x, (void*)&ws, (void*)&e, (void*)&eps, (void*)&idx_trace, (void*)&wts_trace, (void*)&limit};
   err = cudaLaunchCooperativeKernel((const void*)stack::k_moe_stack, dim3(dev.sms), dim3(stack::THREADS), args, stack::SMEM_BYTES, st);
   return err == cudaSuccess ? 0 : (int)err;
+}
+
+// Test hook (no counterpart in the reference): launches one block whose bounded wait runs out after `limit` polls
+// (which: 1 = mbar_wait, 2 = wait_full, 3 = tagged-word polls; word: 512 zeroed bytes of device memory; clocks: a
+// device word receiving the clocks the later polls of case 3 took, or NULL). The launch completes normally; the
+// code is then read with drb_device_error(). limit <= 65536 (a few milliseconds), else -1.
+extern "C" int drb_test_wait_runs_out(int which, unsigned limit, const void* word, unsigned* clocks, cudaStream_t st) {
+  if (which < 1 || which > 3 || limit == 0 || limit > 65536u || !word) return -1;
+  const DrbDevice& dev = drb_device(st);
+  if (!dev.ready) return -2;
+  stack::k_test_waits<<<1, 64, 0, st>>>(which, limit, static_cast<const unsigned long long*>(word), clocks);
+  return (int)cudaGetLastError();
 }

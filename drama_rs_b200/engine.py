@@ -45,26 +45,20 @@ class MoeDecoder:
     """Batch-1 decode over a stack of MoE layers: x <- x + moe_l(rmsnorm(x)) for each layer."""
 
     def __init__(self, layers: list[MoeLayer], topk: int = 8, eps: float = 1e-6, st: Stream | None = None,
-                 chained: bool = False, trace_routing: bool = False, fp8: list | None = None, lib=None) -> None:
-        """chained (not in the reference): the layers run drb_moe_decode_chained, whose down kernel also produces the
-        next layer's routing, so only the first layer launches dr_router_topk. trace_routing copies every layer's
-        idx to `idx_trace` (tests). lib: another library with the same ABI (ffi.bind) to issue the launches to; buffers
+                 trace_routing: bool = False, fp8: list | None = None, lib=None) -> None:
+        """trace_routing copies every layer's idx to `idx_trace` (tests). lib: another library with the same ABI (ffi.bind) to issue the launches to; buffers
         and streams still come from this one."""
         self.l = lib or ffi.lib()
         self.st = st or Stream()
         self.layers = layers
         self.topk, self.eps = topk, eps
-        self.chained, self.trace_routing = chained, trace_routing
+        self.trace_routing = trace_routing
         # fp8[l] (model.Fp8Experts) replaces layer l's int4 routed experts: src/engine.rs:949, 996-1003 (`Experts::Fp8`)
         self.fp8 = fp8
-        assert not (chained and fp8), "the chained sequence exists for the int4 experts only"
         h, i, e = layers[0].hidden, layers[0].inter, layers[0].experts
         self.hidden = h
         f32 = 4
         self.idx_trace = DevBuf(len(layers) * topk * 4) if trace_routing else None
-        if chained:
-            check(self.l.drb_init(), "init")
-            self.chain_ws = DevBuf.zeros(int(self.l.drb_moe_chain_workspace_bytes()), self.st)
         self.x = DevBuf((h) * f32)
         self.rlog = DevBuf((e + 1) * f32)
         self.idx = DevBuf(topk * 4)
@@ -78,7 +72,6 @@ class MoeDecoder:
         ops: list[Op] = []
         l, st = self.l, self.st.raw
         for li, layer in enumerate(self.layers):
-            nxt_layer = self.layers[li + 1] if li + 1 < len(self.layers) else None
             gq, gs = layer.gate_up.expert(0)
             dq, ds = layer.down.expert(0)
             sizes = (layer.gate_up.q_bytes_per_expert, layer.gate_up.sm_bytes_per_expert,
@@ -94,8 +87,7 @@ class MoeDecoder:
                     "router_topk",
                 )
 
-            if not (self.chained and li > 0):  # chained: the previous layer's down kernel has left this layer's routing
-                ops.append(Op((layer.router.ptr, (layer.experts + 1) * layer.hidden * 2), router))
+            ops.append(Op((layer.router.ptr, (layer.experts + 1) * layer.hidden * 2), router))
             if self.trace_routing:
                 ops.append(Op(None, lambda pf, pfb, li=li: check(
                     l.dr_d2d(self.idx_trace.at(li * self.topk * 4), self.idx.at(0), self.topk * 4, st), "d2d")))
@@ -112,19 +104,6 @@ class MoeDecoder:
                     "moe_decode",
                 )
 
-            def decode_chained(pf, pfb, li=li, layer=layer, nxt=nxt_layer, gq=gq, gs=gs, dq=dq, ds=ds, sgq=sgq, sgs=sgs, sdq=sdq,
-                               sds=sds):
-                launched(
-                    l.drb_moe_decode_chained(
-                        gq, gs, dq, ds, sgq, sgs, sdq, sds, self.x.at(0), self.idx.at(0), self.wts.at(0), self.sgate.at(0),
-                        self.x.at(0), self.act.at(0), self.x.at(0), layer.hidden, layer.inter, self.topk,
-                        layer.post_norm.at(0), self.eps, nxt.router.at(0) if nxt else NULL,
-                        nxt.post_norm.at(0) if nxt else NULL, nxt.experts if nxt else 0, self.rlog.at(0),
-                        self.chain_ws.at(0), 1 if li > 0 else 0, st,
-                    ),
-                    "moe_decode_chained",
-                )
-
             def decode_fp8(pf, pfb, li=li, layer=layer, sgq=sgq, sgs=sgs, sdq=sdq, sds=sds):
                 f8 = self.fp8[li]
                 launched(
@@ -136,7 +115,7 @@ class MoeDecoder:
                     "moe_decode_fp8",
                 )
 
-            ops.append(Op(None, decode_fp8 if self.fp8 else decode_chained if self.chained else decode))
+            ops.append(Op(None, decode_fp8 if self.fp8 else decode))
         return ops
 
     def record_step(self) -> None:

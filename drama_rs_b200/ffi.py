@@ -69,12 +69,11 @@ SIGNATURES: dict[str, tuple] = {
     "drb_rmsnorm_f16": (I32, [P, P, P, I32, I32, F32, P]),
     "drb_router_logits_f16": (I32, [P, P, P, I32, I32, I32, F32, P]),
     "drb_router_logits": (I32, [P, P, P, I32, I32, I32, F32, P]),
-    "drb_moe_decode_chained": (I32, [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I32, I32, I32, P, F32, P, P, I32, P, P, I32, P]),
-    "drb_moe_chain_workspace_bytes": (SZ, []),
     "drb_quant_q4": (I32, [P, SZ, P, P, P]),
     "drb_quant_q8": (I32, [P, SZ, P, P, P]),
     "drb_init": (I32, []),
     "drb_device_error": (I32, [C.POINTER(U32)]),
+    "drb_test_wait_runs_out": (I32, [I32, U32, P, P, P]),
     "drb_grid_blocks": (I32, []),
 }
 

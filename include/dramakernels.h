@@ -157,10 +157,16 @@ typedef struct {
   const void *router, *post_norm, *gu_q, *gu_sm, *d_q, *d_sm, *sgu_q, *sgu_s, *sd_q, *sd_s;
 } drb_moe_layer;
 /* x <- x + moe_l(rmsnorm(x, post_norm_l)) for l = 0 .. n_layers-1, in place, as ONE persistent cooperative
- * kernel (the benchmark's 40-layer decode step without per-layer launches). layers: device array.
- * workspace: drb_moe_stack_workspace_bytes() bytes of device memory. idx_trace / wts_trace: optional
- * [n_layers, topk] device arrays receiving each layer's routing. h == 2048, i == 512, topk == 8, e <= 256,
- * >= 148 multiprocessors; -1 otherwise. The per-layer dr_router_topk + dr_moe_decode compute the same. */
+ * kernel (the benchmark's 40-layer decode step without per-layer launches; what src/engine.rs:946-1042 issues as
+ * dr_router_topk + dr_moe_decode per layer). layers: device array. workspace: drb_moe_stack_workspace_bytes() bytes
+ * of device memory, 256-byte aligned, any contents (every call clears it first, on `st`); calls that share a
+ * workspace must not overlap on the GPU. idx_trace / wts_trace: optional [n_layers, topk] device arrays receiving
+ * each layer's routing. Blocks hand the hidden state, the router logits and the activations to one another as
+ * tagged 64-bit words; every wait on such a word is bounded and reports through drb_device_error().
+ * The top-k is chosen on the logits (softmax is monotonic), ties towards the lower index as dr_moe_topk does; the
+ * weights are the softmax over all e logits, renormalised over the chosen k.
+ * h == 2048, i == 512, topk == 8, topk <= e <= 256, at least 144 multiprocessors (one block each, all resident);
+ * -1 otherwise. Capturable in a graph. */
 int drb_moe_stack_workspace_bytes(void);
 int drb_moe_stack_decode(const drb_moe_layer* layers, int n_layers, float* x, void* workspace, int e, int topk, int h,
                          int i, float eps, int* idx_trace, float* wts_trace, dr_stream st);
@@ -173,27 +179,51 @@ int drb_moe_offsets(const int* counts, int e, int* offsets, dr_stream st);
  * a host that spreads rows over several GPUs uses this call so that the routing is the same at every split.
  * h == 2048, else -1. */
 int drb_router_logits(const dr_bf16* xb, const dr_bf16* w, float* logits, int rows, int e1, int h, float beta, dr_stream st);
-/* Chained decode: dr_moe_decode as one link of a chain over consecutive MoE layers, on a caller-owned workspace of
- * drb_moe_chain_workspace_bytes() bytes (zeroed once by the caller, private to one stream of launches).
- *   next_router != NULL: the down kernel also computes the NEXT layer's routing. Every block adds its share of
- *     next_router . (y * next_nw) and of sum(y^2) to fixed-point accumulators in the workspace (integer atomics: the
- *     totals do not depend on the order of arrival); the last block to arrive applies rsqrt(mean(y^2) + eps), runs
- *     softmax + top-k and OVERWRITES idx / wts / sgate (and logits [e_next + 1], if not NULL) with the next layer's
- *     routing: what dr_router_topk(next_router, y, next_nw, eps, ...) would write. The router rows are fetched while
- *     the kernel waits for its activations, so the next layer needs no router launch.
- *   next_router == NULL ends the chain: idx / wts / sgate are left as they are.
- *   have_prev != 0: this layer's routing was produced by the previous chained call on the same workspace and x is that
- *     call's y; both are then read from replicas in the workspace (one per group of blocks, so that 148 blocks do not
- *     read the same cache lines at once). idx / wts / sgate / x are still passed and hold the same values.
- * topk == 8, 8 <= e_next <= 256, h == 2048; other limits and return codes as dr_moe_decode. In the reference's engine
- * the call replaces dr_moe_decode(layer l) and dr_router_topk(layer l + 1) (src/engine.rs:959-1042). */
-int drb_moe_decode_chained(const uint8_t* gu_q, const dr_half* gu_sm, const uint8_t* d_q, const dr_half* d_sm,
-                           const int8_t* sgu_q, const dr_half* sgu_s, const int8_t* sd_q, const dr_half* sd_s,
-                           const float* x, int* idx, float* wts, float* sgate, const float* res, float* act, float* y,
-                           int h, int i, int topk, const float* nw, float eps, const dr_bf16* next_router,
-                           const float* next_nw, int e_next, float* logits, float* workspace, int have_prev,
-                           dr_stream st);
-size_t drb_moe_chain_workspace_bytes(void);
+/* ---- prefill without a library GEMM, a permuted copy or a host round trip -------------------- */
+/* dr_rmsnorm / drb_router_logits for rows kept in fp16 (the reference rounds the normalised rows to bf16,
+ * src/engine.rs:499): yh [rows, d] = fp16(rmsnorm(x) * w), clamped to +-65504; logits as drb_router_logits. With
+ * drb_moe_prefill_block(x_f16 = 1) the whole block then works on rows with eleven significant bits instead of eight. */
+int drb_rmsnorm_f16(const float* x, const float* w, dr_half* yh, int rows, int d, float eps, dr_stream st);
+int drb_router_logits_f16(const dr_half* xh, const dr_bf16* w, float* logits, int rows, int e1, int h, float beta, dr_stream st);
+/* Count, exclusive scan and slot assignment of the (row, k) pairs in one launch: counts [e_n], offsets [e_n],
+ * slot_of [rows * topk] (-1 for a pair whose expert lies outside [e_lo, e_lo + e_n)), row_of [slot] = row.
+ * Replaces dr_moe_count + the host scan + dr_moe_permute (src/engine.rs:565-580) when the grouped GEMM is
+ * drb_moe_prefill_block, which reads its rows through row_of. The order of the slots inside an expert is
+ * arbitrary, as dr_moe_permute's is (both assign them by atomics); no result depends on it. e_n <= 1024, else -1. */
+int drb_moe_group(const int* idx, int rows, int topk, int e_lo, int e_n, int* counts, int* offsets, int* slot_of,
+                  int* row_of, dr_stream st);
+/* The routed experts AND the int8 shared expert of one prefill block in two launches: dr_moe_prefill with
+ * (a) the operand rows read in place through row_of (xb: the normalised rows in row order, [rows_sh, h], bf16 or with
+ *     x_f16 != 0 fp16; row_of == NULL: slot s reads row s, as dr_moe_prefill does), and
+ * (b) the shared expert as one more expert that owns every row, its int8 weights dequantised into the same
+ *     tensor-core tiles (sh_act: 16-bit scratch [rows_sh, i]; sh_out: f32 [rows_sh, h]). The reference runs it through
+ *     cuBLAS on weights dequantised to bf16 (src/engine.rs:351-355, 560-562).
+ * y [slots, h] f32; y_row_of (or NULL): slot -> row of y. rows_sh = 0 skips the shared expert, e = 0 the routed
+ * ones. Every pointer except row_of / y_row_of must be a valid device address even for a part that does not run
+ * (any buffer will do): NULL returns -1. Intermediates are fp16: SwiGLU values beyond +-65504 are clamped.
+ * h == 2048, i == 512, else -1. */
+int drb_moe_prefill_block(const uint8_t* gu_q, const dr_half* gu_sm, const uint8_t* d_q, const dr_half* d_sm,
+                          const int8_t* sgu_q, const dr_half* sgu_s, const int8_t* sd_q, const dr_half* sd_s,
+                          const dr_bf16* xb, const int* row_of, const int* offsets, const int* counts, dr_bf16* act,
+                          float* y, dr_bf16* sh_act, float* sh_out, int rows_sh, int e, int h, int i, int x_f16,
+                          const int* y_row_of, dr_stream st);
+/* ---- expert parallelism (the reference is single-GPU) ---------------------------------------- */
+/* Rows travel between ranks in a buffer of `world` blocks; a block is drb_ep_block_rows(cap, row_bytes) rows of
+ * row_bytes bytes: cap row slots, then the cap local expert ids of those rows (int32, `per` = empty slot), padded
+ * to whole rows, so that ONE fixed-size all-to-all moves rows and ids together and no sizes are exchanged first.
+ *   drb_ep_pack   sender: places this rank's (row, k) pairs (idx [n_rows, topk]; `per` experts per rank) into `send`;
+ *                 slot_of [n_rows * topk] = owner * cap + slot, for dr_moe_combine on the returned rows;
+ *                 dst_row [n_rows * topk]: scratch. *overflow (device word, zeroed by the caller) is set when a
+ *                 block was full: the step's result is void then, and the caller repeats it with a larger cap.
+ *   drb_ep_group  owner: groups the received world * cap pairs by local expert: counts / offsets [per],
+ *                 slot_of [world * cap] scratch, row_of [slot] = row of `recv` (operand gather of
+ *                 drb_moe_prefill_block), pair_of [slot] = position of the pair in receive order (its y_row_of).
+ * row_bytes % 16 == 0, world <= 64, per <= 1024; -1 otherwise. */
+int drb_ep_block_rows(int cap, int row_bytes);
+int drb_ep_pack(const void* rows, const int* idx, int n_rows, int topk, int per, int world, int cap, int row_bytes,
+                void* send, int* slot_of, int* dst_row, unsigned* overflow, dr_stream st);
+int drb_ep_group(const void* recv, int world, int cap, int row_bytes, int per, int* counts, int* offsets, int* slot_of,
+                 int* row_of, int* pair_of, dr_stream st);
 /* The checkpoint quantisers of the reference's converter on the GPU (tools/convert.py:33-41 `quant_q8`, 44-101
  * `quant_q4_groups` / `quant_q4`: 24-step clipping search with a least-squares refit). w: `groups` x 64 (q4) or
  * 128 (q8) consecutive floats, i.e. a row-major weight whose last dimension is a multiple of the group; outputs in
@@ -205,6 +235,11 @@ int dr_cublas_destroy(void* h);
 int drb_init(void);                    /* per-device setup; also run by the pre-capture hooks above */
 int drb_device_error(unsigned* out);   /* reads and clears the bounded-wait error word; synchronises */
 int drb_grid_blocks(void);             /* blocks of the persistent kernels on the current device */
+/* Test hook: one block whose bounded wait runs out after `limit` polls (which: 1 = copy wait of the per-layer
+ * kernels, 2 = copy wait of the persistent kernel, 3 = its tagged-word polls; word: 512 zeroed device bytes; clocks:
+ * device word or NULL). The launch completes normally and the code is read with drb_device_error().
+ * limit <= 65536 (milliseconds at most), else -1. */
+int drb_test_wait_runs_out(int which, unsigned limit, const void* word, unsigned* clocks, dr_stream st);
 
 #ifdef __cplusplus
 }

@@ -114,3 +114,17 @@ def test_gemv_bf16(st, n):
     ref = orc.gemv_bf16(w, x, dtype=np.float64)
     assert np.abs(y - ref).max() <= 2e-6 * np.abs(ref).max() + 1e-7
     assert l.dr_gemv_bf16(dw.at(0), dx.at(0), dy.at(0), n, 1024, NULL, 0.0, NULL, 0, st.raw) == -1
+
+
+def test_gemv_q8_extreme_codes_against_a_constant_slice(st):
+    """Every code at -128 against a slice of equal negative activations: each 16-byte chunk's integer sum reaches
+    16 * 128 * 2^20 = 2^31, one past what an int32 recombination of the limbs can hold."""
+    n, k = 64, 2048
+    q = np.full((n, k), -128, dtype=np.int8)
+    q[1::2] = 127
+    s = np.full((n, k // 128), 0.01, dtype=np.float16)
+    x = np.full(k, -1.5, dtype=np.float32)
+    y = run_q8(st, q, s, x)
+    ref = orc.gemv_q8(q, s, x, dtype=np.float64)
+    assert np.abs(y - ref).max() <= 1e-5 * np.abs(ref).max(), (y[:4], ref[:4])
+    assert device_error_word() == 0

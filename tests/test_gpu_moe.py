@@ -159,33 +159,28 @@ def test_moe_decode_stack_of_layers(st, layers):
     assert device_error_word() == 0
 
 
-def test_moe_decode_chained_routing(st, layers):
-    """drb_moe_decode_chained: the down kernel of layer l also produces the routing of layer l + 1. Four layers (256 experts) and three layers of 16 experts: every layer's routing bit-exact against the
-    fp64 oracle, the hidden state within the layer bar, eager == graph replay, and within fp32 noise of the plain
-    dr_router_topk + dr_moe_decode sequence."""
-    for experts, seeds in ((256, (0, 1, 0, 1)), (16, (3, 4, 3))):
-        pairs = [layers(s, experts) for s in seeds]
-        x = synth.make_x(21, 1, 2048)[0]
-        ref = x.astype(np.float64)[None]
-        ref_idx = []
-        for host, _ in pairs:
-            ref, ridx, _, _, _ = orc.moe_layer(host, ref, 8, 1e-6, np.float64)
-            ref_idx.append(ridx[0])
-        dec = MoeDecoder([d for _, d in pairs], st=st, chained=True, trace_routing=True)
-        dec.set_x(x)
-        y = dec.step_eager()
-        assert device_error_word() == 0
-        assert np.array_equal(dec.routing_trace(), np.stack(ref_idx)), f"routing, {experts} experts"
-        scale = np.abs(ref).max()
-        assert_parity(y, ref[0], f"chained stack, {experts} experts", max_abs=max(1e-2, 4e-6 * scale))
-        plain = MoeDecoder([d for _, d in pairs], st=st)
-        plain.set_x(x)
-        assert np.abs(y - plain.step_eager()).max() <= 4e-6 * scale
-        dec.capture()
-        for _ in range(3):
-            dec.set_x(x)
-            assert np.array_equal(dec.step(), y), "graph replay of the chained sequence differs from the eager launches"
-        assert device_error_word() == 0
+def test_moe_decode_shared_expert_extreme_codes(st):
+    """The shared expert's int8 codes all at +127 against a constant hidden state: every 32-value slice of the
+    normalised row sits at full scale, and a chunk's integer sum (32 * 127 * 2^20) exceeds int32. Per-layer entry
+    points and the persistent kernel against the fp64 oracle."""
+    shape = synth.MoeShape(experts=16)
+    host = dict(synth.make_layer(5, shape))
+    host["moe.shared_gate_up.q8"] = np.full_like(host["moe.shared_gate_up.q8"], 127)
+    host["moe.shared_gate_up.s"] = np.full_like(host["moe.shared_gate_up.s"], 2e-5)
+    host["post_norm"] = np.ones_like(host["post_norm"])
+    dev = MoeLayer.upload(host, st)
+    x = np.full(shape.hidden, 3.0, dtype=np.float32)
+    ref, ridx, _, _, _ = orc.moe_layer(host, x[None], shape.topk, shape.eps, np.float64)
+    scale = np.abs(ref).max()
+    dec = MoeDecoder([dev], st=st)
+    dec.set_x(x)
+    y = dec.step_eager()
+    assert np.array_equal(dec.routing()[0], ridx[0])
+    assert_parity(y, ref[0], "per-layer decode, saturated shared expert", max_abs=max(1e-2, 4e-6 * scale))
+    stack = MoeStackDecoder([dev], st=st)
+    stack.set_x(x)
+    assert_parity(stack.step(), ref[0], "stack decode, saturated shared expert", max_abs=max(1e-2, 4e-6 * scale))
+    assert device_error_word() == 0
 
 
 def test_moe_stack_persistent_kernel(st, layers, golden_dir):
