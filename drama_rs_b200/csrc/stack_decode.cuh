@@ -87,15 +87,19 @@ constexpr int D_STAGE = TOPK * D_EXPERT + RT * I;  // 45,056
 // hand-over buffers
 constexpr int ACT_R_WORDS = 26;  // per routed block of 32 inputs: limbs [3][8] (even/odd order), delta, sum
 constexpr int ACT_S_WORDS = 14;  // per shared block of 16 inputs: limbs [3][4] (natural order), delta, pad
-// Everything that crosses blocks, as tagged words. (Replicating it so that fewer blocks poll the same cache
-// lines was measured and bought nothing: the polls are whole-line requests that L2 serves in a few hundred
-// nanoseconds whatever their number.)
+// Everything that crosses blocks, as tagged words. The kernel can keep `reps` replicas of it (producers write all
+// of them, block b reads replica b % reps) so that fewer blocks poll the same cache lines; measured, more than one
+// replica buys nothing (the polls are whole-line requests that L2 serves in a few hundred nanoseconds whatever
+// their number), so every launch passes reps = 1. The count stays a run-time value all the same: with it folded
+// into the code the same kernel measured 11.45 us per layer instead of 10.85, a matter of the compiler's schedule
+// around the tagged stores and polls.
 struct alignas(128) Copy {
   unsigned long long y[H];
   unsigned long long logits[MAX_E + 8];
   unsigned long long act_r[ROUTED_UB * ACT_R_WORDS];
   unsigned long long act_s[2 * SHARED_UB * ACT_S_WORDS];
 };
+constexpr int COPY_WORDS = (int)(sizeof(Copy) / sizeof(unsigned long long));
 static_assert(sizeof(Copy) % 128 == 0 && (sizeof(unsigned long long) * (H + MAX_E + 8)) % 16 == 0, "aligned sections");
 
 // shared memory map
@@ -144,6 +148,10 @@ DRB_DEV void bar_arrive(int id) {
 DRB_DEV void ll_store(unsigned long long* p, uint32_t payload, uint32_t tag) {
   const unsigned long long v = ((unsigned long long)tag << 32) | payload;
   asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// The same word into every replica (p points into replica 0).
+DRB_DEV void ll_store_all(unsigned long long* p, int reps, uint32_t payload, uint32_t tag) {
+  for (int r = 0; r < reps; ++r) ll_store(p + (size_t)r * COPY_WORDS, payload, tag);
 }
 DRB_DEV void ll_load2(const unsigned long long* p, unsigned long long& a, unsigned long long& b) {
   asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
@@ -277,8 +285,8 @@ DRB_DEV void wait_full(uint64_t* bar, unsigned parity, unsigned limit, volatile 
   }
 }
 
-// One warp turns 32 values (lane = input index) into the 26 tagged words of a routed activation block.
-DRB_DEV void publish_block32(float v, unsigned long long* dst, uint32_t tag, int lane) {
+// One warp turns 32 values (lane = input index) into the 26 tagged words of a routed activation block, in every replica.
+DRB_DEV void publish_block32(float v, unsigned long long* dst, int reps, uint32_t tag, int lane) {
   const float m = warp_max(fabsf(v));
   const float sum = warp_sum(v);
   const float delta = m > 0.f ? m * (1.f / 1048576.f) : 1.f;
@@ -294,12 +302,12 @@ DRB_DEV void publish_block32(float v, unsigned long long* dst, uint32_t tag, int
   uint32_t w = prmt(prmt(t0, t1, sel), prmt(t2, t3, sel), 0x5410u);
   if (lane == 24) w = __float_as_uint(delta);
   if (lane == 25) w = __float_as_uint(sum);
-  if (lane < ACT_R_WORDS) ll_store(dst + lane, w, tag);
+  if (lane < ACT_R_WORDS) ll_store_all(dst + lane, reps, w, tag);
 }
 
 // Each half-warp turns 16 values (lane & 15 = input index) into the 14 tagged words of a shared-expert block
-// at dst + 14 * half.
-DRB_DEV void publish_block16x2(float v, unsigned long long* dst, uint32_t tag, int lane) {
+// at dst + 14 * half, in every replica.
+DRB_DEV void publish_block16x2(float v, unsigned long long* dst, int reps, uint32_t tag, int lane) {
   float m = fabsf(v);
 #pragma unroll
   for (int o = 1; o < 16; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
@@ -316,7 +324,7 @@ DRB_DEV void publish_block16x2(float v, unsigned long long* dst, uint32_t tag, i
   uint32_t w = prmt(prmt(t0, t1, sel), prmt(t2, t3, sel), 0x5410u);
   if (li == 12) w = __float_as_uint(delta);
   if (li == 13) w = 0u;
-  if (li < ACT_S_WORDS) ll_store(dst + h * ACT_S_WORDS + li, w, tag);
+  if (li < ACT_S_WORDS) ll_store_all(dst + h * ACT_S_WORDS + li, reps, w, tag);
 }
 
 // The down rows are requested once this part of the block's gate/up rows has landed: asked for at once they
@@ -324,7 +332,7 @@ DRB_DEV void publish_block16x2(float v, unsigned long long* dst, uint32_t tag, i
 constexpr int DOWN_AFTER_PART = 3;
 
 __global__ void __launch_bounds__(THREADS, 1)
-    k_moe_stack(const drb_moe_layer* __restrict__ layers, int n_layers, float* x, Copy* ws, int E, float eps,
+    k_moe_stack(const drb_moe_layer* __restrict__ layers, int n_layers, float* x, Copy* ws, int reps, int E, float eps,
                 int* __restrict__ idx_trace, float* __restrict__ wts_trace, unsigned poll_limit) {
   extern __shared__ __align__(128) unsigned char dyn[];
   Ctl& ctl = *reinterpret_cast<Ctl*>(dyn);
@@ -345,7 +353,7 @@ __global__ void __launch_bounds__(THREADS, 1)
   const int n0 = (int)((long long)H * b / G), n1 = (int)((long long)H * (b + 1) / G), nr = n1 - n0;  // down rows
   const int rrow0 = 2 * b, nrr = max(0, min(2, E + 1 - rrow0));                                     // router rows
   const bool needs_x = has_units || nrr > 0;
-  const Copy* mine = ws;
+  const Copy* mine = ws + (b % reps);  // the replica this block reads
 
   if (threadIdx.x == 0) {
     for (int q = 0; q < PARTS; ++q) mbar_init(&ctl.gfull[q], 1);
@@ -501,7 +509,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         float u = 0.f;
 #pragma unroll
         for (int w = 0; w < CW; ++w) u += ctl.red[1 + t][w];
-        ll_store(ws->logits + rrow0 + t, __float_as_uint(u * inv), tag);
+        ll_store_all(ws->logits + rrow0 + t, reps, __float_as_uint(u * inv), tag);
       }
       if (warp < 2 && nrr > 0) bar_arrive<64 + 32>(BAR_RT);  // every warp read its part of the rows before the barrier above
       if (has_units) {
@@ -698,8 +706,8 @@ __global__ void __launch_bounds__(THREADS, 1)
       bar_sync<NT>(BAR_CONS);
       if (warp == 0) {
         const float a = ctl.actv[lane];
-        if (shared_blk) publish_block16x2(a, ws->act_s + (size_t)(b - ROUTED_UB) * 2 * ACT_S_WORDS, tag, lane);
-        else publish_block32(a, ws->act_r + (size_t)b * ACT_R_WORDS, tag, lane);
+        if (shared_blk) publish_block16x2(a, ws->act_s + (size_t)(b - ROUTED_UB) * 2 * ACT_S_WORDS, reps, tag, lane);
+        else publish_block32(a, ws->act_r + (size_t)b * ACT_R_WORDS, reps, tag, lane);
       }
     } else {
       bar_arrive<THREADS>(BAR_GU);
@@ -784,7 +792,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         for (int k = 0; k < TOPK; ++k) acc += ctl.wts[k] * (ctl.part[k][0][t] + ctl.part[k][1][t]);
         const float yn = xres + sigmoid_f(ctl.sgate) * ctl.part_s[t] + acc;
         xres = yn;
-        if (l + 1 < n_layers) ll_store(ws->y + n0 + t, __float_as_uint(yn), tag);
+        if (l + 1 < n_layers) ll_store_all(ws->y + n0 + t, reps, __float_as_uint(yn), tag);
         else x[n0 + t] = yn;
       }
     }
@@ -805,7 +813,7 @@ static cudaError_t configure_all() {
 __global__ void __launch_bounds__(64, 1) k_test_waits(int which, unsigned limit, const unsigned long long* word, unsigned* polls_after) {
   __shared__ uint64_t bar;
   __shared__ int abort_word;
-  __shared__ uint32_t pay[2 * 32];
+  __shared__ __align__(16) uint32_t pay[2 * 32];  // ll_poll_warp stores payload pairs as 8-byte words
   const int lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     mbar_init(&bar, 1);
@@ -850,11 +858,12 @@ extern "C" int drb_moe_stack_decode(const drb_moe_layer* layers, int n_layers, f
   if (dev.sms < stack::MIN_GRID || dev.sms > stack::MAX_GRID) return -1;
   if (n_layers == 0) return 0;
   stack::Copy* ws = static_cast<stack::Copy*>(workspace);
+  int reps = 1;  // see Copy
   // tags restart at 1 with every launch, so whatever an earlier launch left must not look valid
   cudaError_t err = cudaMemsetAsync(ws, 0, sizeof(stack::Copy), st);
   if (err != cudaSuccess) return (int)err;
   unsigned limit = stack::POLL_LIMIT;
-  void* args[] = {(void*)&layers, (void*)&n_layers, (void*)&x, (void*)&ws, (void*)&e, (void*)&eps, (void*)&idx_trace, (void*)&wts_trace, (void*)&limit};
+  void* args[] = {(void*)&layers, (void*)&n_layers, (void*)&x, (void*)&ws, (void*)&reps, (void*)&e, (void*)&eps, (void*)&idx_trace, (void*)&wts_trace, (void*)&limit};
   err = cudaLaunchCooperativeKernel((const void*)stack::k_moe_stack, dim3(dev.sms), dim3(stack::THREADS), args, stack::SMEM_BYTES, st);
   return err == cudaSuccess ? 0 : (int)err;
 }

@@ -11,7 +11,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-# DRAMA_KERNELS_LIB points at another build of the same library (development builds with probes).
+# DRAMA_KERNELS_LIB points at another build of the same library.
 LIB_PATH = os.environ.get("DRAMA_KERNELS_LIB") or os.path.join(HERE, "libdramakernels.so")
 
 P, I32, F32, SZ, U32 = C.c_void_p, C.c_int, C.c_float, C.c_size_t, C.c_uint
