@@ -205,7 +205,7 @@ def run_reference(args) -> None:
                                    f"restatement of the reference kernels, OpenMP over {cores} threads; mean {dt / args.steps / args.layers * 1e6:.1f} us/layer"},
         "e2e": {"value": us, "unit": "us/layer", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ----------------------------------------------------------------------------- GPU arm
@@ -801,12 +801,34 @@ def run_gpu(args) -> None:
                 line["reference_cuda_sm100"] = r
     if not args.no_cpu and world == 1:  # the CPU baseline is a single-GPU-run figure (torchrun also pins OMP to one thread)
         line["cpu_baseline"] = cpu_decode_baseline()
-    print(json.dumps(line), flush=True)
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 
 
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result() -> None:
+    """Libraries write to file descriptor 1 behind Python's back (NCCL prints its version there): everything but the
+    result line goes to stderr, the line itself to the descriptor stdout had when the program started."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main() -> None:
+    keep_stdout_for_the_result()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
