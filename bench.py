@@ -388,9 +388,30 @@ def fp8_extra(torch, layers, st, ext_stream) -> dict:
     y = dec.x.download(np.float32, h, st)
     layer_bytes = SHAPE.router_bytes + SHAPE.topk * (3 * h * i + 4 * ((2 * i // 128) * (h // 128) + (h // 128) * (i // 128))) + SHAPE.shared_bytes
     gbs = layer_bytes / us / 1e3
+    # Prefill over the same FP8 experts (dr_moe_prefill_fp8): the grouping of configuration 3 (300 rows, Zipf 1.1), the
+    # layers' FP8 tensors rotated so that the weights stream from HBM.
+    from drama_rs_b200.engine import MoePrefill
+    from drama_rs_b200.gpu import launched
+
+    rows = 300
+    pre = MoePrefill(layers[0], rows, st=st, reference_calls=True)
+    pre.run(synth.make_x(33, rows, h), logit_bias=synth.zipf_router_bias(33, e, 1.1))  # leaves xp, offsets, counts behind
+    hit = int((pre.counts.download(np.int32, e, st) > 0).sum())
+    lib = pre.l
+
+    def grouped(k):
+        f8 = f8s[k % n_layers]
+        launched(lib.dr_moe_prefill_fp8(f8.gu_w.at(0), f8.gu_s.at(0), f8.d_w.at(0), f8.d_s.at(0), pre.xp.at(0), pre.offsets.at(0),
+                                        pre.counts.at(0), pre.ap.at(0), pre.yp.at(0), e, h, i, st.raw), "moe_prefill_fp8", debug=False)
+
+    us_pf = time_on_stream(torch, st, ext_stream, grouped, 40)
+    pf_bytes = hit * (3 * h * i + 4 * ((2 * i // 128) * (h // 128) + (h // 128) * (i // 128)))
+    yp = pre.yp.download(np.float32, rows * SHAPE.topk * h, st)
     del keep
     return {"workload": f"decode_stack{n_layers}_b1_fp8_experts", "us_per_layer": us, "algorithmic_bytes_per_layer": layer_bytes,
-            "hbm_gbs": gbs, "frac_of_measured_hbm": gbs / peaks()[0], "finite": bool(np.isfinite(y).all())}
+            "hbm_gbs": gbs, "frac_of_measured_hbm": gbs / peaks()[0], "finite": bool(np.isfinite(y).all()),
+            "prefill_300rows_grouped_gemm_us": us_pf, "prefill_experts_hit": hit, "prefill_hbm_gbs": pf_bytes / us_pf / 1e3,
+            "prefill_frac_of_measured_hbm": pf_bytes / us_pf / 1e3 / peaks()[0], "prefill_finite": bool(np.isfinite(yp).all())}
 
 
 def gemv_extra(torch, st, ext_stream, lib, what: str = "this library") -> list:
@@ -741,7 +762,7 @@ def run_gpu(args) -> None:
     word = C.c_uint(0)
     lib.drb_device_error(C.byref(word))
     ep_info = ep_info64 = None
-    if not args.no_extras:
+    if not args.no_extras and set(args.extras.split(",")) & {"all", "ep"}:
         ep_info = prefill_ep_extra(torch, dist, layers[0], st, ext_stream, rank, world)
         ep_info64 = decode64_ep_extra(torch, dist, layers, st, ext_stream, rank, world)
     if rank != 0:
@@ -785,12 +806,17 @@ def run_gpu(args) -> None:
     }
     if ep_info is not None:
         line["ep_scaling"] = {"n_gpus": world, "prefill_300rows": ep_info, "decode_64streams": ep_info64}
+    want = set(args.extras.split(","))
     if not args.no_extras:
-        line["parity_check"] = parity_check(st)
-        line["prefill"] = prefill_extra(torch, layers, st, ext_stream)
-        line["gemv_q8_sweep"] = gemv_extra(torch, st, ext_stream, lib)
-        line["decode_fp8"] = fp8_extra(torch, layers, st, ext_stream)
-        if world == 1:
+        if want & {"all", "parity"}:
+            line["parity_check"] = parity_check(st)
+        if want & {"all", "prefill"}:
+            line["prefill"] = prefill_extra(torch, layers, st, ext_stream)
+        if want & {"all", "gemv"}:
+            line["gemv_q8_sweep"] = gemv_extra(torch, st, ext_stream, lib)
+        if want & {"all", "fp8"}:
+            line["decode_fp8"] = fp8_extra(torch, layers, st, ext_stream)
+        if world == 1 and want & {"all", "reference"}:
             try:
                 r = reference_cuda_extra(torch, layers, st, ext_stream)
             except Exception as exc:  # noqa: BLE001 - a checker's failure must not take the bench line with it
@@ -837,6 +863,8 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip everything but the headline decode step")
+    ap.add_argument("--extras", default="all", help="comma list of the extra legs to run: ep, parity, prefill, gemv, fp8, reference "
+                                                    "(default all); small profiling cases pick one")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -147,6 +147,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
     }
   }
 
+  bool dead = false;
   for (int c = 0; c < nchunks; ++c) {
     const int s = c % STAGES;
     const int r0 = u0 + c * RB;
@@ -167,7 +168,9 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1)
           }
       }
     }
-    mbar_wait(&sm.full[s], (c / STAGES) & 1, DRB_ERR_FULL_WAIT);
+    // after the first wait of this thread that ran out no later wait spins again: the error word is set, the
+    // results are void, and a vocabulary-sized launch must not hold the GPU for a second per remaining chunk
+    if (!dead) dead = !mbar_wait(&sm.full[s], (c / STAGES) & 1, DRB_ERR_FULL_WAIT);
     if (MODE != BF16_PLAIN && S_IN_STAGE) {
       const __half* ss = reinterpret_cast<const __half*>(st + U * RB * ROW_BYTES);
 #pragma unroll
