@@ -536,6 +536,23 @@ extern "C" int drb_moe_prefill_block(const uint8_t* gu_q, const __half2* gu_sm, 
     return -1;
   const DrbDevice& dev = drb_device(st);
   if (!dev.ready) return -2;
+  if (x_f16 && E <= pft::MAX_ITEM_SETS - 1) {
+    // fp16 rows: the kernels of moe_prefill_tma.cuh (weights by tiled TMA, token tiles by asynchronous copies)
+    const uint64_t ne = (uint64_t)(E > 0 ? E : 1);
+    CUtensorMap m_gu, m_d, m_sgu, m_sd;
+    if (pft::map_gate_up(&m_gu, gu_q, ne, I, H / 2) || pft::map_gate_up(&m_sgu, sgu_q, 1, I, H) ||
+        pft::map_rows(&m_d, d_q, ne * H, I / 2) || pft::map_rows(&m_sd, sd_q, H, I))
+      return -3;
+    const dim3 grid2(2 * dev.sms), block2(pft::THREADS);
+    const int ee = E > 0 ? E : 0, rs = rows_sh > 0 ? rows_sh : 0;
+    const __half* rows16 = reinterpret_cast<const __half*>(xb);
+    drb_launch(pft::k_grouped_tma<0>, grid2, block2, pft::SMEM_BYTES, st, false, m_gu, gu_sm, m_sgu, sgu_s, rows16, rows16, (void*)act,
+               (void*)sh_act, offsets, counts, ee, rs, row_of, (const int*)nullptr);
+    drb_launch(pft::k_grouped_tma<1>, grid2, block2, pft::SMEM_BYTES, st, false, m_d, d_sm, m_sd, sd_s,
+               reinterpret_cast<const __half*>(act), reinterpret_cast<const __half*>(sh_act), (void*)y, (void*)sh_out, offsets, counts, ee, rs,
+               (const int*)nullptr, y_row_of);
+    return 0;
+  }
   const dim3 grid(pfmma::BLOCKS_PER_SM * dev.sms), block(pfmma::THREADS);
   const pfmma::SharedExpert s0{sgu_q, sgu_s, (const void*)xb, (void*)sh_act, rows_sh};
   const pfmma::SharedExpert s1{sd_q, sd_s, (const void*)sh_act, (void*)sh_out, rows_sh};

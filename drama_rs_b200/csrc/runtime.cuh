@@ -29,6 +29,7 @@ namespace pf { static cudaError_t configure_all(); }
 namespace moe { static cudaError_t configure_all(); namespace f8 { static cudaError_t configure_all(); } }
 namespace stack { static cudaError_t configure_all(); }
 namespace pfmma { static cudaError_t configure_all(); }
+namespace pft { static cudaError_t configure_all(); }
 
 namespace rt {
 
@@ -54,6 +55,7 @@ static cudaError_t setup(int d) {
   if ((e = moe::f8::configure_all()) != cudaSuccess) return e;
   if ((e = stack::configure_all()) != cudaSuccess) return e;
   if ((e = pfmma::configure_all()) != cudaSuccess) return e;
+  if ((e = pft::configure_all()) != cudaSuccess) return e;
   dv.ready = true;
   g_dev[d] = dv;
   g_ready[d].store(true, std::memory_order_release);
