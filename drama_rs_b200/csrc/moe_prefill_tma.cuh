@@ -23,6 +23,8 @@
 // shared expert of src/engine.rs:351-355, 560-562.
 #pragma once
 
+#include <type_traits>
+
 #include <cuda.h>  // CUtensorMap and the encode function's type only: the entry point is resolved at run time
 
 #include "common.cuh"
@@ -99,18 +101,22 @@ DRB_DEV void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1, int 
       : "memory");
 }
 
-// Eight nibbles of one word -> eight fp16 weights q*s + m in k order. 0x6400 | q is the half 1024 + q; subtracting
-// 1024 is exact, the fused multiply-add rounds once.
+// Eight nibbles of one word -> eight fp16 weights q*s + m in k order. A nibble in bits 0..3 of a 16-bit half, or-ed
+// into 0x6400, is the half 1024 + q; a nibble in bits 4..7, or-ed into 0x5400, is the half 64 + q (the unit in the last
+// place of 64 is 1/16, sixteen of them per step of the nibble): one shift serves the upper byte of both halves.
+// Subtracting the offset is exact, the fused multiply-add rounds once.
 DRB_DEV uint4 dequant8_nat(uint32_t w, __half2 s2, __half2 m2) {
   const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
+  const __half2 k64 = __half2half2(__ushort_as_half((unsigned short)0x5400));
+  const uint32_t w8 = w >> 8;
   uint32_t t[4];  // (k0, k4), (k1, k5), (k2, k6), (k3, k7)
   t[0] = lop3_and_or(w, 0x000F000Fu, 0x64006400u);
-  t[1] = lop3_and_or(w >> 4, 0x000F000Fu, 0x64006400u);
-  t[2] = lop3_and_or(w >> 8, 0x000F000Fu, 0x64006400u);
-  t[3] = lop3_and_or(w >> 12, 0x000F000Fu, 0x64006400u);
+  t[1] = lop3_and_or(w, 0x00F000F0u, 0x54005400u);
+  t[2] = lop3_and_or(w8, 0x000F000Fu, 0x64006400u);
+  t[3] = lop3_and_or(w8, 0x00F000F0u, 0x54005400u);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const __half2 r = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t[i]), k1024), s2, m2);
+    const __half2 r = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t[i]), (i & 1) ? k64 : k1024), s2, m2);
     t[i] = *reinterpret_cast<const uint32_t*>(&r);
   }
   return make_uint4(prmt(t[0], t[1], 0x5410u), prmt(t[2], t[3], 0x5410u), prmt(t[0], t[1], 0x7632u), prmt(t[2], t[3], 0x7632u));
@@ -260,6 +266,23 @@ __global__ void __launch_bounds__(THREADS, 2)
       if (lane == 0) mbar_arrive(&ctl.bfull[b_done % NBT]);
       ++b_done;
     };
+    // Announces requested tiles, oldest first, each as soon as it has landed, until at most `keep` are still under way
+    // (cp.async.wait_group takes its count as an immediate: one instance per possible count).
+    auto settle = [&](unsigned requested, unsigned keep) {
+      static_assert(NBT == 6, "one step per possible count");
+      auto step = [&](auto n) {
+        if (requested - b_done > (unsigned)decltype(n)::value && (unsigned)decltype(n)::value >= keep) {
+          asm volatile("cp.async.wait_group %0;" ::"n"(decltype(n)::value) : "memory");
+          announce();
+        }
+      };
+      step(std::integral_constant<int, 5>{});
+      step(std::integral_constant<int, 4>{});
+      step(std::integral_constant<int, 3>{});
+      step(std::integral_constant<int, 2>{});
+      step(std::integral_constant<int, 1>{});
+      step(std::integral_constant<int, 0>{});
+    };
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
       const Item it = decode(item);
       if (!dead) dead = !mbar_wait(&ctl.tabfull[it_no % NTAB], (it_no / NTAB) & 1, DRB_ERR_FULL_WAIT);
@@ -284,8 +307,7 @@ __global__ void __launch_bounds__(THREADS, 2)
           // Before a wait that may block, announce everything that is under way: a tile must not be held back by
           // the request for a later one.
           if (!mbar_try_wait(&ctl.bempty[s], ((ch_no / NBT) - 1) & 1)) {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            while (b_done < ch_no) announce();
+            settle(ch_no, 0);
             dead = !mbar_wait(&ctl.bempty[s], ((ch_no / NBT) - 1) & 1, DRB_ERR_EMPTY_WAIT);
           }
         }
@@ -294,14 +316,10 @@ __global__ void __launch_bounds__(THREADS, 2)
         for (int i = 0; i < BPL; ++i)
           if (bsrc[i]) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(tile + bdst[i]), "l"(bsrc[i] + (size_t)kc * KC * 2) : "memory");
         asm volatile("cp.async.commit_group;" ::: "memory");
-        if (ch_no - b_done >= (unsigned)(NBT - 1)) {  // all but the latest NBT - 1 requests have completed
-          asm volatile("cp.async.wait_group %0;" ::"n"(NBT - 1) : "memory");
-          announce();
-        }
+        settle(ch_no + 1, 2);  // two tiles stay under way (about an L2 round trip of requests); older ones are announced
       }
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    while (b_done < ch_no) announce();
+    settle(ch_no, 0);
   } else if (warp == TABLE_WARP) {
     // ================= table warp: the tokens of every item, one item ahead =================
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
