@@ -201,8 +201,8 @@ int drb_moe_group(const int* idx, int rows, int topk, int e_lo, int e_n, int* co
  * y [slots, h] f32; y_row_of (or NULL): slot -> row of y. rows_sh = 0 skips the shared expert, e = 0 the routed
  * ones. Every pointer except row_of / y_row_of must be a valid device address even for a part that does not run
  * (any buffer will do): NULL returns -1. Intermediates are fp16: SwiGLU values beyond +-65504 are clamped.
- * h == 2048, i == 512, else -1.  * With x_f16 != 0 and e <= 256 the weights are addressed through TMA tensor maps built from the pointers given
- * (gu_q / d_q: e experts from the pointer on); -3 when the driver refuses a map. */
+ * h == 2048, i == 512, else -1. With x_f16 != 0 and e <= 256 the weights are addressed through TMA tensor maps built
+ * from the pointers given (gu_q / d_q: e experts from the pointer on); -3 when the driver refuses a map. */
 int drb_moe_prefill_block(const uint8_t* gu_q, const dr_half* gu_sm, const uint8_t* d_q, const dr_half* d_sm,
                           const int8_t* sgu_q, const dr_half* sgu_s, const int8_t* sd_q, const dr_half* sd_s,
                           const dr_bf16* xb, const int* row_of, const int* offsets, const int* counts, dr_bf16* act,
