@@ -594,7 +594,7 @@ def prefill_ep_extra(torch, dist, layer, st, ext_stream, rank: int, world: int) 
             "routing_equals_single_gpu_on_every_rank": d[4] == 0.0,
             "max_abs_diff_to_single_gpu": {"eager": d[0], "graph_replay": d[1], "output_scale": d[2]},
             "capacity_slots_per_peer": cap, "capacity_worst_case": max_rows * SHAPE.topk, "overflow": bool(d[3]),
-            "exchange": "2 all_to_all_single of fixed size per layer: fp16 rows + expert ids out, f32 results back"}
+            "exchange": f"2 fixed-size exchanges per layer (fp16 rows + expert ids out, f32 results back) by {ops.exchange_kind}"}
 
 
 def decode64_ep_extra(torch, dist, layers, st, ext_stream, rank: int, world: int) -> dict:

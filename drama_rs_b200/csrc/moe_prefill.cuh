@@ -191,6 +191,55 @@ __global__ void __launch_bounds__(256)
   for (int c = lane; c < row_bytes / 16; c += 32) dst[c] = __ldg(src + c);
 }
 
+// The exchange of an expert-parallel step over NVLink peer stores (drb_ep_put / drb_ep_signal / drb_ep_wait): block p of
+// this rank's send buffer goes straight into peer p's receive buffer, slot `rank`, with 16-byte stores; every
+// writing thread fences at system scope after its stores, so that the flag the next kernel writes to the peer
+// can only be seen after the data.
+__global__ void __launch_bounds__(256)
+    k_ep_put(const uint4* __restrict__ send, uint4* const* __restrict__ peer_recv, int rank, size_t block_vecs) {
+  pdl_wait();
+  const int p = blockIdx.y;
+  const uint4* src = send + (size_t)p * block_vecs;
+  uint4* dst = peer_recv[p] + (size_t)rank * block_vecs;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < block_vecs; i += (size_t)gridDim.x * blockDim.x) dst[i] = __ldg(src + i);
+  __threadfence_system();
+}
+
+// ++*step; then peer p's flag word `rank` takes the new step number (one thread per peer).
+__global__ void __launch_bounds__(64) k_ep_signal(unsigned* const* __restrict__ peer_flags, int world, int rank, unsigned* __restrict__ step) {
+  pdl_wait();
+  __shared__ unsigned now;
+  if (threadIdx.x == 0) now = ++*step;
+  __syncthreads();
+  __threadfence_system();
+  if ((int)threadIdx.x < world) {
+    volatile unsigned* f = peer_flags[threadIdx.x] + rank;
+    *f = now;
+  }
+}
+
+// ++*step; then waits until every peer's flag has reached the new step number. Bounded: a peer that never signals
+// costs `limit` polls, sets the error word and lets the step run on (its result is void).
+__global__ void __launch_bounds__(64) k_ep_wait(const unsigned* __restrict__ flags, int world, unsigned* __restrict__ step, unsigned limit) {
+  pdl_wait();
+  __shared__ unsigned now;
+  if (threadIdx.x == 0) now = ++*step;
+  __syncthreads();
+  if ((int)threadIdx.x < world) {
+    const volatile unsigned* f = flags + threadIdx.x;
+    unsigned it = 0;
+    // signed distance: the counters wrap together
+    while ((int)(*f - now) < 0) {
+      if (++it >= limit) {
+        atomicMax(&g_drb_error, (unsigned)DRB_ERR_GRID_WAIT);
+        break;
+      }
+      if (it > 64) __nanosleep(it > 4096 ? 256 : 32);
+    }
+  }
+  __threadfence_system();
+}
+
 // x[r] += sigmoid(sgate[r]) * shared[r] + sum_k w[r,k] * Y[slot_of[r,k]], k ascending (fixed order, so
 // the result does not depend on how slots were handed out).
 __global__ void __launch_bounds__(256)
@@ -383,6 +432,7 @@ static cudaError_t configure_all() {
   if ((e = drb_carveout(k_group)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_ep_plan)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_ep_scatter)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_ep_put)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_dequant_q8)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_f32_to_bf16)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_swiglu_rows)) != cudaSuccess) return e;
@@ -512,6 +562,36 @@ extern "C" int drb_ep_group(const void* recv, int world, int cap, int row_bytes,
   if (row_bytes % 16 != 0 || world <= 0 || per <= 0 || per > pf::GRP_MAX_E || cap <= 0) return -1;
   drb_launch(pf::k_group, dim3(1), dim3(pf::GRP_THREADS), 0, st, false, (const int*)recv, world * cap, 1, 0, per, counts, offsets,
              slot_of, row_of, pair_of, cap, drb_ep_block_rows(cap, row_bytes), row_bytes / 4);
+  return 0;
+}
+
+// The expert-parallel exchange over NVLink peer stores instead of a library collective (no counterpart in the
+// reference). peer_recv / peer_flags: device arrays of `world` pointers, entry p = rank p's receive buffer / flag
+// array (memory every rank can store to: symmetric memory), this rank's own included.
+//   drb_ep_put     block p (block_bytes each) of `send` -> peer p's receive buffer at slot `rank`
+//   drb_ep_signal  ++*step (device word, zero at start on every rank); peer p's flag [rank] = *step
+//   drb_ep_wait    ++*step (another device word, zero at start); returns once flags [0, world) have all reached it, or
+//                  after poll_limit polls (error word set, the step's result is void)
+// One exchange = put, signal on the sender; wait on the receiver before it reads. A rank starts the next exchange
+// into a peer's buffer only after that peer's reply to the current one, so a buffer is never overwritten while it
+// is read. block_bytes % 16 == 0, world <= 64, else -1.
+extern "C" int drb_ep_put(const void* send, void* const* peer_recv, int world, int rank, size_t block_bytes, cudaStream_t st) {
+  if (!send || !peer_recv || world <= 0 || world > 64 || rank < 0 || rank >= world || block_bytes % 16 != 0) return -1;
+  if (block_bytes == 0) return 0;
+  const size_t vecs = block_bytes / 16;
+  const unsigned per = (unsigned)((vecs + 4095) / 4096);  // about sixteen 16-byte stores per thread
+  drb_launch(pf::k_ep_put, dim3(per < 1 ? 1 : (per > 64 ? 64 : per), (unsigned)world), dim3(256), 0, st, false,
+             static_cast<const uint4*>(send), reinterpret_cast<uint4* const*>(peer_recv), rank, vecs);
+  return 0;
+}
+extern "C" int drb_ep_signal(unsigned* const* peer_flags, int world, int rank, unsigned* step, cudaStream_t st) {
+  if (!peer_flags || !step || world <= 0 || world > 64 || rank < 0 || rank >= world) return -1;
+  drb_launch(pf::k_ep_signal, dim3(1), dim3(64), 0, st, false, peer_flags, world, rank, step);
+  return 0;
+}
+extern "C" int drb_ep_wait(const unsigned* flags, int world, unsigned* step, unsigned poll_limit, cudaStream_t st) {
+  if (!flags || !step || world <= 0 || world > 64 || poll_limit == 0) return -1;
+  drb_launch(pf::k_ep_wait, dim3(1), dim3(64), 0, st, false, flags, world, step, poll_limit);
   return 0;
 }
 

@@ -21,8 +21,10 @@ prefill-side MoE block (src/engine.rs:544-604) that the benchmark configurations
     the shared expert and the residual (dr_moe_combine), so the result does not depend on N;
   * the replicated shared expert runs on a second stream beside the dispatch exchange.
 
-The exchange is NCCL over NVLink on GPUs (gloo on CPU in the tests). Received rows land in this rank's
-own memory before any kernel reads them; nothing here reads a peer's memory directly.
+The exchange is, on GPUs, this library's own: every rank stores its blocks straight into the peers' receive
+buffers over NVLink (symmetric memory, drb_ep_put) and signals with a step counter (drb_ep_signal / drb_ep_wait,
+bounded); `EpGpu(p2p=False)`, and the CPU tests over gloo, use the library collective instead. Received rows
+land in this rank's own memory before any kernel reads them: nothing here loads from a peer's memory.
 
 `ops` supplies the per-rank compute (the C-ABI kernels on a GPU; the tests plug in the oracle on CPU), so
 the bookkeeping below is the same code on both.
@@ -64,14 +66,17 @@ def ep_moe_block(x: torch.Tensor, ops, cap: int, group=None) -> torch.Tensor:
     ops.combine(x, y_home, slot_of, wts, sgate, shared) -> x'             (fixed k order)
     ops.recv_like(send) / ops.home_like(y_send): buffers to receive into
     """
+    exchange = getattr(ops, "exchange", None)  # an exchange of the ops' own (peer stores over NVLink) instead of the collective
     rows16, idx, wts, sgate = ops.route(x)
     ops.shared_begin(rows16)
     send, slot_of = ops.pack(rows16, idx, cap)
     recv = ops.recv_like(send)
-    _all_to_all(recv, send, group)
+    if exchange is None or not exchange(0, recv, send):
+        _all_to_all(recv, send, group)
     y_send = ops.experts(recv)
     y_home = ops.home_like(y_send)
-    _all_to_all(y_home, y_send, group)
+    if exchange is None or not exchange(1, y_home, y_send):
+        _all_to_all(y_home, y_send, group)
     shared = ops.shared_end()
     return ops.combine(x, y_home, slot_of, wts, sgate, shared)
 
@@ -110,7 +115,8 @@ class EpGpu:
     launches can be captured). One workspace serves every layer of a stack: `layer` is switched per call. The
     kernels run on `st`, which is also made torch's current stream for the collectives (`stream`)."""
 
-    def __init__(self, layer, rank: int, world: int, max_rows: int, cap: int, topk: int = 8, eps: float = 1e-6, st=None) -> None:
+    def __init__(self, layer, rank: int, world: int, max_rows: int, cap: int, topk: int = 8, eps: float = 1e-6, st=None,
+                 p2p: bool = True, group=None) -> None:
         import ctypes as C
 
         from . import ffi
@@ -145,7 +151,17 @@ class EpGpu:
         self.overflow_word = torch.zeros(1, dtype=i32, device=dev)
         # Row slots that are never written travel as they are: zero them once so that what travels is finite.
         self.send = torch.zeros((world, self.blk_rows, h), dtype=f16, device=dev)
-        self.recv = torch.zeros((world, self.blk_rows, h), dtype=f16, device=dev)
+        self.p2p = bool(p2p) and world > 1 and dist.is_initialized()
+        self.exchange_kind = "all_to_all_single (NCCL)"
+        if self.p2p:
+            try:
+                self._symmetric_buffers(world, n, h, dev, group)
+                self.exchange_kind = "peer stores over NVLink into symmetric memory + step flags (drb_ep_put / signal / wait)"
+            except Exception as exc:  # noqa: BLE001 - no symmetric memory on this system: the collective does the exchange
+                self.p2p = False
+                self.exchange_kind += f" (symmetric memory unavailable: {type(exc).__name__})"
+        if not self.p2p:
+            self.recv = torch.zeros((world, self.blk_rows, h), dtype=f16, device=dev)
         self.counts = torch.empty(per, dtype=i32, device=dev)
         self.offsets = torch.empty(per, dtype=i32, device=dev)
         self.slot2 = torch.empty(n, dtype=i32, device=dev)
@@ -153,8 +169,47 @@ class EpGpu:
         self.pair_of = torch.empty(n, dtype=i32, device=dev)
         self.ap = torch.empty((n, i), dtype=f16, device=dev)
         self.y_send = torch.zeros((n, h), dtype=f32, device=dev)
-        self.y_home = torch.zeros((n, h), dtype=f32, device=dev)
+        if not self.p2p:
+            self.y_home = torch.zeros((n, h), dtype=f32, device=dev)
         self.n_rows = 0
+
+    def _symmetric_buffers(self, world: int, n: int, h: int, dev: str, group) -> None:
+        """Receive buffers and flag words in symmetric memory, and the tables of every rank's addresses of them."""
+        import torch.distributed._symmetric_memory as symm_mem
+
+        g = group if group is not None else dist.group.WORLD
+        self.recv = symm_mem.empty((world, self.blk_rows, h), dtype=torch.float16, device=dev)
+        self.y_home = symm_mem.empty((n, h), dtype=torch.float32, device=dev)
+        self.flags = symm_mem.empty((2, 64), dtype=torch.int32, device=dev)  # [dispatch | results][source rank]
+        self.recv.zero_()
+        self.y_home.zero_()
+        self.flags.zero_()
+        torch.cuda.synchronize()
+        handles = [symm_mem.rendezvous(t, g) for t in (self.recv, self.y_home, self.flags)]
+        i64 = torch.int64
+        self.peer_bufs = [torch.tensor(list(hd.buffer_ptrs), dtype=i64, device=dev) for hd in handles[:2]]
+        fl = list(handles[2].buffer_ptrs)
+        self.peer_flags = [torch.tensor([p + 256 * which for p in fl], dtype=i64, device=dev) for which in (0, 1)]
+        self.steps = torch.zeros(4, dtype=torch.int32, device=dev)  # signalled / awaited step of each direction
+        self._handles = handles
+        torch.cuda.synchronize()
+        dist.barrier(group=g)  # nobody stores into a peer before that peer has cleared its flags
+
+    def exchange(self, which: int, out: torch.Tensor, inp: torch.Tensor) -> bool:
+        """Direction `which` (0: rows to the owners, 1: results home) by peer stores; False when this object uses the
+        collective."""
+        if not self.p2p:
+            return False
+        from .gpu import launched
+
+        l, st = self.l, self.st.raw
+        block_bytes = inp[0].numel() * inp.element_size() if which == 0 else (inp.shape[0] // self.world) * inp.shape[1] * inp.element_size()
+        launched(l.drb_ep_put(self._p(inp), self._p(self.peer_bufs[which]), self.world, self.rank, block_bytes, st), "ep_put", debug=False)
+        launched(l.drb_ep_signal(self._p(self.peer_flags[which]), self.world, self.rank, self.C.c_void_p(self.steps.data_ptr() + 8 * which), st),
+                 "ep_signal", debug=False)
+        launched(l.drb_ep_wait(self.C.c_void_p(self.flags.data_ptr() + 256 * which), self.world, self.C.c_void_p(self.steps.data_ptr() + 8 * which + 4),
+                               1 << 24, st), "ep_wait", debug=False)
+        return True
 
     def _p(self, t: torch.Tensor):
         return self.C.c_void_p(t.data_ptr())

@@ -66,6 +66,9 @@ SIGNATURES: dict[str, tuple] = {
     "drb_ep_block_rows": (I32, [I32, I32]),
     "drb_ep_pack": (I32, [P, P, I32, I32, I32, I32, I32, I32, P, P, P, P, P]),
     "drb_ep_group": (I32, [P, I32, I32, I32, I32, P, P, P, P, P, P]),
+    "drb_ep_put": (I32, [P, P, I32, I32, SZ, P]),
+    "drb_ep_signal": (I32, [P, I32, I32, P, P]),
+    "drb_ep_wait": (I32, [P, I32, P, U32, P]),
     "drb_rmsnorm_f16": (I32, [P, P, P, I32, I32, F32, P]),
     "drb_router_logits_f16": (I32, [P, P, P, I32, I32, I32, F32, P]),
     "drb_router_logits": (I32, [P, P, P, I32, I32, I32, F32, P]),

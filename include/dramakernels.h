@@ -225,6 +225,19 @@ int drb_ep_pack(const void* rows, const int* idx, int n_rows, int topk, int per,
                 void* send, int* slot_of, int* dst_row, unsigned* overflow, dr_stream st);
 int drb_ep_group(const void* recv, int world, int cap, int row_bytes, int per, int* counts, int* offsets, int* slot_of,
                  int* row_of, int* pair_of, dr_stream st);
+/* The exchange itself over NVLink peer stores instead of a library collective. peer_recv / peer_flags: device arrays
+ * of `world` pointers, entry p = rank p's receive buffer / flag array (memory every rank can store to, e.g. symmetric
+ * memory), this rank's own included.
+ *   drb_ep_put     block p (block_bytes each) of `send` -> peer p's receive buffer at slot `rank`, 16-byte stores
+ *   drb_ep_signal  ++*step (device word, zero at start on every rank); peer p's flag [rank] = *step
+ *   drb_ep_wait    ++*step (another device word, zero at start); returns once flags [0, world) have all reached it, or
+ *                  after poll_limit polls (drb_device_error() then reads non-zero and the step's result is void)
+ * One exchange = put + signal on the sender, wait on the receiver before it reads. A rank may start its next
+ * exchange into a peer's buffer only after that peer's reply to the current one (the combine step's wait).
+ * block_bytes % 16 == 0, world <= 64, else -1. */
+int drb_ep_put(const void* send, void* const* peer_recv, int world, int rank, size_t block_bytes, dr_stream st);
+int drb_ep_signal(unsigned* const* peer_flags, int world, int rank, unsigned* step, dr_stream st);
+int drb_ep_wait(const unsigned* flags, int world, unsigned* step, unsigned poll_limit, dr_stream st);
 /* The checkpoint quantisers of the reference's converter on the GPU (tools/convert.py:33-41 `quant_q8`, 44-101
  * `quant_q4_groups` / `quant_q4`: 24-step clipping search with a least-squares refit). w: `groups` x 64 (q4) or
  * 128 (q8) consecutive floats, i.e. a row-major weight whose last dimension is a multiple of the group; outputs in

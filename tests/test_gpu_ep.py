@@ -24,8 +24,9 @@ def _watchdog(seconds: int = 120) -> None:
     faulthandler.dump_traceback_later(seconds, exit=True, file=sys.stderr)
 
 
-def worker(rank, world, port, out, cap):
-    """One layer through ep_moe_block: eager once, then captured in a CUDA graph and replayed twice."""
+def worker(rank, world, port, out, cap, p2p=True):
+    """One layer through ep_moe_block: eager once, then captured in a CUDA graph and replayed twice. p2p: the exchange by
+    this library's peer stores (falls back to the collective where symmetric memory is unavailable), else NCCL."""
     import torch.distributed as dist
 
     _watchdog()
@@ -43,7 +44,9 @@ def worker(rank, world, port, out, cap):
     x_all = synth.make_x(11, ROWS, SHAPE.hidden)
     lo, hi = ROWS * rank // world, ROWS * (rank + 1) // world
     max_rows = -(-ROWS // world)
-    ops = ep.EpGpu(layer, rank, world, max_rows, cap, st=st)
+    ops = ep.EpGpu(layer, rank, world, max_rows, cap, st=st, p2p=p2p)
+    if rank == 0:
+        print("exchange:", ops.exchange_kind, flush=True)
     with torch.cuda.stream(ops.stream):
         x0 = torch.from_numpy(x_all[lo:hi].copy()).cuda()
         x = x0.clone()
@@ -67,6 +70,12 @@ def worker(rank, world, port, out, cap):
     np.save(os.path.join(out, f"replay{rank}.npy"), replay)
     np.save(os.path.join(out, f"idx{rank}.npy"), idx)
     np.save(os.path.join(out, f"over{rank}.npy"), np.array([over_eager, over_replay]))
+    if rank == 0:
+        with open(os.path.join(out, "exchange.txt"), "w") as f:
+            f.write(ops.exchange_kind)
+    from tests.helpers import device_error_word
+
+    assert device_error_word() == 0, "a bounded wait of the exchange ran out"
     dist.destroy_process_group()
 
 
@@ -88,8 +97,8 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("world", [1, 2])
-def test_ep_eager_and_graph_match_the_single_gpu_block(tmp_path, world):
+@pytest.mark.parametrize("world,p2p", [(1, True), (2, True), (2, False)])
+def test_ep_eager_and_graph_match_the_single_gpu_block(tmp_path, world, p2p):
     if torch.cuda.device_count() < world:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -97,7 +106,8 @@ def test_ep_eager_and_graph_match_the_single_gpu_block(tmp_path, world):
     from drama_rs_b200 import ep
 
     cap = ep.capacity(-(-ROWS // world), SHAPE.topk, world)
-    mp.spawn(worker, args=(world, _free_port(), str(tmp_path), cap), nprocs=world, join=True)
+    mp.spawn(worker, args=(world, _free_port(), str(tmp_path), cap, p2p), nprocs=world, join=True)
+    print("exchange:", open(tmp_path / "exchange.txt").read())
     ref, ref_idx = _single_gpu_reference()
     assert not any(np.load(tmp_path / f"over{r}.npy").any() for r in range(world))
     # the routing is the single-GPU routing, bit for bit, at every split
