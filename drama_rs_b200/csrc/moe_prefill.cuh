@@ -147,20 +147,26 @@ __global__ void __launch_bounds__(GRP_THREADS)
 // results with), dst_row[pair] = the row of `send` that the pair's row must be copied to (-1: dropped).
 // A pair that finds its block full is dropped, its slot_of points at a valid slot of the block, and *overflow is set:
 // the step's result is then void and the caller must repeat it with a larger capacity. Nothing waits or faults.
+// With `peers` (device array of every rank's receive buffer) block o is not a part of `send` but this rank's slot in
+// peer o's receive buffer: the ids and rows are stored straight into the owner's memory over NVLink, and every
+// thread fences at system scope after its stores (the flag that announces them is written by a later kernel).
 __global__ void __launch_bounds__(GRP_THREADS)
     k_ep_plan(const int* __restrict__ idx, int pairs, int per, int world, int cap, int blk_rows, int row_ints,
-              int* __restrict__ send, int* __restrict__ slot_of, int* __restrict__ dst_row, unsigned* __restrict__ overflow) {
+              int* __restrict__ send_local, int* __restrict__ slot_of, int* __restrict__ dst_row, unsigned* __restrict__ overflow,
+              int* const* __restrict__ peers, int rank) {
   pdl_wait();
   __shared__ int cnt[64];
+  __shared__ int* blk[64];
   const int t = threadIdx.x;
   if (t < 64) cnt[t] = 0;
+  if (t < world) blk[t] = peers ? peers[t] + (size_t)rank * blk_rows * row_ints : send_local + (size_t)t * blk_rows * row_ints;
   __syncthreads();
   for (int p = t; p < pairs; p += GRP_THREADS) {
     const int e = __ldg(idx + p);
     const int o = e / per;
     const int r = atomicAdd(&cnt[o], 1);
     if (r < cap) {
-      send[((size_t)o * blk_rows + cap) * row_ints + r] = e - o * per;
+      blk[o][(size_t)cap * row_ints + r] = e - o * per;
       slot_of[p] = o * cap + r;
       dst_row[p] = o * blk_rows + r;
     } else {
@@ -172,14 +178,15 @@ __global__ void __launch_bounds__(GRP_THREADS)
   __syncthreads();
   for (int j = t; j < world * cap; j += GRP_THREADS) {
     const int o = j / cap, r = j - o * cap;
-    if (r >= cnt[o]) send[((size_t)o * blk_rows + cap) * row_ints + r] = per;
+    if (r >= cnt[o]) blk[o][(size_t)cap * row_ints + r] = per;
   }
+  if (peers) __threadfence_system();
 }
 
 // Step 2: one warp per pair copies its row (row_bytes each, 16-byte accesses) to its place in the send buffer.
 __global__ void __launch_bounds__(256)
     k_ep_scatter(const unsigned char* __restrict__ rows, int pairs, int topk, const int* __restrict__ dst_row,
-                 unsigned char* __restrict__ send, int row_bytes) {
+                 unsigned char* __restrict__ send, int row_bytes, unsigned char* const* __restrict__ peers, int rank, int blk_rows) {
   pdl_wait();
   const int lane = threadIdx.x & 31;
   const int p = blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -187,8 +194,15 @@ __global__ void __launch_bounds__(256)
   const int d = __ldg(dst_row + p);
   if (d < 0) return;
   const uint4* src = reinterpret_cast<const uint4*>(rows + (size_t)(p / topk) * row_bytes);
-  uint4* dst = reinterpret_cast<uint4*>(send + (size_t)d * row_bytes);
+  uint4* dst;
+  if (peers) {
+    const int o = d / blk_rows;
+    dst = reinterpret_cast<uint4*>(peers[o] + ((size_t)rank * blk_rows + (d - o * blk_rows)) * row_bytes);
+  } else {
+    dst = reinterpret_cast<uint4*>(send + (size_t)d * row_bytes);
+  }
   for (int c = lane; c < row_bytes / 16; c += 32) dst[c] = __ldg(src + c);
+  if (peers) __threadfence_system();
 }
 
 // The exchange of an expert-parallel step over NVLink peer stores (drb_ep_put / drb_ep_signal / drb_ep_wait): block p of
@@ -551,10 +565,25 @@ extern "C" int drb_ep_pack(const void* rows, const int* idx, int n_rows, int top
   const int pairs = n_rows * topk;
   const int blk_rows = drb_ep_block_rows(cap, row_bytes);
   drb_launch(pf::k_ep_plan, dim3(1), dim3(pf::GRP_THREADS), 0, st, false, idx, pairs, per, world, cap, blk_rows, row_bytes / 4,
-             (int*)send, slot_of, dst_row, overflow);
+             (int*)send, slot_of, dst_row, overflow, (int* const*)nullptr, 0);
   if (pairs > 0)
     drb_launch(pf::k_ep_scatter, dim3((pairs + 7) / 8), dim3(256), 0, st, false, (const unsigned char*)rows, pairs, topk,
-               (const int*)dst_row, (unsigned char*)send, row_bytes);
+               (const int*)dst_row, (unsigned char*)send, row_bytes, (unsigned char* const*)nullptr, 0, blk_rows);
+  return 0;
+}
+// drb_ep_pack with the blocks stored straight into the owners' receive buffers (peer_recv: device array of `world`
+// pointers as for drb_ep_put; this rank's block in peer o's buffer is block `rank`). Follow with drb_ep_signal.
+extern "C" int drb_ep_pack_peers(const void* rows, const int* idx, int n_rows, int topk, int per, int world, int cap, int row_bytes,
+                                 void* const* peer_recv, int rank, int* slot_of, int* dst_row, unsigned* overflow, cudaStream_t st) {
+  if (row_bytes % 16 != 0 || world <= 0 || world > 64 || per <= 0 || cap <= 0 || topk <= 0 || !peer_recv || rank < 0 || rank >= world)
+    return -1;
+  const int pairs = n_rows * topk;
+  const int blk_rows = drb_ep_block_rows(cap, row_bytes);
+  drb_launch(pf::k_ep_plan, dim3(1), dim3(pf::GRP_THREADS), 0, st, false, idx, pairs, per, world, cap, blk_rows, row_bytes / 4,
+             (int*)nullptr, slot_of, dst_row, overflow, reinterpret_cast<int* const*>(peer_recv), rank);
+  if (pairs > 0)
+    drb_launch(pf::k_ep_scatter, dim3((pairs + 7) / 8), dim3(256), 0, st, false, (const unsigned char*)rows, pairs, topk,
+               (const int*)dst_row, (unsigned char*)nullptr, row_bytes, reinterpret_cast<unsigned char* const*>(peer_recv), rank, blk_rows);
   return 0;
 }
 extern "C" int drb_ep_group(const void* recv, int world, int cap, int row_bytes, int per, int* counts, int* offsets, int* slot_of,
@@ -605,11 +634,11 @@ extern "C" int drb_ep_wait(const unsigned* flags, int world, unsigned* step, uns
 // Every pointer of a part that runs must be a valid device address; with E = 0 or rows_sh = 0 the arrays of the part
 // that does not run are not used, but must still be valid addresses (any buffer will do, NULL will not): the compiler
 // may issue a load ahead of the branch that decides whether its value is needed. row_of and y_row_of may be NULL.
-extern "C" int drb_moe_prefill_block(const uint8_t* gu_q, const __half2* gu_sm, const uint8_t* d_q, const __half2* d_sm,
+static int prefill_block_impl(const uint8_t* gu_q, const __half2* gu_sm, const uint8_t* d_q, const __half2* d_sm,
                                      const int8_t* sgu_q, const __half* sgu_s, const int8_t* sd_q, const __half* sd_s,
                                      const __nv_bfloat16* xb, const int* row_of, const int* offsets, const int* counts,
                                      __nv_bfloat16* act, float* y, __nv_bfloat16* sh_act, float* sh_out, int rows_sh, int E,
-                                     int H, int I, int x_f16, const int* y_row_of, cudaStream_t st) {
+                                     int H, int I, int x_f16, const int* y_row_of, float* const* peer_y, int peer_cap, int peer_rank, cudaStream_t st) {
   if (H != pf::H || I != pf::I) return -1;
   if (E <= 0 && rows_sh <= 0) return 0;
   if (!gu_q || !gu_sm || !d_q || !d_sm || !sgu_q || !sgu_s || !sd_q || !sd_s || !xb || !offsets || !counts || !act || !y || !sh_act || !sh_out)
@@ -627,12 +656,13 @@ extern "C" int drb_moe_prefill_block(const uint8_t* gu_q, const __half2* gu_sm, 
     const int ee = E > 0 ? E : 0, rs = rows_sh > 0 ? rows_sh : 0;
     const __half* rows16 = reinterpret_cast<const __half*>(xb);
     drb_launch(pft::k_grouped_tma<0>, grid2, block2, pft::SMEM_BYTES, st, false, m_gu, gu_sm, m_sgu, sgu_s, rows16, rows16, (void*)act,
-               (void*)sh_act, offsets, counts, ee, rs, row_of, (const int*)nullptr);
+               (void*)sh_act, offsets, counts, ee, rs, row_of, (const int*)nullptr, (float* const*)nullptr, 0, 0);
     drb_launch(pft::k_grouped_tma<1>, grid2, block2, pft::SMEM_BYTES, st, false, m_d, d_sm, m_sd, sd_s,
                reinterpret_cast<const __half*>(act), reinterpret_cast<const __half*>(sh_act), (void*)y, (void*)sh_out, offsets, counts, ee, rs,
-               (const int*)nullptr, y_row_of);
+               (const int*)nullptr, y_row_of, peer_y, peer_cap, peer_rank);
     return 0;
   }
+  if (peer_y) return -1;  // results to the peers: the TMA kernels only
   const dim3 grid(pfmma::BLOCKS_PER_SM * dev.sms), block(pfmma::THREADS);
   const pfmma::SharedExpert s0{sgu_q, sgu_s, (const void*)xb, (void*)sh_act, rows_sh};
   const pfmma::SharedExpert s1{sd_q, sd_s, (const void*)sh_act, (void*)sh_out, rows_sh};
@@ -641,6 +671,30 @@ extern "C" int drb_moe_prefill_block(const uint8_t* gu_q, const __half2* gu_sm, 
   drb_launch(pfmma::k_grouped<1, 0, true>, grid, block, pfmma::SMEM_BYTES, st, false, d_q, (const void*)d_sm, (const void*)act,
              (void*)y, offsets, counts, E, s1, (const int*)nullptr, 1, y_row_of);
   return 0;
+}
+
+extern "C" int drb_moe_prefill_block(const uint8_t* gu_q, const __half2* gu_sm, const uint8_t* d_q, const __half2* d_sm,
+                                     const int8_t* sgu_q, const __half* sgu_s, const int8_t* sd_q, const __half* sd_s,
+                                     const __nv_bfloat16* xb, const int* row_of, const int* offsets, const int* counts,
+                                     __nv_bfloat16* act, float* y, __nv_bfloat16* sh_act, float* sh_out, int rows_sh, int E,
+                                     int H, int I, int x_f16, const int* y_row_of, cudaStream_t st) {
+  return prefill_block_impl(gu_q, gu_sm, d_q, d_sm, sgu_q, sgu_s, sd_q, sd_s, xb, row_of, offsets, counts, act, y, sh_act, sh_out, rows_sh, E,
+                            H, I, x_f16, y_row_of, nullptr, 0, 0, st);
+}
+// drb_moe_prefill_block on an expert-parallel rank, with the routed results stored straight into the home ranks'
+// buffers: y_row_of[slot] = s * cap + j names the token's source rank s and its slot j in this rank's receive
+// order; its result row goes to peer_y[s] (device array of every rank's result buffer [world * cap, h] f32) at row
+// rank * cap + j, over NVLink, from the down GEMM's epilogue. Follow with drb_ep_signal; the home rank's
+// drb_ep_wait then covers the results. fp16 rows and e <= 256 only (-1 otherwise). y is not written.
+extern "C" int drb_moe_prefill_block_peers(const uint8_t* gu_q, const __half2* gu_sm, const uint8_t* d_q, const __half2* d_sm,
+                                           const int8_t* sgu_q, const __half* sgu_s, const int8_t* sd_q, const __half* sd_s,
+                                           const __nv_bfloat16* xb, const int* row_of, const int* offsets, const int* counts,
+                                           __nv_bfloat16* act, float* y, __nv_bfloat16* sh_act, float* sh_out, int rows_sh, int E,
+                                           int H, int I, const int* y_row_of, float* const* peer_y, int cap, int rank,
+                                           cudaStream_t st) {
+  if (!peer_y || !y_row_of || cap <= 0 || rank < 0) return -1;
+  return prefill_block_impl(gu_q, gu_sm, d_q, d_sm, sgu_q, sgu_s, sd_q, sd_s, xb, row_of, offsets, counts, act, y, sh_act, sh_out, rows_sh, E,
+                            H, I, 1, y_row_of, peer_y, cap, rank, st);
 }
 
 // dr_moe_prefill over block-FP8 experts (include/dramakernels.h). Reference: kernels/drama.cu:971-1109; src/ffi.rs:52-55.

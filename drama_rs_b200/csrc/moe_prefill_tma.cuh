@@ -129,12 +129,16 @@ DRB_DEV uint4 dequant8_nat(uint32_t w, __half2 s2, __half2 m2) {
 //   normalised rows, a routed token's row is row_of[slot] (or slot), the shared expert's token n is row n;  down:
 //   the two act arrays, row slot / row n.
 //   dst / sh_dst: gate/up: act fp16 [., I], row slot / row n;  down: f32 [., H], row dst_row_of[slot] (or slot) / row n.
+//   peer_y (down, routed results only; or NULL): device array of every rank's result buffer. dst_row_of[slot] = s * cap + j
+//   then names the token's source rank s and its slot j there, and the row is stored straight into rank s's buffer
+//   at row rank * cap + j over NVLink: the GEMM's epilogue is the second half of the expert-parallel exchange.
 template <int GEMM>
 __global__ void __launch_bounds__(THREADS, 2)
     k_grouped_tma(const __grid_constant__ CUtensorMap tm_q, const __half2* __restrict__ SM, const __grid_constant__ CUtensorMap tm_sh,
                   const __half* __restrict__ shs, const __half* __restrict__ src, const __half* __restrict__ sh_src,
                   void* __restrict__ dst, void* __restrict__ sh_dst, const int* __restrict__ offsets, const int* __restrict__ counts, int E, int rows_sh,
-                  const int* __restrict__ row_of, const int* __restrict__ dst_row_of) {
+                  const int* __restrict__ row_of, const int* __restrict__ dst_row_of, float* const* __restrict__ peer_y, int peer_cap,
+                  int peer_rank) {
   constexpr int K = GEMM == 0 ? H : I;
   constexpr int R = GEMM == 0 ? 2 * I : H;
   constexpr int MT = R / TILE_M;  // tiles per expert: 8 / 16
@@ -377,6 +381,14 @@ __global__ void __launch_bounds__(THREADS, 2)
             const float other = __shfl_xor_sync(0xffffffffu, mine, 1);  // even lane: gate, odd lane: up
             if ((lane & 1) == 0 && c0 + i < nt) act[(size_t)drow[c0 + i] * I + j] = f2h_sat(silu_f(mine) * other);
           }
+        } else if (GEMM == 1 && peer_y && !pit.shared) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (c0 + i < nt) {
+              const int q = drow[c0 + i], s = q / peer_cap;
+              peer_y[s][((size_t)peer_rank * peer_cap + (q - s * peer_cap)) * H + pit.mt * TILE_M + r] = __uint_as_float(v[i]);
+            }
+          __threadfence_system();  // before the flag that a later kernel writes to the peers
         } else {
           float* y = static_cast<float*>(pit.shared ? sh_dst : dst);
 #pragma unroll

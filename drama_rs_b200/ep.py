@@ -21,9 +21,11 @@ prefill-side MoE block (src/engine.rs:544-604) that the benchmark configurations
     the shared expert and the residual (dr_moe_combine), so the result does not depend on N;
   * the replicated shared expert runs on a second stream beside the dispatch exchange.
 
-The exchange is, on GPUs, this library's own: every rank stores its blocks straight into the peers' receive
-buffers over NVLink (symmetric memory, drb_ep_put) and signals with a step counter (drb_ep_signal / drb_ep_wait,
-bounded); `EpGpu(p2p=False)`, and the CPU tests over gloo, use the library collective instead. Received rows
+The exchange is, on GPUs, this library's own and fused with the kernels on either side of it: the pack kernels
+store rows and ids straight into the owners' receive buffers over NVLink (symmetric memory), the down GEMM's
+epilogue stores every result row straight into its home rank's buffer, and a step counter announces each
+(drb_ep_signal / drb_ep_wait, bounded); `EpGpu(p2p=False)`, and the CPU tests over gloo, use the library
+collective instead. Received rows
 land in this rank's own memory before any kernel reads them: nothing here loads from a peer's memory.
 
 `ops` supplies the per-rank compute (the C-ABI kernels on a GPU; the tests plug in the oracle on CPU), so
@@ -156,7 +158,8 @@ class EpGpu:
         if self.p2p:
             try:
                 self._symmetric_buffers(world, n, h, dev, group)
-                self.exchange_kind = "peer stores over NVLink into symmetric memory + step flags (drb_ep_put / signal / wait)"
+                self.exchange_kind = ("peer stores over NVLink into symmetric memory, issued by the pack kernels and by the down GEMM's "
+                                      "epilogue, + step flags (drb_ep_signal / drb_ep_wait)")
             except Exception as exc:  # noqa: BLE001 - no symmetric memory on this system: the collective does the exchange
                 self.p2p = False
                 self.exchange_kind += f" (symmetric memory unavailable: {type(exc).__name__})"
@@ -203,8 +206,7 @@ class EpGpu:
         from .gpu import launched
 
         l, st = self.l, self.st.raw
-        block_bytes = inp[0].numel() * inp.element_size() if which == 0 else (inp.shape[0] // self.world) * inp.shape[1] * inp.element_size()
-        launched(l.drb_ep_put(self._p(inp), self._p(self.peer_bufs[which]), self.world, self.rank, block_bytes, st), "ep_put", debug=False)
+        # the data is already in the peers' memory: the pack kernels and the down GEMM's epilogue store it there
         launched(l.drb_ep_signal(self._p(self.peer_flags[which]), self.world, self.rank, self.C.c_void_p(self.steps.data_ptr() + 8 * which), st),
                  "ep_signal", debug=False)
         launched(l.drb_ep_wait(self.C.c_void_p(self.flags.data_ptr() + 256 * which), self.world, self.C.c_void_p(self.steps.data_ptr() + 8 * which + 4),
@@ -273,6 +275,11 @@ class EpGpu:
         assert cap == self.cap
         n, h = rows16.shape
         pairs = n * self.topk
+        if self.p2p:
+            launched(self.l.drb_ep_pack_peers(self._p(rows16), self._p(idx), n, self.topk, self.per, self.world, cap, h * 2,
+                                              self._p(self.peer_bufs[0]), self.rank, self._p(self.slot_of), self._p(self.dst_row),
+                                              self._p(self.overflow_word), self.st.raw), "ep_pack_peers", debug=False)
+            return self.send, self.slot_of[:pairs]
         launched(self.l.drb_ep_pack(self._p(rows16), self._p(idx), n, self.topk, self.per, self.world, cap, h * 2, self._p(self.send),
                                     self._p(self.slot_of), self._p(self.dst_row), self._p(self.overflow_word), self.st.raw), "ep_pack", debug=False)
         return self.send, self.slot_of[:pairs]
@@ -289,6 +296,12 @@ class EpGpu:
         sgq, sgs = ly.shared_gate_up.rows(0)
         sdq, sds = ly.shared_down.rows(0)
         # rows_sh = 0: only the routed experts run here (the shared expert is on the side stream); its pointers stay valid
+        if self.p2p:
+            launched(l.drb_moe_prefill_block_peers(gq, gs, dq, ds, sgq, sgs, sdq, sds, self._p(recv), self._p(self.row_of), self._p(self.offsets),
+                                                   self._p(self.counts), self._p(self.ap), self._p(self.y_send), self._p(self.sh_act2),
+                                                   self._p(self.shared2), 0, per, h, ly.inter, self._p(self.pair_of), self._p(self.peer_bufs[1]),
+                                                   self.cap, self.rank, st), "moe_prefill_block_peers", debug=False)
+            return self.y_send
         launched(l.drb_moe_prefill_block(gq, gs, dq, ds, sgq, sgs, sdq, sds, self._p(recv), self._p(self.row_of), self._p(self.offsets),
                                          self._p(self.counts), self._p(self.ap), self._p(self.y_send), self._p(self.sh_act2),
                                          self._p(self.shared2), 0, per, h, ly.inter, 1, self._p(self.pair_of), st), "moe_prefill_block", debug=False)

@@ -67,6 +67,8 @@ SIGNATURES: dict[str, tuple] = {
     "drb_ep_pack": (I32, [P, P, I32, I32, I32, I32, I32, I32, P, P, P, P, P]),
     "drb_ep_group": (I32, [P, I32, I32, I32, I32, P, P, P, P, P, P]),
     "drb_ep_put": (I32, [P, P, I32, I32, SZ, P]),
+    "drb_ep_pack_peers": (I32, [P, P, I32, I32, I32, I32, I32, I32, P, I32, P, P, P, P]),
+    "drb_moe_prefill_block_peers": (I32, [P] * 16 + [I32, I32, I32, I32, P, P, I32, I32, P]),
     "drb_ep_signal": (I32, [P, I32, I32, P, P]),
     "drb_ep_wait": (I32, [P, I32, P, U32, P]),
     "drb_rmsnorm_f16": (I32, [P, P, P, I32, I32, F32, P]),

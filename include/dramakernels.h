@@ -236,6 +236,19 @@ int drb_ep_group(const void* recv, int world, int cap, int row_bytes, int per, i
  * exchange into a peer's buffer only after that peer's reply to the current one (the combine step's wait).
  * block_bytes % 16 == 0, world <= 64, else -1. */
 int drb_ep_put(const void* send, void* const* peer_recv, int world, int rank, size_t block_bytes, dr_stream st);
+/* drb_ep_pack with the blocks stored straight into the owners' receive buffers (this rank's block in peer o's buffer is
+ * block `rank`; no local send buffer, no drb_ep_put), and drb_moe_prefill_block (fp16 rows, e <= 256) with the routed
+ * results stored straight into the home ranks' result buffers from the down GEMM's epilogue: y_row_of[slot] = s * cap + j
+ * names the token's source rank s and its slot j in this rank's receive order (drb_ep_group's pair_of); the row goes to
+ * peer_y[s] ([world * cap, h] f32 on rank s) at row rank * cap + j. y must be a valid address and is not written.
+ * Either call is followed by drb_ep_signal on this rank and awaited with drb_ep_wait on the peers. */
+int drb_ep_pack_peers(const void* rows, const int* idx, int n_rows, int topk, int per, int world, int cap, int row_bytes,
+                      void* const* peer_recv, int rank, int* slot_of, int* dst_row, unsigned* overflow, dr_stream st);
+int drb_moe_prefill_block_peers(const uint8_t* gu_q, const dr_half* gu_sm, const uint8_t* d_q, const dr_half* d_sm,
+                                const int8_t* sgu_q, const dr_half* sgu_s, const int8_t* sd_q, const dr_half* sd_s,
+                                const dr_bf16* xb, const int* row_of, const int* offsets, const int* counts, dr_bf16* act,
+                                float* y, dr_bf16* sh_act, float* sh_out, int rows_sh, int e, int h, int i,
+                                const int* y_row_of, float* const* peer_y, int cap, int rank, dr_stream st);
 int drb_ep_signal(unsigned* const* peer_flags, int world, int rank, unsigned* step, dr_stream st);
 int drb_ep_wait(const unsigned* flags, int world, unsigned* step, unsigned poll_limit, dr_stream st);
 /* The checkpoint quantisers of the reference's converter on the GPU (tools/convert.py:33-41 `quant_q8`, 44-101
