@@ -254,6 +254,31 @@ __global__ void __launch_bounds__(64) k_ep_wait(const unsigned* __restrict__ fla
   __threadfence_system();
 }
 
+// k_ep_signal and k_ep_wait in one launch: announce this rank's stores to every peer, then wait for every peer's.
+__global__ void __launch_bounds__(64)
+    k_ep_sync(unsigned* const* __restrict__ peer_flags, const unsigned* __restrict__ flags, int world, int rank, unsigned* __restrict__ steps,
+              unsigned limit) {
+  pdl_wait();
+  __shared__ unsigned now_s, now_w;
+  if (threadIdx.x == 0) now_s = ++steps[0], now_w = ++steps[1];
+  __syncthreads();
+  __threadfence_system();
+  if ((int)threadIdx.x < world) {
+    volatile unsigned* out = peer_flags[threadIdx.x] + rank;
+    *out = now_s;
+    const volatile unsigned* f = flags + threadIdx.x;
+    unsigned it = 0;
+    while ((int)(*f - now_w) < 0) {
+      if (++it >= limit) {
+        atomicMax(&g_drb_error, (unsigned)DRB_ERR_GRID_WAIT);
+        break;
+      }
+      if (it > 64) __nanosleep(it > 4096 ? 256 : 32);
+    }
+  }
+  __threadfence_system();
+}
+
 // x[r] += sigmoid(sgate[r]) * shared[r] + sum_k w[r,k] * Y[slot_of[r,k]], k ascending (fixed order, so
 // the result does not depend on how slots were handed out).
 __global__ void __launch_bounds__(256)
@@ -616,6 +641,13 @@ extern "C" int drb_ep_put(const void* send, void* const* peer_recv, int world, i
 extern "C" int drb_ep_signal(unsigned* const* peer_flags, int world, int rank, unsigned* step, cudaStream_t st) {
   if (!peer_flags || !step || world <= 0 || world > 64 || rank < 0 || rank >= world) return -1;
   drb_launch(pf::k_ep_signal, dim3(1), dim3(64), 0, st, false, peer_flags, world, rank, step);
+  return 0;
+}
+// drb_ep_signal followed by drb_ep_wait in one launch; steps: two device words (signalled, awaited), zero at start.
+extern "C" int drb_ep_sync(unsigned* const* peer_flags, const unsigned* flags, int world, int rank, unsigned* steps, unsigned poll_limit,
+                           cudaStream_t st) {
+  if (!peer_flags || !flags || !steps || world <= 0 || world > 64 || rank < 0 || rank >= world || poll_limit == 0) return -1;
+  drb_launch(pf::k_ep_sync, dim3(1), dim3(64), 0, st, false, peer_flags, flags, world, rank, steps, poll_limit);
   return 0;
 }
 extern "C" int drb_ep_wait(const unsigned* flags, int world, unsigned* step, unsigned poll_limit, cudaStream_t st) {

@@ -24,7 +24,7 @@ prefill-side MoE block (src/engine.rs:544-604) that the benchmark configurations
 The exchange is, on GPUs, this library's own and fused with the kernels on either side of it: the pack kernels
 store rows and ids straight into the owners' receive buffers over NVLink (symmetric memory), the down GEMM's
 epilogue stores every result row straight into its home rank's buffer, and a step counter announces each
-(drb_ep_signal / drb_ep_wait, bounded); `EpGpu(p2p=False)`, and the CPU tests over gloo, use the library
+(drb_ep_sync, bounded); `EpGpu(p2p=False)`, and the CPU tests over gloo, use the library
 collective instead. Received rows
 land in this rank's own memory before any kernel reads them: nothing here loads from a peer's memory.
 
@@ -159,7 +159,7 @@ class EpGpu:
             try:
                 self._symmetric_buffers(world, n, h, dev, group)
                 self.exchange_kind = ("peer stores over NVLink into symmetric memory, issued by the pack kernels and by the down GEMM's "
-                                      "epilogue, + step flags (drb_ep_signal / drb_ep_wait)")
+                                      "epilogue, + step flags (drb_ep_sync)")
             except Exception as exc:  # noqa: BLE001 - no symmetric memory on this system: the collective does the exchange
                 self.p2p = False
                 self.exchange_kind += f" (symmetric memory unavailable: {type(exc).__name__})"
@@ -207,10 +207,8 @@ class EpGpu:
 
         l, st = self.l, self.st.raw
         # the data is already in the peers' memory: the pack kernels and the down GEMM's epilogue store it there
-        launched(l.drb_ep_signal(self._p(self.peer_flags[which]), self.world, self.rank, self.C.c_void_p(self.steps.data_ptr() + 8 * which), st),
-                 "ep_signal", debug=False)
-        launched(l.drb_ep_wait(self.C.c_void_p(self.flags.data_ptr() + 256 * which), self.world, self.C.c_void_p(self.steps.data_ptr() + 8 * which + 4),
-                               1 << 24, st), "ep_wait", debug=False)
+        launched(l.drb_ep_sync(self._p(self.peer_flags[which]), self.C.c_void_p(self.flags.data_ptr() + 256 * which), self.world, self.rank,
+                               self.C.c_void_p(self.steps.data_ptr() + 8 * which), 1 << 24, st), "ep_sync", debug=False)
         return True
 
     def _p(self, t: torch.Tensor):

@@ -71,6 +71,7 @@ SIGNATURES: dict[str, tuple] = {
     "drb_moe_prefill_block_peers": (I32, [P] * 16 + [I32, I32, I32, I32, P, P, I32, I32, P]),
     "drb_ep_signal": (I32, [P, I32, I32, P, P]),
     "drb_ep_wait": (I32, [P, I32, P, U32, P]),
+    "drb_ep_sync": (I32, [P, P, I32, I32, P, U32, P]),
     "drb_rmsnorm_f16": (I32, [P, P, P, I32, I32, F32, P]),
     "drb_router_logits_f16": (I32, [P, P, P, I32, I32, I32, F32, P]),
     "drb_router_logits": (I32, [P, P, P, I32, I32, I32, F32, P]),

@@ -251,6 +251,9 @@ int drb_moe_prefill_block_peers(const uint8_t* gu_q, const dr_half* gu_sm, const
                                 const int* y_row_of, float* const* peer_y, int cap, int rank, dr_stream st);
 int drb_ep_signal(unsigned* const* peer_flags, int world, int rank, unsigned* step, dr_stream st);
 int drb_ep_wait(const unsigned* flags, int world, unsigned* step, unsigned poll_limit, dr_stream st);
+/* drb_ep_signal followed by drb_ep_wait in one launch; steps: two device words (signalled, awaited), zero at start. */
+int drb_ep_sync(unsigned* const* peer_flags, const unsigned* flags, int world, int rank, unsigned* steps, unsigned poll_limit,
+                dr_stream st);
 /* The checkpoint quantisers of the reference's converter on the GPU (tools/convert.py:33-41 `quant_q8`, 44-101
  * `quant_q4_groups` / `quant_q4`: 24-step clipping search with a least-squares refit). w: `groups` x 64 (q4) or
  * 128 (q8) consecutive floats, i.e. a row-major weight whose last dimension is a multiple of the group; outputs in
