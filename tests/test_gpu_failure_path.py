@@ -62,3 +62,40 @@ def test_wait_hook_refuses_long_limits():
     assert lib.drb_test_wait_runs_out(0, 100, word.at(0), None, st.raw) == -1
     assert lib.drb_test_wait_runs_out(3, 100, None, None, st.raw) == -1
     assert device_error_word() == 0
+
+
+def test_exchange_entry_points_on_one_rank_and_a_wait_nobody_answers():
+    """The peer-store exchange with this rank as its own only peer: put + signal + wait, then sync, move the blocks and
+    advance the step words. Then a wait for a step nobody signals: it gives up after its poll limit, the error word
+    reads DRB_ERR_GRID_WAIT once, and the exchange works again afterwards."""
+    lib = ffi.lib()
+    st = Stream()
+    block = np.arange(4096, dtype=np.float32)
+    send = DevBuf.from_array(block, st)
+    recv = DevBuf.zeros(block.nbytes, st)
+    flags = DevBuf.zeros(256, st)
+    steps = DevBuf.zeros(16, st)  # signalled, awaited (first exchange); signalled, awaited (sync)
+    peer_recv = DevBuf.from_array(np.array([recv.ptr], dtype=np.uint64), st)
+    peer_flags = DevBuf.from_array(np.array([flags.ptr], dtype=np.uint64), st)
+    check(lib.drb_ep_put(send.at(0), peer_recv.at(0), 1, 0, block.nbytes, st.raw), "put")
+    check(lib.drb_ep_signal(peer_flags.at(0), 1, 0, steps.at(0), st.raw), "signal")
+    check(lib.drb_ep_wait(flags.at(0), 1, steps.at(4), 4000, st.raw), "wait")
+    assert np.array_equal(recv.download(np.float32, block.size, st), block)
+    assert device_error_word() == 0
+    # signal and wait in one launch: the step words move on together
+    check(lib.drb_ep_sync(peer_flags.at(0), flags.at(0), 1, 0, steps.at(0), 4000, st.raw), "sync")
+    check(lib.dr_stream_sync(st.raw), "sync completes")
+    assert steps.download(np.uint32, 2, st).tolist() == [2, 2] and flags.download(np.uint32, 1, st)[0] == 2
+    assert device_error_word() == 0
+    # nobody signals step 3: the wait runs out, reports, and leaves the context usable
+    t0 = time.perf_counter()
+    check(lib.drb_ep_wait(flags.at(0), 1, steps.at(4), 4000, st.raw), "wait that runs out")
+    check(lib.dr_stream_sync(st.raw), "the launch completes normally")
+    assert time.perf_counter() - t0 < 0.5
+    assert device_error_word() == GRID_WAIT and device_error_word() == 0
+    check(lib.drb_ep_signal(peer_flags.at(0), 1, 0, steps.at(0), st.raw), "signal")  # step 3 arrives after all
+    check(lib.drb_ep_sync(peer_flags.at(0), flags.at(0), 1, 0, steps.at(0), 4000, st.raw), "sync")  # step 4 both ways
+    check(lib.dr_stream_sync(st.raw), "sync completes")
+    assert device_error_word() == 0
+    assert lib.drb_ep_put(send.at(0), peer_recv.at(0), 1, 0, 24, st.raw) == -1  # not a multiple of 16 bytes
+    assert lib.drb_ep_sync(peer_flags.at(0), flags.at(0), 1, 1, steps.at(0), 4000, st.raw) == -1  # rank outside the world
