@@ -656,8 +656,8 @@ extern "C" int drb_ep_wait(const unsigned* flags, int world, unsigned* step, uns
   return 0;
 }
 
-// No counterpart in the reference. The routed experts AND the int8 shared expert of one prefill block in two
-// launches: dr_moe_prefill with (a) the operand rows read in place through row_of (xb holds the normalised rows in row
+// drb_moe_prefill_block and drb_moe_prefill_block_peers (no counterpart in the reference). The routed experts AND the
+// int8 shared expert of one prefill block in two launches: dr_moe_prefill with (a) the operand rows read in place through row_of (xb holds the normalised rows in row
 // order, [rows, H], bf16 or with x_f16 != 0 fp16; nothing is permuted) and (b) the shared expert as one more expert that owns every row, its
 // int8 weights dequantised into the same tensor-core tiles (sh_act: fp16 scratch [rows, I]; sh_out: f32 [rows, H]).
 // The reference runs the shared expert through cuBLAS on weights dequantised to bf16 (src/engine.rs:351-355, 560-562);
@@ -666,6 +666,8 @@ extern "C" int drb_ep_wait(const unsigned* flags, int world, unsigned* step, uns
 // Every pointer of a part that runs must be a valid device address; with E = 0 or rows_sh = 0 the arrays of the part
 // that does not run are not used, but must still be valid addresses (any buffer will do, NULL will not): the compiler
 // may issue a load ahead of the branch that decides whether its value is needed. row_of and y_row_of may be NULL.
+// fp16 rows and E <= 256 take the kernels of moe_prefill_tma.cuh (and only they can store results to peers: peer_y);
+// bf16 rows, or more experts, the kernels of moe_prefill_mma.cuh.
 static int prefill_block_impl(const uint8_t* gu_q, const __half2* gu_sm, const uint8_t* d_q, const __half2* d_sm,
                                      const int8_t* sgu_q, const __half* sgu_s, const int8_t* sd_q, const __half* sd_s,
                                      const __nv_bfloat16* xb, const int* row_of, const int* offsets, const int* counts,

@@ -3,7 +3,7 @@
 Meant for hosts that cannot allocate device memory when they call (fixed memory budget, foreign allocator,
 a capture in progress elsewhere). The test calls it through the C ABI next to dr_moe_decode on the same
 inputs, twice in a row with different activations, and expects identical results: both entry points run the
-same two kernels and differ only in where the 4608 scratch floats live. Each round ends with the call form the
+same two kernels and differ only in where the 4608 scratch floats live. Each pass ends with the call form the
 reference's engine uses, one buffer passed as x, res and y. Collected last on purpose.
 """
 
