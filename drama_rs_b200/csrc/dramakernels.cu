@@ -9,6 +9,7 @@
 #include "moe_decode_fp8.cuh"
 #include "moe_prefill_mma.cuh"
 #include "moe_prefill_tma.cuh"
+#include "moe_prefill_fp8.cuh"
 #include "moe_prefill.cuh"
 #include "stack_decode.cuh"
 #include "quant.cuh"

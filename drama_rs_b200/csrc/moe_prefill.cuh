@@ -739,6 +739,21 @@ extern "C" int dr_moe_prefill_fp8(const uint8_t* gu_w, const float* gu_s, const 
   if (E <= 0) return 0;
   const DrbDevice& dev = drb_device(st);
   if (!dev.ready) return -2;
+  // The weights reach the tensor cores as E4M3 (moe_prefill_fp8.cuh). DRB_FP8_DEQUANT=1 selects the earlier kernels,
+  // whose threads turn every weight into fp16 first (kept for comparison; same results within the parity bar).
+  static const bool dequant_route = [] {
+    const char* v = getenv("DRB_FP8_DEQUANT");
+    return v && v[0] == '1';
+  }();
+  if (!dequant_route && E <= pf8::MAX_ITEM_SETS) {
+    CUtensorMap tm_gu, tm_d;
+    if (pft::map_rows(&tm_gu, gu_w, (uint64_t)E * 2 * pf::I, pf::H) != 0) return -3;
+    if (pft::map_rows(&tm_d, d_w, (uint64_t)E * pf::H, pf::I) != 0) return -3;
+    const dim3 grid(2 * dev.sms), block(pf8::THREADS);
+    drb_launch(pf8::k_grouped_fp8<0>, grid, block, pf8::SMEM, st, false, tm_gu, gu_s, (const void*)xp, (void*)act, offsets, counts, E);
+    drb_launch(pf8::k_grouped_fp8<1>, grid, block, pf8::SMEM, st, false, tm_d, d_s, (const void*)act, (void*)y, offsets, counts, E);
+    return 0;
+  }
   const dim3 grid(pfmma::BLOCKS_PER_SM * dev.sms), block(pfmma::THREADS);
   drb_launch(pfmma::k_grouped<0, 1, false>, grid, block, pfmma::SMEM_BYTES, st, false, gu_w, (const void*)gu_s, (const void*)xp,
              (void*)act, offsets, counts, E, pfmma::SharedExpert{}, (const int*)nullptr, 0, (const int*)nullptr);

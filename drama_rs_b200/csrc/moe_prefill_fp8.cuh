@@ -1,0 +1,412 @@
+// dr_moe_prefill_fp8 on the native type: the E4M3 weight bytes go from HBM to the tensor cores untouched
+// (tiled TMA with the 128-byte swizzle writes the MMA's A operand; tcgen05.mma.kind::f8f6f4), no thread ever
+// converts a weight.
+//
+// The checkpoint's FP8 experts carry one f32 scale per 128 x 128 block (src/model.rs:99-106). A 128-row tile of this
+// kernel IS one block row, so over a 128-input chunk the scale is one scalar for the whole tile, and a scalar can
+// ride on the other operand: the token tile of chunk kb is B'[t][k] = x[t][k] * s[kb] / c_t, where c_t (one number
+// per token and tile, the row's largest magnitude times the tile's largest scale over 256) brings every entry into
+// E4M3 range; the accumulator then runs over the whole K without a drain, and the epilogue multiplies by c_t.
+// The 8-bit MMA kind takes both operands as 8-bit floats, so B' is written as three E4M3 terms (value, residual,
+// residual of the residual: about twelve significant bits, what fp16 operands carry) and each K = 32 step issues
+// three MMAs into the same accumulator; the tensor pipe has the room (it is a few per cent busy on this path).
+// A gate/up item holds two accumulators, the 128 gate rows of units [128 mt, +128) and their 128 up rows (two block
+// rows with their own scales, hence two B' tiles per chunk); SiLU(gate) * up is formed in the epilogue by the thread
+// that holds both.
+//
+// One block = four prep warps (B' tiles, epilogue), two MMA-issuing warps (gate / up accumulator; an MMA issue costs
+// the issuing thread ~170 cycles, and there are 24 per chunk), a loader warp, a table warp (one item ahead: token
+// rows, scales, c_t); two blocks per multiprocessor. Roles meet only on mbarriers; every wait is bounded.
+// Work items: (expert, group of up to 16 tokens, 128-row tile), enumerated from the device-side counts.
+// Replaces kernels/drama.cu:971-1109 of the reference (k_moe_pf_gate_up_fp8, k_moe_pf_down_fp8).
+#pragma once
+
+#include "common.cuh"
+#include "moe_prefill_mma.cuh"
+#include "moe_prefill_tma.cuh"
+
+namespace pf8 {
+
+using pfmma::f2h_sat;
+using pfmma::fence_async_smem;
+using pfmma::mma_commit;
+using pfmma::smem_desc;
+using pfmma::swz_off;
+using pfmma::tc_fence_after;
+using pfmma::tc_fence_before;
+using pfmma::tmem_alloc;
+using pfmma::tmem_dealloc;
+using pfmma::tmem_ld16;
+using pft::tma_load_2d;
+
+constexpr int H = 2048, I = 512;
+constexpr int PREP_WARPS = 4, PREPPERS = PREP_WARPS * 32;
+constexpr int MMA_WARP0 = PREP_WARPS, LOAD_WARP = PREP_WARPS + 2, TABLE_WARP = PREP_WARPS + 3;
+constexpr int THREADS = PREPPERS + 128;
+constexpr int TILE_M = 128;
+constexpr int KC = 128;                 // K chunk = one scale block = one 128-byte swizzle row of E4M3
+constexpr int NT = 16;                  // tokens per work item = accumulator columns
+constexpr int TERMS = 3;
+constexpr int A_BYTES = TILE_M * KC;    // 16 KB per accumulator and chunk
+constexpr int BT_BYTES = NT * KC;       // 2 KB: one term of one accumulator's token tile
+constexpr int MAX_ITEM_SETS = 256;
+constexpr int MAX_KB = H / KC;          // 16 scale blocks along the widest K
+constexpr int CTL_BYTES = 1024;
+constexpr int TAB_SLOT = (2 * NT + 2 * NT + 2 * MAX_KB) * 4 + 16;  // rows, result rows | c (gate, up) | scales (gate, up) | nt
+constexpr int NTAB = 2;
+constexpr int BASE_BYTES = ((MAX_ITEM_SETS + 1) * 4 + 127) / 128 * 128;
+
+constexpr int NACC = 2;                          // accumulators per item = MMA warps
+constexpr int NSA = 2;                           // A stages of 32 KB
+constexpr int NSB = 3;                           // B' stages of 12 KB
+constexpr int A_STAGE = NACC * A_BYTES;
+constexpr int B_STAGE = NACC * TERMS * BT_BYTES;
+constexpr size_t SMEM = 1024 + CTL_BYTES + (size_t)NSA * A_STAGE + NSB * B_STAGE + NTAB * TAB_SLOT + BASE_BYTES;
+constexpr int TMEM_COLS = 2 * NACC * NT;         // two items in flight
+static_assert(SMEM <= 113 * 1024, "two blocks per multiprocessor");
+
+struct Ctl {
+  uint64_t afull[4], aempty[4];     // A stage landed (TMA) / its MMAs completed (one commit per MMA warp at work)
+  uint64_t bfull[3], bempty[3];     // B' stage written (one arrival per prep warp) / its MMAs completed
+  uint64_t accfull[2], accfree[2];  // an item's accumulators complete (one commit per MMA warp) / drained (per prep warp)
+  uint64_t tabfull[NTAB], tabempty[NTAB];
+  uint32_t tmem_base;
+};
+static_assert(sizeof(Ctl) <= CTL_BYTES, "control block");
+
+// kind::f8f6f4, both operands E4M3, fp32 accumulators, K-major, M = 128, N = n.
+DRB_DEV uint32_t instr_desc_e4m3(int n) {
+  return (1u << 4) /* D = f32 */ | (0u << 7) /* A = E4M3 */ | (0u << 10) /* B = E4M3 */ | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(TILE_M >> 4) << 24);
+}
+DRB_DEV void mma_e4m3(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+      : "memory");
+}
+
+// Two floats -> two E4M3 bytes (lo in bits 0..7), round to nearest, saturating; and back, exactly.
+DRB_DEV uint32_t f2e4m3x2(float lo, float hi) {
+  unsigned short r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+DRB_DEV float2 e4m3x2_to_f2(uint32_t p) {
+  uint32_t h2;
+  asm("{.reg .b16 t; cvt.u16.u32 t, %1; cvt.rn.f16x2.e4m3x2 %0, t;}" : "=r"(h2) : "r"(p));
+  return __half22float2(*reinterpret_cast<const __half2*>(&h2));
+}
+// v0, v1 -> three packed E4M3 pairs whose sums approximate them: value, residual, residual of the residual.
+DRB_DEV void split3(float v0, float v1, uint32_t (&t)[TERMS]) {
+#pragma unroll
+  for (int j = 0; j < TERMS; ++j) {
+    t[j] = f2e4m3x2(v0, v1);
+    const float2 b = e4m3x2_to_f2(t[j]);
+    v0 -= b.x, v1 -= b.y;
+  }
+}
+
+// GEMM = 0: gate/up + SwiGLU: src = xp bf16 [slots, H] -> dst = act fp16 [slots, I];  GEMM = 1: down: src = act fp16
+// [slots, I] -> dst = y f32 [slots, H]. tm: the weights as a tensor map over [E * R rows, K bytes], boxes of 128 rows x
+// 128 bytes, 128-byte swizzle (R = 2I, K = H / R = H, K = I). S: f32 scales [E, R / 128, K / 128].
+//
+// An item runs in steps; in each step MMA warp w multiplies one 128 x 128 weight box into accumulator w:
+//   gate/up: 16 steps; warp 0 the gate rows' box of chunk `step`, warp 1 the up rows' box of the same chunk;
+//   down:     2 steps; both warps the tile's rows, warp w the chunk 2 w + step (the two accumulators are the two halves
+//             of K and the epilogue adds them: one warp alone could not issue fast enough to keep up with HBM).
+template <int GEMM>
+__global__ void __launch_bounds__(THREADS, 2)
+    k_grouped_fp8(const __grid_constant__ CUtensorMap tm, const float* __restrict__ S, const void* __restrict__ src,
+                  void* __restrict__ dst, const int* __restrict__ offsets, const int* __restrict__ counts, int E) {
+  constexpr int K = GEMM == 0 ? H : I;
+  constexpr int R = GEMM == 0 ? 2 * I : H;
+  constexpr int MT = (GEMM == 0 ? I : H) / TILE_M;  // tiles per expert: 4 (128 units: gate + up rows) / 16
+  constexpr int NKB = K / KC;                       // chunks along K: 16 / 4
+  constexpr int NSTEP = GEMM == 0 ? NKB : NKB / NACC;
+  extern __shared__ unsigned char dyn_raw[];
+  unsigned char* dyn = reinterpret_cast<unsigned char*>(((uintptr_t)dyn_raw + 1023) & ~(uintptr_t)1023);
+  Ctl& ctl = *reinterpret_cast<Ctl*>(dyn);
+  unsigned char* aring = dyn + CTL_BYTES;
+  unsigned char* bring = aring + NSA * A_STAGE;
+  unsigned char* tabs = bring + NSB * B_STAGE;
+  int* base = reinterpret_cast<int*>(tabs + NTAB * TAB_SLOT);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NSA; ++s) mbar_init(&ctl.afull[s], 1), mbar_init(&ctl.aempty[s], NACC);
+    for (int s = 0; s < NSB; ++s) mbar_init(&ctl.bfull[s], PREP_WARPS), mbar_init(&ctl.bempty[s], NACC);
+    for (int s = 0; s < 2; ++s) mbar_init(&ctl.accfull[s], NACC), mbar_init(&ctl.accfree[s], PREP_WARPS);
+    for (int s = 0; s < NTAB; ++s) mbar_init(&ctl.tabfull[s], 1), mbar_init(&ctl.tabempty[s], PREP_WARPS);
+    mbar_fence_init();
+  }
+  if (warp == MMA_WARP0) tmem_alloc(&ctl.tmem_base, TMEM_COLS);
+  // Items per expert, exclusive prefix in base[]: warp 0 scans.
+  if (warp == 0) {
+    int carry = 0;
+    for (int s0 = 0; s0 < E; s0 += 32) {
+      const int s = s0 + lane;
+      const int cnt = s < E ? __ldg(counts + s) : 0;
+      const int items = ((cnt + NT - 1) / NT) * MT;
+      int incl = items;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += u;
+      }
+      if (s < E) base[s] = carry + incl - items;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) base[E] = carry;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl.tmem_base;
+  const int total_items = base[E];
+
+  struct Item {
+    int e, mt, n0;
+  };
+  auto decode = [&](int item) {
+    int lo = 0, hi = E;  // the last expert whose range starts at or before the item
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (base[mid] <= item) lo = mid;
+      else hi = mid;
+    }
+    Item it;
+    it.e = lo;
+    const int local = item - base[lo];
+    it.mt = local % MT;
+    it.n0 = (local / MT) * NT;
+    return it;
+  };
+  // table slot: token rows [NT] | (unused) [NT] | c of accumulator 0, 1 [NT each] | scales of block row 0, 1 [MAX_KB each] | nt
+  auto tab_row = [&](unsigned n) { return reinterpret_cast<int*>(tabs + (n % NTAB) * TAB_SLOT); };
+  auto tab_c = [&](unsigned n, int w) { return reinterpret_cast<float*>(tab_row(n) + 2 * NT) + w * NT; };
+  auto tab_s = [&](unsigned n, int w) { return reinterpret_cast<float*>(tab_row(n) + 4 * NT) + w * MAX_KB; };
+  auto tab_nt = [&](unsigned n) { return tab_row(n) + 4 * NT + 2 * MAX_KB; };
+  // What accumulator w works on in a step: the block row of the scale array (= 128-row box of the expert's rows) and
+  // the chunk along K.
+  auto block_row = [&](int mt, int w) { return GEMM == 0 ? w * (I / TILE_M) + mt : mt; };
+  auto chunk_of = [&](int step, int w) { return GEMM == 0 ? step : w * NSTEP + step; };
+
+  bool dead = false;   // a wait ran out once: stop waiting (the error word is set; results are void)
+  unsigned st_no = 0;  // steps so far (every role counts alike)
+  unsigned it_no = 0;  // items so far
+
+  if (warp == LOAD_WARP) {
+    // ================= loader: lane 0 requests the step's two weight boxes =================
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+      const Item it = decode(item);
+      for (int step = 0; step < NSTEP; ++step, ++st_no) {
+        const int s = st_no % NSA;
+        if (st_no >= NSA && !dead) dead = !mbar_wait(&ctl.aempty[s], ((st_no / NSA) - 1) & 1, DRB_ERR_EMPTY_WAIT);
+        if (lane == 0) {
+          unsigned char* dstp = aring + (size_t)s * A_STAGE;
+          mbar_expect_tx(&ctl.afull[s], A_STAGE);
+#pragma unroll
+          for (int w = 0; w < NACC; ++w)
+            tma_load_2d(dstp + w * A_BYTES, &tm, chunk_of(step, w) * KC, it.e * R + block_row(it.mt, w) * TILE_M, &ctl.afull[s]);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == MMA_WARP0 || warp == MMA_WARP0 + 1) {
+    // ================= MMA warps: warp w issues accumulator w =================
+    const int w = warp - MMA_WARP0;
+    const uint32_t idesc = instr_desc_e4m3(NT);
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
+      const int a = it_no & 1;
+      if (it_no >= 2 && !dead) dead = !mbar_wait(&ctl.accfree[a], ((it_no >> 1) - 1) & 1, DRB_ERR_TMEM);
+      const uint32_t acc = tmem + (uint32_t)((a * NACC + w) * NT);
+      for (int step = 0; step < NSTEP; ++step, ++st_no) {
+        const int sa = st_no % NSA, sb = st_no % NSB;
+        if (!dead) dead = !mbar_wait(&ctl.bfull[sb], (st_no / NSB) & 1, DRB_ERR_TMEM);
+        if (!dead) dead = !mbar_wait(&ctl.afull[sa], (st_no / NSA) & 1, DRB_ERR_TMEM);
+        tc_fence_after();
+        if (lane == 0) {
+          const uint64_t ad = smem_desc(aring + (size_t)sa * A_STAGE + w * A_BYTES);
+          const unsigned char* bt = bring + (size_t)sb * B_STAGE + w * TERMS * BT_BYTES;
+#pragma unroll
+          for (int j = 0; j < TERMS; ++j) {
+            const uint64_t bd = smem_desc(bt + j * BT_BYTES);
+#pragma unroll
+            for (int k32 = 0; k32 < KC / 32; ++k32) mma_e4m3(acc, ad + 2 * k32, bd + 2 * k32, idesc, step > 0 || j > 0 || k32 > 0);
+          }
+          mma_commit(&ctl.aempty[sa]);
+          mma_commit(&ctl.bempty[sb]);
+          if (step == NSTEP - 1) mma_commit(&ctl.accfull[a]);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == TABLE_WARP) {
+    // ================= table warp: one item ahead: token rows, the tile's scales, every token's c =================
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
+      const Item it = decode(item);
+      if (it_no >= NTAB && !dead) dead = !mbar_wait(&ctl.tabempty[it_no % NTAB], ((it_no / NTAB) - 1) & 1, DRB_ERR_EMPTY_WAIT);
+      const int cnt = __ldg(counts + it.e), off = __ldg(offsets + it.e);
+      const int nt = min(NT, cnt - it.n0);
+      float smax[NACC];
+#pragma unroll
+      for (int w = 0; w < NACC; ++w) {
+        const float sv = lane < NKB ? __ldg(S + ((size_t)it.e * (R / TILE_M) + block_row(it.mt, w)) * NKB + lane) : 0.f;
+        if (lane < NKB) tab_s(it_no, w)[lane] = sv;
+        smax[w] = warp_max(fabsf(sv));
+      }
+      for (int t = 0; t < NT; ++t) {
+        const int row = off + it.n0 + (t < nt ? t : 0);
+        uint32_t m = 0u;
+        if (t < nt) {
+          // largest magnitude of the row: 16-bit floats with the sign bit cleared order like integers (bf16 and fp16 alike)
+          const uint4* p = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(src) + (size_t)row * K);
+#pragma unroll
+          for (int i = 0; i < K / 8 / 32; ++i) {
+            const uint4 v = GEMM == 0 ? __ldg(p + i * 32 + lane) : __ldcg(p + i * 32 + lane);
+            const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) m = max(m, max(wv[q] & 0x7fffu, (wv[q] >> 16) & 0x7fffu));
+          }
+          m = __reduce_max_sync(0xffffffffu, m);
+        }
+        const float rmax = GEMM == 0 ? __uint_as_float(m << 16) : __half2float(__ushort_as_half((unsigned short)m));
+        if (lane == 0) {
+          tab_row(it_no)[t] = row;
+#pragma unroll
+          for (int w = 0; w < NACC; ++w) {
+            const float c = rmax * smax[w] * (1.f / 256.f);
+            tab_c(it_no, w)[t] = (c > 1.0e-30f && c <= 3.0e38f) ? c : 1.f;
+          }
+        }
+      }
+      if (lane == 0) tab_nt(it_no)[0] = nt;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl.tabfull[it_no % NTAB]);
+    }
+  } else {
+    // ================= prep warps: the token tiles B', and the epilogue =================
+    const int pt = threadIdx.x;         // 0 .. 127
+    const int t = pt >> 3, c = pt & 7;  // token and 16-input piece of the chunk this thread prepares
+    const int r = warp * 32 + lane;     // tile row in the epilogue (warp = tensor-memory lane quarter)
+    const uint32_t b_off = swz_off(t, c);
+    // An item's epilogue: accumulators [128 tile rows (lanes), nt tokens (columns)] -> SwiGLU / store.
+    auto epilogue = [&](const Item& pit, unsigned pno) {
+      const int nt = tab_nt(pno)[0];
+      const int* rows = tab_row(pno);
+      const int a = pno & 1;
+      if (!dead) dead = !mbar_wait(&ctl.accfull[a], (pno >> 1) & 1, DRB_ERR_TMEM);
+      tc_fence_after();
+      uint32_t v0[16], v1[16];
+      tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)((a * NACC) * NT), v0);
+      tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)((a * NACC + 1) * NT), v1);
+      const float* c0 = tab_c(pno, 0);
+      const float* c1 = tab_c(pno, 1);
+#pragma unroll
+      for (int i = 0; i < NT; ++i)
+        if (i < nt) {
+          if (GEMM == 0) {
+            const float g = __uint_as_float(v0[i]) * c0[i], u = __uint_as_float(v1[i]) * c1[i];
+            static_cast<__half*>(dst)[(size_t)rows[i] * I + pit.mt * TILE_M + r] = f2h_sat(silu_f(g) * u);
+          } else {
+            static_cast<float*>(dst)[(size_t)rows[i] * H + pit.mt * TILE_M + r] = (__uint_as_float(v0[i]) + __uint_as_float(v1[i])) * c0[i];
+          }
+        }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl.accfree[a]), mbar_arrive(&ctl.tabempty[pno % NTAB]);
+    };
+    Item pend_it = {};
+    unsigned pend_no = 0;
+    bool pending = false;
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
+      const Item it = decode(item);
+      if (!dead) dead = !mbar_wait(&ctl.tabfull[it_no % NTAB], (it_no / NTAB) & 1, DRB_ERR_FULL_WAIT);
+      const int nt = tab_nt(it_no)[0];
+      const bool live = t < nt;
+      const unsigned char* rowp = static_cast<const unsigned char*>(src) + (size_t)tab_row(it_no)[t] * K * 2 + 32 * c;
+      float inv_c[NACC];
+#pragma unroll
+      for (int w = 0; w < NACC; ++w) inv_c[w] = 1.f / tab_c(it_no, GEMM == 0 ? w : 0)[t];
+      constexpr int NX = GEMM == 0 ? 1 : NACC;  // distinct chunks of the token row a step reads
+      uint4 xl[NX], xh[NX];
+      auto load_x = [&](int step) {
+#pragma unroll
+        for (int w = 0; w < NX; ++w) {
+          xl[w] = xh[w] = make_uint4(0u, 0u, 0u, 0u);
+          if (!live || step >= NSTEP) continue;
+          const uint4* p = reinterpret_cast<const uint4*>(rowp + (size_t)chunk_of(step, w) * KC * 2);
+          if (GEMM == 0) xl[w] = __ldg(p), xh[w] = __ldg(p + 1);
+          else xl[w] = __ldcg(p), xh[w] = __ldcg(p + 1);
+        }
+      };
+      load_x(0);
+      for (int step = 0; step < NSTEP; ++step, ++st_no) {
+        const int sb = st_no % NSB;
+        uint32_t xw[NX][8];
+#pragma unroll
+        for (int w = 0; w < NX; ++w) {
+          xw[w][0] = xl[w].x, xw[w][1] = xl[w].y, xw[w][2] = xl[w].z, xw[w][3] = xl[w].w;
+          xw[w][4] = xh[w].x, xw[w][5] = xh[w].y, xw[w][6] = xh[w].z, xw[w][7] = xh[w].w;
+        }
+        load_x(step + 1);
+        // the MMAs that read this stage NSB steps ago must have completed
+        if (st_no >= NSB && !dead) dead = !mbar_wait(&ctl.bempty[sb], ((st_no / NSB) - 1) & 1, DRB_ERR_TMEM);
+        unsigned char* bt = bring + (size_t)sb * B_STAGE;
+#pragma unroll
+        for (int w = 0; w < NACC; ++w) {
+          const float f = (GEMM == 0 ? tab_s(it_no, w)[step] : tab_s(it_no, 0)[chunk_of(step, w)]) * inv_c[w];
+          const uint32_t* xs = xw[GEMM == 0 ? 0 : w];
+          uint32_t o[TERMS][4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t pa[TERMS], pb[TERMS];
+            float e0, e1, e2, e3;
+            if (GEMM == 0) {  // bf16 pairs
+              e0 = __uint_as_float(xs[2 * q] << 16), e1 = __uint_as_float(xs[2 * q] & 0xffff0000u);
+              e2 = __uint_as_float(xs[2 * q + 1] << 16), e3 = __uint_as_float(xs[2 * q + 1] & 0xffff0000u);
+            } else {  // fp16 pairs
+              const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&xs[2 * q]));
+              const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&xs[2 * q + 1]));
+              e0 = fa.x, e1 = fa.y, e2 = fb.x, e3 = fb.y;
+            }
+            split3(e0 * f, e1 * f, pa);
+            split3(e2 * f, e3 * f, pb);
+#pragma unroll
+            for (int j = 0; j < TERMS; ++j) o[j][q] = pa[j] | (pb[j] << 16);
+          }
+          if (live) {
+#pragma unroll
+            for (int j = 0; j < TERMS; ++j)
+              *reinterpret_cast<uint4*>(bt + (w * TERMS + j) * BT_BYTES + b_off) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+          }
+        }
+        fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl.bfull[sb]);
+        if (step == 0 && pending) {  // the previous item's accumulators, while this item's first MMAs run
+          epilogue(pend_it, pend_no);
+          pending = false;
+        }
+      }
+      pend_it = it, pend_no = it_no, pending = true;
+    }
+    if (pending) epilogue(pend_it, pend_no);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP0) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+static cudaError_t configure_all() {
+  cudaError_t e;
+  if ((e = cudaFuncSetAttribute(k_grouped_fp8<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(k_grouped_fp8<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM)) != cudaSuccess) return e;
+  if ((e = drb_carveout(k_grouped_fp8<0>)) != cudaSuccess) return e;
+  return drb_carveout(k_grouped_fp8<1>);
+}
+
+}  // namespace pf8

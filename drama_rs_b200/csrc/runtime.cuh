@@ -30,6 +30,7 @@ namespace moe { static cudaError_t configure_all(); namespace f8 { static cudaEr
 namespace stack { static cudaError_t configure_all(); }
 namespace pfmma { static cudaError_t configure_all(); }
 namespace pft { static cudaError_t configure_all(); }
+namespace pf8 { static cudaError_t configure_all(); }
 
 namespace rt {
 
@@ -56,6 +57,7 @@ static cudaError_t setup(int d) {
   if ((e = stack::configure_all()) != cudaSuccess) return e;
   if ((e = pfmma::configure_all()) != cudaSuccess) return e;
   if ((e = pft::configure_all()) != cudaSuccess) return e;
+  if ((e = pf8::configure_all()) != cudaSuccess) return e;
   dv.ready = true;
   g_dev[d] = dv;
   g_ready[d].store(true, std::memory_order_release);
