@@ -258,28 +258,36 @@ __global__ void __launch_bounds__(THREADS, 2)
         if (lane < NKB) tab_s(it_no, w)[lane] = sv;
         smax[w] = warp_max(fabsf(sv));
       }
-      for (int t = 0; t < NT; ++t) {
-        const int row = off + it.n0 + (t < nt ? t : 0);
-        uint32_t m = 0u;
-        if (t < nt) {
-          // largest magnitude of the row: 16-bit floats with the sign bit cleared order like integers (bf16 and fp16 alike)
+      // every token row's largest magnitude, two rows per round trip (16-bit floats with the sign bit cleared order like
+      // integers, bf16 and fp16 alike)
+      constexpr int PER = K / 8 / 32;  // 16-byte pieces per lane and row
+      for (int t0 = 0; t0 < NT; t0 += 2) {
+        uint4 v[2][PER];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int row = off + it.n0 + (t0 + u < nt ? t0 + u : 0);
           const uint4* p = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(src) + (size_t)row * K);
 #pragma unroll
-          for (int i = 0; i < K / 8 / 32; ++i) {
-            const uint4 v = GEMM == 0 ? __ldg(p + i * 32 + lane) : __ldcg(p + i * 32 + lane);
-            const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+          for (int i = 0; i < PER; ++i) v[u][i] = GEMM == 0 ? __ldg(p + i * 32 + lane) : __ldcg(p + i * 32 + lane);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          uint32_t m = 0u;
+#pragma unroll
+          for (int i = 0; i < PER; ++i) {
+            const uint32_t wv[4] = {v[u][i].x, v[u][i].y, v[u][i].z, v[u][i].w};
 #pragma unroll
             for (int q = 0; q < 4; ++q) m = max(m, max(wv[q] & 0x7fffu, (wv[q] >> 16) & 0x7fffu));
           }
           m = __reduce_max_sync(0xffffffffu, m);
-        }
-        const float rmax = GEMM == 0 ? __uint_as_float(m << 16) : __half2float(__ushort_as_half((unsigned short)m));
-        if (lane == 0) {
-          tab_row(it_no)[t] = row;
+          const float rmax = GEMM == 0 ? __uint_as_float(m << 16) : __half2float(__ushort_as_half((unsigned short)m));
+          if (lane == 0) {
+            tab_row(it_no)[t0 + u] = off + it.n0 + (t0 + u < nt ? t0 + u : 0);
 #pragma unroll
-          for (int w = 0; w < NACC; ++w) {
-            const float c = rmax * smax[w] * (1.f / 256.f);
-            tab_c(it_no, w)[t] = (c > 1.0e-30f && c <= 3.0e38f) ? c : 1.f;
+            for (int w = 0; w < NACC; ++w) {
+              const float c = rmax * smax[w] * (1.f / 256.f);
+              tab_c(it_no, w)[t0 + u] = (t0 + u < nt && c > 1.0e-30f && c <= 3.0e38f) ? c : 1.f;
+            }
           }
         }
       }
@@ -401,11 +409,299 @@ __global__ void __launch_bounds__(THREADS, 2)
   if (warp == MMA_WARP0) tmem_dealloc(tmem, TMEM_COLS);
 }
 
+// ---- the down projection ------------------------------------------------------------------------------------------
+// K is only four chunks here and a tile is 64 KB, so a work item of one tile would spend more on its token tile, its
+// table entry and its hand-overs than on its weights. Instead the chunk's scale stays out of the token operand:
+// B'[t][k] = act[t][k] / c_t serves EVERY tile of the expert, each chunk of a tile gets an accumulator of its own (four
+// per tile, 16 columns each), and the epilogue forms c_t * sum_kb s[tile][kb] * acc_kb. A work item is (expert, group of
+// up to 16 tokens, four consecutive tiles): B' is prepared once per item (24 KB, two items' worth resident), the table
+// warp reads each token row once per item, and the weights stream through a ring of 16 KB boxes, one per chunk, which
+// the two MMA warps take in turns.
+namespace down {
+
+constexpr int NKB = I / KC;                 // 4 chunks = 4 accumulators per tile
+constexpr int TPI = 4;                      // tiles per item
+constexpr int QPE = H / TILE_M / TPI;       // items per expert and token group: 4
+constexpr int NSA = 3;                      // weight boxes in flight
+constexpr int BI_BYTES = NKB * TERMS * BT_BYTES;  // one item's token operand: 24 KB
+constexpr int TAB_SLOT = (NT + NT + TPI * NKB) * 4 + 16;  // token rows | c | scales [tile][chunk] | nt
+constexpr size_t SMEM = 1024 + CTL_BYTES + (size_t)NSA * A_BYTES + 2 * BI_BYTES + NTAB * TAB_SLOT + BASE_BYTES;
+constexpr int TMEM_COLS = 2 * NKB * NT;     // two tiles in flight: 128 columns
+static_assert(SMEM <= 113 * 1024, "two blocks per multiprocessor");
+
+struct Ctl {
+  uint64_t afull[NSA], aempty[NSA];    // a weight box landed / the MMAs that read it completed
+  uint64_t bfull[2][NKB], bempty[2];   // a chunk of an item's token operand written (per prep warp) / the item's MMAs completed (per MMA warp)
+  uint64_t accfull[2], accfree[2];     // a tile's four accumulators complete (per MMA warp) / drained (per prep warp)
+  uint64_t tabfull[NTAB], tabempty[NTAB];
+  uint32_t tmem_base;
+};
+static_assert(sizeof(Ctl) <= CTL_BYTES, "control block");
+
+// tm: d_w as a tensor map over [E * H rows, I bytes]. S: f32 [E, H / 128, I / 128]. src: act fp16 [slots, I]. dst: y f32 [slots, H].
+__global__ void __launch_bounds__(THREADS, 2)
+    k_down_fp8(const __grid_constant__ CUtensorMap tm, const float* __restrict__ S, const __half* __restrict__ src,
+               float* __restrict__ dst, const int* __restrict__ offsets, const int* __restrict__ counts, int E) {
+  extern __shared__ unsigned char dyn_raw[];
+  unsigned char* dyn = reinterpret_cast<unsigned char*>(((uintptr_t)dyn_raw + 1023) & ~(uintptr_t)1023);
+  Ctl& ctl = *reinterpret_cast<Ctl*>(dyn);
+  unsigned char* aring = dyn + CTL_BYTES;
+  unsigned char* bbuf = aring + NSA * A_BYTES;
+  unsigned char* tabs = bbuf + 2 * BI_BYTES;
+  int* base = reinterpret_cast<int*>(tabs + NTAB * TAB_SLOT);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NSA; ++s) mbar_init(&ctl.afull[s], 1), mbar_init(&ctl.aempty[s], 1);
+    for (int s = 0; s < 2; ++s) {
+      for (int kb = 0; kb < NKB; ++kb) mbar_init(&ctl.bfull[s][kb], PREP_WARPS);
+      mbar_init(&ctl.bempty[s], NACC);
+      mbar_init(&ctl.accfull[s], NACC), mbar_init(&ctl.accfree[s], PREP_WARPS);
+    }
+    for (int s = 0; s < NTAB; ++s) mbar_init(&ctl.tabfull[s], 1), mbar_init(&ctl.tabempty[s], PREP_WARPS);
+    mbar_fence_init();
+  }
+  if (warp == MMA_WARP0) tmem_alloc(&ctl.tmem_base, TMEM_COLS);
+  if (warp == 0) {  // items per expert, exclusive prefix in base[]
+    int carry = 0;
+    for (int s0 = 0; s0 < E; s0 += 32) {
+      const int s = s0 + lane;
+      const int cnt = s < E ? __ldg(counts + s) : 0;
+      const int items = ((cnt + NT - 1) / NT) * QPE;
+      int incl = items;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += u;
+      }
+      if (s < E) base[s] = carry + incl - items;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) base[E] = carry;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl.tmem_base;
+  const int total_items = base[E];
+
+  struct Item {
+    int e, q, n0;
+  };
+  auto decode = [&](int item) {
+    int lo = 0, hi = E;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (base[mid] <= item) lo = mid;
+      else hi = mid;
+    }
+    Item it;
+    it.e = lo;
+    const int local = item - base[lo];
+    it.q = local % QPE;
+    it.n0 = (local / QPE) * NT;
+    return it;
+  };
+  auto tab_row = [&](unsigned n) { return reinterpret_cast<int*>(tabs + (n % NTAB) * TAB_SLOT); };
+  auto tab_c = [&](unsigned n) { return reinterpret_cast<float*>(tab_row(n) + NT); };
+  auto tab_s = [&](unsigned n) { return reinterpret_cast<float*>(tab_row(n) + 2 * NT); };
+  auto tab_nt = [&](unsigned n) { return tab_row(n) + 2 * NT + TPI * NKB; };
+
+  bool dead = false;
+  unsigned it_no = 0;  // items so far
+  unsigned ch_no = 0;  // weight boxes so far (loader and MMA warps count alike)
+
+  if (warp == LOAD_WARP) {
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+      const Item it = decode(item);
+      for (int i = 0; i < TPI; ++i)
+        for (int kb = 0; kb < NKB; ++kb, ++ch_no) {
+          const int s = ch_no % NSA;
+          if (ch_no >= NSA && !dead) dead = !mbar_wait(&ctl.aempty[s], ((ch_no / NSA) - 1) & 1, DRB_ERR_EMPTY_WAIT);
+          if (lane == 0) {
+            mbar_expect_tx(&ctl.afull[s], A_BYTES);
+            tma_load_2d(aring + (size_t)s * A_BYTES, &tm, kb * KC, it.e * H + (it.q * TPI + i) * TILE_M, &ctl.afull[s]);
+          }
+          __syncwarp();
+        }
+    }
+  } else if (warp == MMA_WARP0 || warp == MMA_WARP0 + 1) {
+    // ================= MMA warps: chunk kb of every tile is warp (kb & 1)'s =================
+    const int w = warp - MMA_WARP0;
+    const uint32_t idesc = instr_desc_e4m3(NT);
+    unsigned tl_no = 0;  // tiles so far
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
+      const int ip = it_no & 1;
+      for (int i = 0; i < TPI; ++i, ++tl_no) {
+        const int tp = tl_no & 1;
+        if (tl_no >= 2 && !dead) dead = !mbar_wait(&ctl.accfree[tp], ((tl_no >> 1) - 1) & 1, DRB_ERR_TMEM);
+        for (int kb = 0; kb < NKB; ++kb, ++ch_no) {
+          if ((kb & 1) != w) continue;
+          const int sa = ch_no % NSA;
+          if (i == 0 && !dead) dead = !mbar_wait(&ctl.bfull[ip][kb], (it_no >> 1) & 1, DRB_ERR_TMEM);
+          if (!dead) dead = !mbar_wait(&ctl.afull[sa], (ch_no / NSA) & 1, DRB_ERR_TMEM);
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t acc = tmem + (uint32_t)((tp * NKB + kb) * NT);
+            const uint64_t ad = smem_desc(aring + (size_t)sa * A_BYTES);
+            const unsigned char* bt = bbuf + (size_t)ip * BI_BYTES + kb * TERMS * BT_BYTES;
+#pragma unroll
+            for (int j = 0; j < TERMS; ++j) {
+              const uint64_t bd = smem_desc(bt + j * BT_BYTES);
+#pragma unroll
+              for (int k32 = 0; k32 < KC / 32; ++k32) mma_e4m3(acc, ad + 2 * k32, bd + 2 * k32, idesc, j > 0 || k32 > 0);
+            }
+            mma_commit(&ctl.aempty[sa]);
+            if (kb >= NKB - 2) {
+              mma_commit(&ctl.accfull[tp]);
+              if (i == TPI - 1) mma_commit(&ctl.bempty[ip]);
+            }
+          }
+          __syncwarp();
+        }
+      }
+    }
+  } else if (warp == TABLE_WARP) {
+    // ================= table warp: one item ahead =================
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
+      const Item it = decode(item);
+      if (it_no >= NTAB && !dead) dead = !mbar_wait(&ctl.tabempty[it_no % NTAB], ((it_no / NTAB) - 1) & 1, DRB_ERR_EMPTY_WAIT);
+      const int cnt = __ldg(counts + it.e), off = __ldg(offsets + it.e);
+      const int nt = min(NT, cnt - it.n0);
+      if (lane < TPI * NKB) tab_s(it_no)[lane] = __ldg(S + ((size_t)it.e * (H / TILE_M) + it.q * TPI) * NKB + lane);
+      // every token row's largest magnitude, four rows per round trip (fp16 with the sign cleared orders like an integer)
+      for (int t0 = 0; t0 < NT; t0 += 4) {
+        uint4 v[4][2];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int row = off + it.n0 + (t0 + u < nt ? t0 + u : 0);
+          const uint4* p = reinterpret_cast<const uint4*>(src + (size_t)row * I);
+          v[u][0] = __ldcg(p + lane), v[u][1] = __ldcg(p + 32 + lane);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint32_t wv[8] = {v[u][0].x, v[u][0].y, v[u][0].z, v[u][0].w, v[u][1].x, v[u][1].y, v[u][1].z, v[u][1].w};
+          uint32_t m = 0u;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) m = max(m, max(wv[q] & 0x7fffu, (wv[q] >> 16) & 0x7fffu));
+          m = __reduce_max_sync(0xffffffffu, m);
+          if (lane == 0) {
+            const float c = __half2float(__ushort_as_half((unsigned short)m)) * (1.f / 256.f);
+            tab_row(it_no)[t0 + u] = off + it.n0 + (t0 + u < nt ? t0 + u : 0);
+            tab_c(it_no)[t0 + u] = (t0 + u < nt && c > 1.0e-30f && c <= 3.0e38f) ? c : 1.f;
+          }
+        }
+      }
+      if (lane == 0) tab_nt(it_no)[0] = nt;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl.tabfull[it_no % NTAB]);
+    }
+  } else {
+    // ================= prep warps: the item's token operand, and every tile's epilogue =================
+    const int pt = threadIdx.x;
+    const int t = pt >> 3, c = pt & 7;
+    const int r = warp * 32 + lane;
+    const uint32_t b_off = swz_off(t, c);
+    struct Tile {
+      int mt;
+      unsigned it_no, tl_no;
+      bool last;
+    };
+    auto epilogue = [&](const Tile& tl) {
+      const int nt = tab_nt(tl.it_no)[0];
+      const int* rows = tab_row(tl.it_no);
+      const float* cs = tab_c(tl.it_no);
+      const float* sc = tab_s(tl.it_no) + (tl.mt % TPI) * NKB;
+      const int tp = tl.tl_no & 1;
+      if (!dead) dead = !mbar_wait(&ctl.accfull[tp], (tl.tl_no >> 1) & 1, DRB_ERR_TMEM);
+      tc_fence_after();
+      float sum[NT];
+#pragma unroll
+      for (int kb = 0; kb < NKB; ++kb) {
+        uint32_t v[16];
+        tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)((tp * NKB + kb) * NT), v);
+        const float s = sc[kb];
+#pragma unroll
+        for (int i = 0; i < NT; ++i) sum[i] = kb == 0 ? s * __uint_as_float(v[i]) : fmaf(s, __uint_as_float(v[i]), sum[i]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl.accfree[tp]);
+#pragma unroll
+      for (int i = 0; i < NT; ++i)
+        if (i < nt) dst[(size_t)rows[i] * H + tl.mt * TILE_M + r] = sum[i] * cs[i];
+      if (tl.last) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl.tabempty[tl.it_no % NTAB]);
+      }
+    };
+    Tile pend[2];
+    int npend = 0;
+    unsigned tl_no = 0;
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
+      const Item it = decode(item);
+      const int ip = it_no & 1;
+      if (!dead) dead = !mbar_wait(&ctl.tabfull[it_no % NTAB], (it_no / NTAB) & 1, DRB_ERR_FULL_WAIT);
+      // the MMAs of the item before last read this buffer
+      if (it_no >= 2 && !dead) dead = !mbar_wait(&ctl.bempty[ip], ((it_no >> 1) - 1) & 1, DRB_ERR_TMEM);
+      const int nt = tab_nt(it_no)[0];
+      const bool live = t < nt;
+      const float inv_c = 1.f / tab_c(it_no)[t];
+      const uint4* rowp = reinterpret_cast<const uint4*>(src + (size_t)tab_row(it_no)[t] * I + 16 * c);
+      uint4 xl[NKB], xh[NKB];
+#pragma unroll
+      for (int kb = 0; kb < NKB; ++kb) {
+        xl[kb] = xh[kb] = make_uint4(0u, 0u, 0u, 0u);
+        if (live) xl[kb] = __ldcg(rowp + kb * (KC / 8)), xh[kb] = __ldcg(rowp + kb * (KC / 8) + 1);
+      }
+#pragma unroll
+      for (int kb = 0; kb < NKB; ++kb) {
+        const uint32_t xs[8] = {xl[kb].x, xl[kb].y, xl[kb].z, xl[kb].w, xh[kb].x, xh[kb].y, xh[kb].z, xh[kb].w};
+        uint32_t o[TERMS][4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint32_t pa[TERMS], pb[TERMS];
+          const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&xs[2 * q]));
+          const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&xs[2 * q + 1]));
+          split3(fa.x * inv_c, fa.y * inv_c, pa);
+          split3(fb.x * inv_c, fb.y * inv_c, pb);
+#pragma unroll
+          for (int j = 0; j < TERMS; ++j) o[j][q] = pa[j] | (pb[j] << 16);
+        }
+        if (live) {
+          unsigned char* bt = bbuf + (size_t)ip * BI_BYTES + kb * TERMS * BT_BYTES;
+#pragma unroll
+          for (int j = 0; j < TERMS; ++j) *reinterpret_cast<uint4*>(bt + j * BT_BYTES + b_off) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl.bfull[ip][kb]);
+      }
+      // epilogues: the two tiles left over from the item before, then this item's first two
+      for (int i = 0; i < npend; ++i) epilogue(pend[i]);
+      for (int i = 0; i < TPI - 2; ++i, ++tl_no) epilogue(Tile{it.q * TPI + i, it_no, tl_no, false});
+      for (int i = TPI - 2; i < TPI; ++i, ++tl_no) pend[i - (TPI - 2)] = Tile{it.q * TPI + i, it_no, tl_no, i == TPI - 1};
+      npend = 2;
+      // the rows of pend[] are looked up in this item's table slot, which the table warp rewrites only after the
+      // last tile's epilogue has released it
+    }
+    for (int i = 0; i < npend; ++i) epilogue(pend[i]);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP0) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+}  // namespace down
+
 static cudaError_t configure_all() {
   cudaError_t e;
   if ((e = cudaFuncSetAttribute(k_grouped_fp8<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM)) != cudaSuccess) return e;
   if ((e = cudaFuncSetAttribute(k_grouped_fp8<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(down::k_down_fp8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)down::SMEM)) != cudaSuccess) return e;
   if ((e = drb_carveout(k_grouped_fp8<0>)) != cudaSuccess) return e;
+  if ((e = drb_carveout(down::k_down_fp8)) != cudaSuccess) return e;
   return drb_carveout(k_grouped_fp8<1>);
 }
 
