@@ -750,13 +750,10 @@ extern "C" int dr_moe_prefill_fp8(const uint8_t* gu_w, const float* gu_s, const 
     if (pft::map_rows(&tm_gu, gu_w, (uint64_t)E * 2 * pf::I, pf::H) != 0) return -3;
     if (pft::map_rows(&tm_d, d_w, (uint64_t)E * pf::H, pf::I) != 0) return -3;
     const dim3 grid(2 * dev.sms), block(pf8::THREADS);
-    drb_launch(pf8::k_grouped_fp8<0>, grid, block, pf8::SMEM, st, false, tm_gu, gu_s, (const void*)xp, (void*)act, offsets, counts, E);
-    static const bool per_tile_down = [] {
-      const char* v = getenv("DRB_FP8_DOWN_PER_TILE");
-      return v && v[0] == '1';
-    }();
-    if (per_tile_down) drb_launch(pf8::k_grouped_fp8<1>, grid, block, pf8::SMEM, st, false, tm_d, d_s, (const void*)act, (void*)y, offsets, counts, E);
-    else drb_launch(pf8::down::k_down_fp8, grid, block, pf8::down::SMEM, st, false, tm_d, d_s, (const __half*)act, y, offsets, counts, E);
+    // y is written last (by the down kernel); until then its first floats hold every token row's largest magnitude
+    pf8::k_rowmax_bf16<<<2 * dev.sms, 256, 0, st>>>(xp, offsets, counts, E, y);
+    drb_launch(pf8::k_gate_up_fp8, grid, block, pf8::SMEM, st, false, tm_gu, gu_s, xp, (const float*)y, (__half*)act, offsets, counts, E);
+    drb_launch(pf8::down::k_down_fp8, grid, block, pf8::down::SMEM, st, false, tm_d, d_s, (const __half*)act, y, offsets, counts, E);
     return 0;
   }
   const dim3 grid(pfmma::BLOCKS_PER_SM * dev.sms), block(pfmma::THREADS);

@@ -14,9 +14,9 @@
 // rows with their own scales, hence two B' tiles per chunk); SiLU(gate) * up is formed in the epilogue by the thread
 // that holds both.
 //
-// One block = four prep warps (B' tiles, epilogue), two MMA-issuing warps (gate / up accumulator; an MMA issue costs
-// the issuing thread ~170 cycles, and there are 24 per chunk), a loader warp, a table warp (one item ahead: token
-// rows, scales, c_t); two blocks per multiprocessor. Roles meet only on mbarriers; every wait is bounded.
+// One block = four prep warps (B' tiles, epilogue), one MMA-issuing warp, a loader warp, a table warp (one item ahead:
+// token rows, scales, c_t); two blocks per multiprocessor. Roles meet only on mbarriers; every wait is bounded, and no
+// role leaves before the completion arrivals it is owed have landed.
 // Work items: (expert, group of up to 16 tokens, 128-row tile), enumerated from the device-side counts.
 // Replaces kernels/drama.cu:971-1109 of the reference (k_moe_pf_gate_up_fp8, k_moe_pf_down_fp8).
 #pragma once
@@ -41,8 +41,8 @@ using pft::tma_load_2d;
 
 constexpr int H = 2048, I = 512;
 constexpr int PREP_WARPS = 4, PREPPERS = PREP_WARPS * 32;
-constexpr int MMA_WARP0 = PREP_WARPS, LOAD_WARP = PREP_WARPS + 2, TABLE_WARP = PREP_WARPS + 3;
-constexpr int THREADS = PREPPERS + 128;
+constexpr int MMA_WARP = PREP_WARPS, LOAD_WARP = PREP_WARPS + 1, TABLE_WARP = PREP_WARPS + 2;
+constexpr int THREADS = PREPPERS + 96;
 constexpr int TILE_M = 128;
 constexpr int KC = 128;                 // K chunk = one scale block = one 128-byte swizzle row of E4M3
 constexpr int NT = 16;                  // tokens per work item = accumulator columns
@@ -56,7 +56,7 @@ constexpr int TAB_SLOT = (2 * NT + 2 * NT + 2 * MAX_KB) * 4 + 16;  // rows, resu
 constexpr int NTAB = 2;
 constexpr int BASE_BYTES = ((MAX_ITEM_SETS + 1) * 4 + 127) / 128 * 128;
 
-constexpr int NACC = 2;                          // accumulators per item = MMA warps
+constexpr int NACC = 2;                          // accumulators per item
 constexpr int NSA = 2;                           // A stages of 32 KB
 constexpr int NSB = 3;                           // B' stages of 12 KB
 constexpr int A_STAGE = NACC * A_BYTES;
@@ -108,23 +108,63 @@ DRB_DEV void split3(float v0, float v1, uint32_t (&t)[TERMS]) {
   }
 }
 
-// GEMM = 0: gate/up + SwiGLU: src = xp bf16 [slots, H] -> dst = act fp16 [slots, I];  GEMM = 1: down: src = act fp16
-// [slots, I] -> dst = y f32 [slots, H]. tm: the weights as a tensor map over [E * R rows, K bytes], boxes of 128 rows x
-// 128 bytes, 128-byte swizzle (R = 2I, K = H / R = H, K = I). S: f32 scales [E, R / 128, K / 128].
-//
-// An item runs in steps; in each step MMA warp w multiplies one 128 x 128 weight box into accumulator w:
-//   gate/up: 16 steps; warp 0 the gate rows' box of chunk `step`, warp 1 the up rows' box of the same chunk;
-//   down:     2 steps; both warps the tile's rows, warp w the chunk 2 w + step (the two accumulators are the two halves
-//             of K and the epilogue adds them: one warp alone could not issue fast enough to keep up with HBM).
-template <int GEMM>
+// A wait on the step-to-step path: polls without sleeping between polls (a sleeping waiter adds its wake-up time to every
+// hand-over of the ring), bounded all the same.
+DRB_DEV bool wait_hot(uint64_t* bar, unsigned parity, unsigned err_code) {
+  for (unsigned it = 0; it < (1u << 24); ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  atomicMax(&g_drb_error, err_code);
+  return false;
+}
+
+// ---- every token row's largest magnitude ------------------------------------------------------------------------
+// One warp per row of xp (bf16 [slots, H]); out[slot] = max |x|. The rows in use end at max_e (offsets[e] + counts[e]).
+// Runs ahead of the gate/up kernel, which would otherwise recompute it in every one of a token group's four tiles.
+__global__ void __launch_bounds__(256) k_rowmax_bf16(const __nv_bfloat16* __restrict__ xp, const int* __restrict__ offsets,
+                                                     const int* __restrict__ counts, int E, float* __restrict__ out) {
+  __shared__ int s_total;
+  pdl_wait();
+  if (threadIdx.x == 0) s_total = 0;
+  __syncthreads();
+  int end = 0;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int c = __ldg(counts + e);
+    if (c > 0) end = max(end, __ldg(offsets + e) + c);
+  }
+  end = __reduce_max_sync(0xffffffffu, end);
+  if ((threadIdx.x & 31) == 0) atomicMax(&s_total, end);
+  __syncthreads();
+  const int total = s_total, lane = threadIdx.x & 31;
+  constexpr int PER = H / 8 / 32;
+  for (int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < total; row += gridDim.x * (blockDim.x >> 5)) {
+    const uint4* p = reinterpret_cast<const uint4*>(xp + (size_t)row * H);
+    uint4 v[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) v[i] = __ldg(p + i * 32 + lane);
+    uint32_t m = 0u;  // bf16 with the sign bit cleared orders like an integer
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const uint32_t wv[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) m = max(m, max(wv[q] & 0x7fffu, (wv[q] >> 16) & 0x7fffu));
+    }
+    m = __reduce_max_sync(0xffffffffu, m);
+    if (lane == 0) out[row] = __uint_as_float(m << 16);
+  }
+}
+
+// ---- gate/up + SwiGLU -----------------------------------------------------------------------------------------------
+// src = xp bf16 [slots, H] -> dst = act fp16 [slots, I]. tm: gu_w as a tensor map over [E * 2I rows, H bytes], boxes of
+// 128 rows x 128 bytes, 128-byte swizzle. S: f32 scales [E, 2I / 128, H / 128]. rmax: k_rowmax_bf16's result.
+// An item is (expert, group of up to 16 tokens, 128 units) and runs in 16 steps, one per chunk of K; a step multiplies
+// the chunk's box of the units' gate rows into accumulator 0 and the box of their up rows into accumulator 1.
 __global__ void __launch_bounds__(THREADS, 2)
-    k_grouped_fp8(const __grid_constant__ CUtensorMap tm, const float* __restrict__ S, const void* __restrict__ src,
-                  void* __restrict__ dst, const int* __restrict__ offsets, const int* __restrict__ counts, int E) {
-  constexpr int K = GEMM == 0 ? H : I;
-  constexpr int R = GEMM == 0 ? 2 * I : H;
-  constexpr int MT = (GEMM == 0 ? I : H) / TILE_M;  // tiles per expert: 4 (128 units: gate + up rows) / 16
-  constexpr int NKB = K / KC;                       // chunks along K: 16 / 4
-  constexpr int NSTEP = GEMM == 0 ? NKB : NKB / NACC;
+    k_gate_up_fp8(const __grid_constant__ CUtensorMap tm, const float* __restrict__ S, const __nv_bfloat16* __restrict__ src,
+                  const float* __restrict__ rmax, __half* __restrict__ dst, const int* __restrict__ offsets,
+                  const int* __restrict__ counts, int E) {
+  constexpr int K = H, R = 2 * I;
+  constexpr int MT = I / TILE_M;  // tiles per expert: 4
+  constexpr int NSTEP = K / KC;   // 16
   extern __shared__ unsigned char dyn_raw[];
   unsigned char* dyn = reinterpret_cast<unsigned char*>(((uintptr_t)dyn_raw + 1023) & ~(uintptr_t)1023);
   Ctl& ctl = *reinterpret_cast<Ctl*>(dyn);
@@ -136,15 +176,14 @@ __global__ void __launch_bounds__(THREADS, 2)
 
   pdl_wait();
   if (threadIdx.x == 0) {
-    for (int s = 0; s < NSA; ++s) mbar_init(&ctl.afull[s], 1), mbar_init(&ctl.aempty[s], NACC);
-    for (int s = 0; s < NSB; ++s) mbar_init(&ctl.bfull[s], PREP_WARPS), mbar_init(&ctl.bempty[s], NACC);
-    for (int s = 0; s < 2; ++s) mbar_init(&ctl.accfull[s], NACC), mbar_init(&ctl.accfree[s], PREP_WARPS);
+    for (int s = 0; s < NSA; ++s) mbar_init(&ctl.afull[s], 1), mbar_init(&ctl.aempty[s], 1);
+    for (int s = 0; s < NSB; ++s) mbar_init(&ctl.bfull[s], PREP_WARPS), mbar_init(&ctl.bempty[s], 1);
+    for (int s = 0; s < 2; ++s) mbar_init(&ctl.accfull[s], 1), mbar_init(&ctl.accfree[s], PREP_WARPS);
     for (int s = 0; s < NTAB; ++s) mbar_init(&ctl.tabfull[s], 1), mbar_init(&ctl.tabempty[s], PREP_WARPS);
     mbar_fence_init();
   }
-  if (warp == MMA_WARP0) tmem_alloc(&ctl.tmem_base, TMEM_COLS);
-  // Items per expert, exclusive prefix in base[]: warp 0 scans.
-  if (warp == 0) {
+  if (warp == MMA_WARP) tmem_alloc(&ctl.tmem_base, TMEM_COLS);
+  if (warp == 0) {  // items per expert, exclusive prefix in base[]
     int carry = 0;
     for (int s0 = 0; s0 < E; s0 += 32) {
       const int s = s0 + lane;
@@ -189,10 +228,8 @@ __global__ void __launch_bounds__(THREADS, 2)
   auto tab_c = [&](unsigned n, int w) { return reinterpret_cast<float*>(tab_row(n) + 2 * NT) + w * NT; };
   auto tab_s = [&](unsigned n, int w) { return reinterpret_cast<float*>(tab_row(n) + 4 * NT) + w * MAX_KB; };
   auto tab_nt = [&](unsigned n) { return tab_row(n) + 4 * NT + 2 * MAX_KB; };
-  // What accumulator w works on in a step: the block row of the scale array (= 128-row box of the expert's rows) and
-  // the chunk along K.
-  auto block_row = [&](int mt, int w) { return GEMM == 0 ? w * (I / TILE_M) + mt : mt; };
-  auto chunk_of = [&](int step, int w) { return GEMM == 0 ? step : w * NSTEP + step; };
+  // the 128-row box of the expert's rows (= block row of the scale array) behind accumulator w of tile mt
+  auto block_row = [&](int mt, int w) { return w * (I / TILE_M) + mt; };
 
   bool dead = false;   // a wait ran out once: stop waiting (the error word is set; results are void)
   unsigned st_no = 0;  // steps so far (every role counts alike)
@@ -204,38 +241,46 @@ __global__ void __launch_bounds__(THREADS, 2)
       const Item it = decode(item);
       for (int step = 0; step < NSTEP; ++step, ++st_no) {
         const int s = st_no % NSA;
-        if (st_no >= NSA && !dead) dead = !mbar_wait(&ctl.aempty[s], ((st_no / NSA) - 1) & 1, DRB_ERR_EMPTY_WAIT);
+        if (st_no >= NSA && !dead) dead = !wait_hot(&ctl.aempty[s], ((st_no / NSA) - 1) & 1, DRB_ERR_EMPTY_WAIT);
         if (lane == 0) {
           unsigned char* dstp = aring + (size_t)s * A_STAGE;
           mbar_expect_tx(&ctl.afull[s], A_STAGE);
 #pragma unroll
           for (int w = 0; w < NACC; ++w)
-            tma_load_2d(dstp + w * A_BYTES, &tm, chunk_of(step, w) * KC, it.e * R + block_row(it.mt, w) * TILE_M, &ctl.afull[s]);
+            tma_load_2d(dstp + w * A_BYTES, &tm, step * KC, it.e * R + block_row(it.mt, w) * TILE_M, &ctl.afull[s]);
         }
         __syncwarp();
       }
     }
-  } else if (warp == MMA_WARP0 || warp == MMA_WARP0 + 1) {
-    // ================= MMA warps: warp w issues accumulator w =================
-    const int w = warp - MMA_WARP0;
+    // Tail: the MMA warp's completion arrivals for the last stages are in flight until they land; the block must not
+    // end (and hand its shared memory to a successor) before they have.
+    for (unsigned k = st_no > NSA ? st_no - NSA : 0; k < st_no; ++k)
+      if (!dead) dead = !mbar_wait(&ctl.aempty[k % NSA], (k / NSA) & 1, DRB_ERR_EMPTY_WAIT);
+  } else if (warp == MMA_WARP) {
+    // ================= MMA warp: lane 0 issues both accumulators' MMAs =================
+    // One issuing thread per block, as in every tcgen05 kernel this library has run for long: a variant with one issuing
+    // warp per accumulator raised rare launch failures (about one in 150 back-to-back calls) that reading did not explain.
     const uint32_t idesc = instr_desc_e4m3(NT);
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
       const int a = it_no & 1;
-      if (it_no >= 2 && !dead) dead = !mbar_wait(&ctl.accfree[a], ((it_no >> 1) - 1) & 1, DRB_ERR_TMEM);
-      const uint32_t acc = tmem + (uint32_t)((a * NACC + w) * NT);
+      if (it_no >= 2 && !dead) dead = !wait_hot(&ctl.accfree[a], ((it_no >> 1) - 1) & 1, DRB_ERR_TMEM);
       for (int step = 0; step < NSTEP; ++step, ++st_no) {
         const int sa = st_no % NSA, sb = st_no % NSB;
-        if (!dead) dead = !mbar_wait(&ctl.bfull[sb], (st_no / NSB) & 1, DRB_ERR_TMEM);
-        if (!dead) dead = !mbar_wait(&ctl.afull[sa], (st_no / NSA) & 1, DRB_ERR_TMEM);
+        if (!dead) dead = !wait_hot(&ctl.bfull[sb], (st_no / NSB) & 1, DRB_ERR_TMEM);
+        if (!dead) dead = !wait_hot(&ctl.afull[sa], (st_no / NSA) & 1, DRB_ERR_TMEM);
         tc_fence_after();
         if (lane == 0) {
-          const uint64_t ad = smem_desc(aring + (size_t)sa * A_STAGE + w * A_BYTES);
-          const unsigned char* bt = bring + (size_t)sb * B_STAGE + w * TERMS * BT_BYTES;
 #pragma unroll
-          for (int j = 0; j < TERMS; ++j) {
-            const uint64_t bd = smem_desc(bt + j * BT_BYTES);
+          for (int w = 0; w < NACC; ++w) {
+            const uint32_t acc = tmem + (uint32_t)((a * NACC + w) * NT);
+            const uint64_t ad = smem_desc(aring + (size_t)sa * A_STAGE + w * A_BYTES);
+            const unsigned char* bt = bring + (size_t)sb * B_STAGE + w * TERMS * BT_BYTES;
 #pragma unroll
-            for (int k32 = 0; k32 < KC / 32; ++k32) mma_e4m3(acc, ad + 2 * k32, bd + 2 * k32, idesc, step > 0 || j > 0 || k32 > 0);
+            for (int j = 0; j < TERMS; ++j) {
+              const uint64_t bd = smem_desc(bt + j * BT_BYTES);
+#pragma unroll
+              for (int k32 = 0; k32 < KC / 32; ++k32) mma_e4m3(acc, ad + 2 * k32, bd + 2 * k32, idesc, step > 0 || j > 0 || k32 > 0);
+            }
           }
           mma_commit(&ctl.aempty[sa]);
           mma_commit(&ctl.bempty[sb]);
@@ -245,52 +290,22 @@ __global__ void __launch_bounds__(THREADS, 2)
       }
     }
   } else if (warp == TABLE_WARP) {
-    // ================= table warp: one item ahead: token rows, the tile's scales, every token's c =================
+    // ================= table warp: one item ahead: token rows, the two block rows' scales, every token's c =================
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
       const Item it = decode(item);
       if (it_no >= NTAB && !dead) dead = !mbar_wait(&ctl.tabempty[it_no % NTAB], ((it_no / NTAB) - 1) & 1, DRB_ERR_EMPTY_WAIT);
       const int cnt = __ldg(counts + it.e), off = __ldg(offsets + it.e);
       const int nt = min(NT, cnt - it.n0);
-      float smax[NACC];
+      const int row = off + it.n0 + (lane < nt ? lane : 0);
+      const float rm = lane < nt ? __ldg(rmax + row) : 0.f;
 #pragma unroll
       for (int w = 0; w < NACC; ++w) {
-        const float sv = lane < NKB ? __ldg(S + ((size_t)it.e * (R / TILE_M) + block_row(it.mt, w)) * NKB + lane) : 0.f;
-        if (lane < NKB) tab_s(it_no, w)[lane] = sv;
-        smax[w] = warp_max(fabsf(sv));
+        const float sv = lane < NSTEP ? __ldg(S + ((size_t)it.e * (R / TILE_M) + block_row(it.mt, w)) * NSTEP + lane) : 0.f;
+        if (lane < NSTEP) tab_s(it_no, w)[lane] = sv;
+        const float c = rm * warp_max(fabsf(sv)) * (1.f / 256.f);
+        if (lane < NT) tab_c(it_no, w)[lane] = (c > 1.0e-30f && c <= 3.0e38f) ? c : 1.f;
       }
-      // every token row's largest magnitude, two rows per round trip (16-bit floats with the sign bit cleared order like
-      // integers, bf16 and fp16 alike)
-      constexpr int PER = K / 8 / 32;  // 16-byte pieces per lane and row
-      for (int t0 = 0; t0 < NT; t0 += 2) {
-        uint4 v[2][PER];
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int row = off + it.n0 + (t0 + u < nt ? t0 + u : 0);
-          const uint4* p = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(src) + (size_t)row * K);
-#pragma unroll
-          for (int i = 0; i < PER; ++i) v[u][i] = GEMM == 0 ? __ldg(p + i * 32 + lane) : __ldcg(p + i * 32 + lane);
-        }
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          uint32_t m = 0u;
-#pragma unroll
-          for (int i = 0; i < PER; ++i) {
-            const uint32_t wv[4] = {v[u][i].x, v[u][i].y, v[u][i].z, v[u][i].w};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) m = max(m, max(wv[q] & 0x7fffu, (wv[q] >> 16) & 0x7fffu));
-          }
-          m = __reduce_max_sync(0xffffffffu, m);
-          const float rmax = GEMM == 0 ? __uint_as_float(m << 16) : __half2float(__ushort_as_half((unsigned short)m));
-          if (lane == 0) {
-            tab_row(it_no)[t0 + u] = off + it.n0 + (t0 + u < nt ? t0 + u : 0);
-#pragma unroll
-            for (int w = 0; w < NACC; ++w) {
-              const float c = rmax * smax[w] * (1.f / 256.f);
-              tab_c(it_no, w)[t0 + u] = (t0 + u < nt && c > 1.0e-30f && c <= 3.0e38f) ? c : 1.f;
-            }
-          }
-        }
-      }
+      if (lane < NT) tab_row(it_no)[lane] = row;
       if (lane == 0) tab_nt(it_no)[0] = nt;
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl.tabfull[it_no % NTAB]);
@@ -301,31 +316,29 @@ __global__ void __launch_bounds__(THREADS, 2)
     const int t = pt >> 3, c = pt & 7;  // token and 16-input piece of the chunk this thread prepares
     const int r = warp * 32 + lane;     // tile row in the epilogue (warp = tensor-memory lane quarter)
     const uint32_t b_off = swz_off(t, c);
-    // An item's epilogue: accumulators [128 tile rows (lanes), nt tokens (columns)] -> SwiGLU / store.
+    // An item's epilogue: accumulators [128 units (lanes), nt tokens (columns)] -> SiLU(gate) * up -> act.
     auto epilogue = [&](const Item& pit, unsigned pno) {
       const int nt = tab_nt(pno)[0];
       const int* rows = tab_row(pno);
       const int a = pno & 1;
-      if (!dead) dead = !mbar_wait(&ctl.accfull[a], (pno >> 1) & 1, DRB_ERR_TMEM);
+      if (!dead) dead = !wait_hot(&ctl.accfull[a], (pno >> 1) & 1, DRB_ERR_TMEM);
       tc_fence_after();
       uint32_t v0[16], v1[16];
       tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)((a * NACC) * NT), v0);
       tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)((a * NACC + 1) * NT), v1);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl.accfree[a]);
       const float* c0 = tab_c(pno, 0);
       const float* c1 = tab_c(pno, 1);
 #pragma unroll
       for (int i = 0; i < NT; ++i)
         if (i < nt) {
-          if (GEMM == 0) {
-            const float g = __uint_as_float(v0[i]) * c0[i], u = __uint_as_float(v1[i]) * c1[i];
-            static_cast<__half*>(dst)[(size_t)rows[i] * I + pit.mt * TILE_M + r] = f2h_sat(silu_f(g) * u);
-          } else {
-            static_cast<float*>(dst)[(size_t)rows[i] * H + pit.mt * TILE_M + r] = (__uint_as_float(v0[i]) + __uint_as_float(v1[i])) * c0[i];
-          }
+          const float g = __uint_as_float(v0[i]) * c0[i], u = __uint_as_float(v1[i]) * c1[i];
+          dst[(size_t)rows[i] * I + pit.mt * TILE_M + r] = f2h_sat(silu_f(g) * u);
         }
-      tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl.accfree[a]), mbar_arrive(&ctl.tabempty[pno % NTAB]);
+      if (lane == 0) mbar_arrive(&ctl.tabempty[pno % NTAB]);
     };
     Item pend_it = {};
     unsigned pend_no = 0;
@@ -335,54 +348,28 @@ __global__ void __launch_bounds__(THREADS, 2)
       if (!dead) dead = !mbar_wait(&ctl.tabfull[it_no % NTAB], (it_no / NTAB) & 1, DRB_ERR_FULL_WAIT);
       const int nt = tab_nt(it_no)[0];
       const bool live = t < nt;
-      const unsigned char* rowp = static_cast<const unsigned char*>(src) + (size_t)tab_row(it_no)[t] * K * 2 + 32 * c;
+      const uint4* rowp = reinterpret_cast<const uint4*>(src + (size_t)tab_row(it_no)[t] * K + 16 * c);
       float inv_c[NACC];
 #pragma unroll
-      for (int w = 0; w < NACC; ++w) inv_c[w] = 1.f / tab_c(it_no, GEMM == 0 ? w : 0)[t];
-      constexpr int NX = GEMM == 0 ? 1 : NACC;  // distinct chunks of the token row a step reads
-      uint4 xl[NX], xh[NX];
-      auto load_x = [&](int step) {
-#pragma unroll
-        for (int w = 0; w < NX; ++w) {
-          xl[w] = xh[w] = make_uint4(0u, 0u, 0u, 0u);
-          if (!live || step >= NSTEP) continue;
-          const uint4* p = reinterpret_cast<const uint4*>(rowp + (size_t)chunk_of(step, w) * KC * 2);
-          if (GEMM == 0) xl[w] = __ldg(p), xh[w] = __ldg(p + 1);
-          else xl[w] = __ldcg(p), xh[w] = __ldcg(p + 1);
-        }
-      };
-      load_x(0);
+      for (int w = 0; w < NACC; ++w) inv_c[w] = 1.f / tab_c(it_no, w)[t];
+      uint4 xl = make_uint4(0u, 0u, 0u, 0u), xh = xl;
+      if (live) xl = __ldg(rowp), xh = __ldg(rowp + 1);
       for (int step = 0; step < NSTEP; ++step, ++st_no) {
         const int sb = st_no % NSB;
-        uint32_t xw[NX][8];
-#pragma unroll
-        for (int w = 0; w < NX; ++w) {
-          xw[w][0] = xl[w].x, xw[w][1] = xl[w].y, xw[w][2] = xl[w].z, xw[w][3] = xl[w].w;
-          xw[w][4] = xh[w].x, xw[w][5] = xh[w].y, xw[w][6] = xh[w].z, xw[w][7] = xh[w].w;
-        }
-        load_x(step + 1);
+        const uint32_t xs[8] = {xl.x, xl.y, xl.z, xl.w, xh.x, xh.y, xh.z, xh.w};
+        if (live && step + 1 < NSTEP) xl = __ldg(rowp + (step + 1) * (KC / 8)), xh = __ldg(rowp + (step + 1) * (KC / 8) + 1);
         // the MMAs that read this stage NSB steps ago must have completed
-        if (st_no >= NSB && !dead) dead = !mbar_wait(&ctl.bempty[sb], ((st_no / NSB) - 1) & 1, DRB_ERR_TMEM);
+        if (st_no >= NSB && !dead) dead = !wait_hot(&ctl.bempty[sb], ((st_no / NSB) - 1) & 1, DRB_ERR_TMEM);
         unsigned char* bt = bring + (size_t)sb * B_STAGE;
 #pragma unroll
         for (int w = 0; w < NACC; ++w) {
-          const float f = (GEMM == 0 ? tab_s(it_no, w)[step] : tab_s(it_no, 0)[chunk_of(step, w)]) * inv_c[w];
-          const uint32_t* xs = xw[GEMM == 0 ? 0 : w];
+          const float f = tab_s(it_no, w)[step] * inv_c[w];
           uint32_t o[TERMS][4];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint32_t pa[TERMS], pb[TERMS];
-            float e0, e1, e2, e3;
-            if (GEMM == 0) {  // bf16 pairs
-              e0 = __uint_as_float(xs[2 * q] << 16), e1 = __uint_as_float(xs[2 * q] & 0xffff0000u);
-              e2 = __uint_as_float(xs[2 * q + 1] << 16), e3 = __uint_as_float(xs[2 * q + 1] & 0xffff0000u);
-            } else {  // fp16 pairs
-              const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&xs[2 * q]));
-              const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&xs[2 * q + 1]));
-              e0 = fa.x, e1 = fa.y, e2 = fb.x, e3 = fb.y;
-            }
-            split3(e0 * f, e1 * f, pa);
-            split3(e2 * f, e3 * f, pb);
+            split3(__uint_as_float(xs[2 * q] << 16) * f, __uint_as_float(xs[2 * q] & 0xffff0000u) * f, pa);
+            split3(__uint_as_float(xs[2 * q + 1] << 16) * f, __uint_as_float(xs[2 * q + 1] & 0xffff0000u) * f, pb);
 #pragma unroll
             for (int j = 0; j < TERMS; ++j) o[j][q] = pa[j] | (pb[j] << 16);
           }
@@ -403,10 +390,12 @@ __global__ void __launch_bounds__(THREADS, 2)
       pend_it = it, pend_no = it_no, pending = true;
     }
     if (pending) epilogue(pend_it, pend_no);
+    for (unsigned k = st_no > NSB ? st_no - NSB : 0; k < st_no; ++k)  // tail: see the loader's
+      if (!dead) dead = !mbar_wait(&ctl.bempty[k % NSB], (k / NSB) & 1, DRB_ERR_TMEM);
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == MMA_WARP0) tmem_dealloc(tmem, TMEM_COLS);
+  if (warp == MMA_WARP) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 // ---- the down projection ------------------------------------------------------------------------------------------
@@ -415,8 +404,7 @@ __global__ void __launch_bounds__(THREADS, 2)
 // B'[t][k] = act[t][k] / c_t serves EVERY tile of the expert, each chunk of a tile gets an accumulator of its own (four
 // per tile, 16 columns each), and the epilogue forms c_t * sum_kb s[tile][kb] * acc_kb. A work item is (expert, group of
 // up to 16 tokens, four consecutive tiles): B' is prepared once per item (24 KB, two items' worth resident), the table
-// warp reads each token row once per item, and the weights stream through a ring of 16 KB boxes, one per chunk, which
-// the two MMA warps take in turns.
+// warp reads each token row once per item, and the weights stream through a ring of 16 KB boxes, one per chunk.
 namespace down {
 
 constexpr int NKB = I / KC;                 // 4 chunks = 4 accumulators per tile
@@ -456,13 +444,13 @@ __global__ void __launch_bounds__(THREADS, 2)
     for (int s = 0; s < NSA; ++s) mbar_init(&ctl.afull[s], 1), mbar_init(&ctl.aempty[s], 1);
     for (int s = 0; s < 2; ++s) {
       for (int kb = 0; kb < NKB; ++kb) mbar_init(&ctl.bfull[s][kb], PREP_WARPS);
-      mbar_init(&ctl.bempty[s], NACC);
-      mbar_init(&ctl.accfull[s], NACC), mbar_init(&ctl.accfree[s], PREP_WARPS);
+      mbar_init(&ctl.bempty[s], 1);
+      mbar_init(&ctl.accfull[s], 1), mbar_init(&ctl.accfree[s], PREP_WARPS);
     }
     for (int s = 0; s < NTAB; ++s) mbar_init(&ctl.tabfull[s], 1), mbar_init(&ctl.tabempty[s], PREP_WARPS);
     mbar_fence_init();
   }
-  if (warp == MMA_WARP0) tmem_alloc(&ctl.tmem_base, TMEM_COLS);
+  if (warp == MMA_WARP) tmem_alloc(&ctl.tmem_base, TMEM_COLS);
   if (warp == 0) {  // items per expert, exclusive prefix in base[]
     int carry = 0;
     for (int s0 = 0; s0 < E; s0 += 32) {
@@ -510,7 +498,7 @@ __global__ void __launch_bounds__(THREADS, 2)
 
   bool dead = false;
   unsigned it_no = 0;  // items so far
-  unsigned ch_no = 0;  // weight boxes so far (loader and MMA warps count alike)
+  unsigned ch_no = 0;  // weight boxes so far (loader and MMA warp count alike)
 
   if (warp == LOAD_WARP) {
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
@@ -518,7 +506,7 @@ __global__ void __launch_bounds__(THREADS, 2)
       for (int i = 0; i < TPI; ++i)
         for (int kb = 0; kb < NKB; ++kb, ++ch_no) {
           const int s = ch_no % NSA;
-          if (ch_no >= NSA && !dead) dead = !mbar_wait(&ctl.aempty[s], ((ch_no / NSA) - 1) & 1, DRB_ERR_EMPTY_WAIT);
+          if (ch_no >= NSA && !dead) dead = !wait_hot(&ctl.aempty[s], ((ch_no / NSA) - 1) & 1, DRB_ERR_EMPTY_WAIT);
           if (lane == 0) {
             mbar_expect_tx(&ctl.afull[s], A_BYTES);
             tma_load_2d(aring + (size_t)s * A_BYTES, &tm, kb * KC, it.e * H + (it.q * TPI + i) * TILE_M, &ctl.afull[s]);
@@ -526,21 +514,22 @@ __global__ void __launch_bounds__(THREADS, 2)
           __syncwarp();
         }
     }
-  } else if (warp == MMA_WARP0 || warp == MMA_WARP0 + 1) {
-    // ================= MMA warps: chunk kb of every tile is warp (kb & 1)'s =================
-    const int w = warp - MMA_WARP0;
+    // Tail: the block must not end before the completion arrivals for its last boxes have landed.
+    for (unsigned k = ch_no > NSA ? ch_no - NSA : 0; k < ch_no; ++k)
+      if (!dead) dead = !mbar_wait(&ctl.aempty[k % NSA], (k / NSA) & 1, DRB_ERR_EMPTY_WAIT);
+  } else if (warp == MMA_WARP) {
+    // ================= MMA warp: lane 0 issues; chunk kb of a tile goes into accumulator kb =================
     const uint32_t idesc = instr_desc_e4m3(NT);
     unsigned tl_no = 0;  // tiles so far
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
       const int ip = it_no & 1;
       for (int i = 0; i < TPI; ++i, ++tl_no) {
         const int tp = tl_no & 1;
-        if (tl_no >= 2 && !dead) dead = !mbar_wait(&ctl.accfree[tp], ((tl_no >> 1) - 1) & 1, DRB_ERR_TMEM);
+        if (tl_no >= 2 && !dead) dead = !wait_hot(&ctl.accfree[tp], ((tl_no >> 1) - 1) & 1, DRB_ERR_TMEM);
         for (int kb = 0; kb < NKB; ++kb, ++ch_no) {
-          if ((kb & 1) != w) continue;
           const int sa = ch_no % NSA;
-          if (i == 0 && !dead) dead = !mbar_wait(&ctl.bfull[ip][kb], (it_no >> 1) & 1, DRB_ERR_TMEM);
-          if (!dead) dead = !mbar_wait(&ctl.afull[sa], (ch_no / NSA) & 1, DRB_ERR_TMEM);
+          if (i == 0 && !dead) dead = !wait_hot(&ctl.bfull[ip][kb], (it_no >> 1) & 1, DRB_ERR_TMEM);
+          if (!dead) dead = !wait_hot(&ctl.afull[sa], (ch_no / NSA) & 1, DRB_ERR_TMEM);
           tc_fence_after();
           if (lane == 0) {
             const uint32_t acc = tmem + (uint32_t)((tp * NKB + kb) * NT);
@@ -553,9 +542,9 @@ __global__ void __launch_bounds__(THREADS, 2)
               for (int k32 = 0; k32 < KC / 32; ++k32) mma_e4m3(acc, ad + 2 * k32, bd + 2 * k32, idesc, j > 0 || k32 > 0);
             }
             mma_commit(&ctl.aempty[sa]);
-            if (kb >= NKB - 2) {
-              mma_commit(&ctl.accfull[tp]);
+            if (kb == NKB - 1) {
               if (i == TPI - 1) mma_commit(&ctl.bempty[ip]);
+              mma_commit(&ctl.accfull[tp]);
             }
           }
           __syncwarp();
@@ -614,7 +603,7 @@ __global__ void __launch_bounds__(THREADS, 2)
       const float* cs = tab_c(tl.it_no);
       const float* sc = tab_s(tl.it_no) + (tl.mt % TPI) * NKB;
       const int tp = tl.tl_no & 1;
-      if (!dead) dead = !mbar_wait(&ctl.accfull[tp], (tl.tl_no >> 1) & 1, DRB_ERR_TMEM);
+      if (!dead) dead = !wait_hot(&ctl.accfull[tp], (tl.tl_no >> 1) & 1, DRB_ERR_TMEM);
       tc_fence_after();
       float sum[NT];
 #pragma unroll
@@ -687,22 +676,22 @@ __global__ void __launch_bounds__(THREADS, 2)
       // last tile's epilogue has released it
     }
     for (int i = 0; i < npend; ++i) epilogue(pend[i]);
+    for (unsigned n = it_no > 2 ? it_no - 2 : 0; n < it_no; ++n)  // tail: see the loader's
+      if (!dead) dead = !mbar_wait(&ctl.bempty[n & 1], (n >> 1) & 1, DRB_ERR_TMEM);
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == MMA_WARP0) tmem_dealloc(tmem, TMEM_COLS);
+  if (warp == MMA_WARP) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 }  // namespace down
 
 static cudaError_t configure_all() {
   cudaError_t e;
-  if ((e = cudaFuncSetAttribute(k_grouped_fp8<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM)) != cudaSuccess) return e;
-  if ((e = cudaFuncSetAttribute(k_grouped_fp8<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(k_gate_up_fp8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM)) != cudaSuccess) return e;
   if ((e = cudaFuncSetAttribute(down::k_down_fp8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)down::SMEM)) != cudaSuccess) return e;
-  if ((e = drb_carveout(k_grouped_fp8<0>)) != cudaSuccess) return e;
-  if ((e = drb_carveout(down::k_down_fp8)) != cudaSuccess) return e;
-  return drb_carveout(k_grouped_fp8<1>);
+  if ((e = drb_carveout(k_gate_up_fp8)) != cudaSuccess) return e;
+  return drb_carveout(down::k_down_fp8);
 }
 
 }  // namespace pf8
