@@ -8,8 +8,10 @@
 // per token and tile, the row's largest magnitude times the tile's largest scale over 256) brings every entry into
 // E4M3 range; the accumulator then runs over the whole K without a drain, and the epilogue multiplies by c_t.
 // The 8-bit MMA kind takes both operands as 8-bit floats, so B' is written as three E4M3 terms (value, residual,
-// residual of the residual: about twelve significant bits, what fp16 operands carry) and each K = 32 step issues
-// three MMAs into the same accumulator; the tensor pipe has the room (it is a few per cent busy on this path).
+// residual of the residual: about twelve significant bits, what fp16 operands carry). The three terms of a token are
+// three ROWS of the token operand (rows t, 16 + t, 32 + t of a 48-row tile), so one MMA of N = 48 multiplies all three
+// and the epilogue adds the three column groups: a third of the MMA issues (an issue costs its thread ~150 cycles, and
+// one thread per block issues), for 48 accumulator columns instead of 16.
 // A gate/up item holds two accumulators, the 128 gate rows of units [128 mt, +128) and their 128 up rows (two block
 // rows with their own scales, hence two B' tiles per chunk); SiLU(gate) * up is formed in the epilogue by the thread
 // that holds both.
@@ -62,7 +64,9 @@ constexpr int NSB = 3;                           // B' stages of 12 KB
 constexpr int A_STAGE = NACC * A_BYTES;
 constexpr int B_STAGE = NACC * TERMS * BT_BYTES;
 constexpr size_t SMEM = 1024 + CTL_BYTES + (size_t)NSA * A_STAGE + NSB * B_STAGE + NTAB * TAB_SLOT + BASE_BYTES;
-constexpr int TMEM_COLS = 2 * NACC * NT;         // two items in flight
+constexpr int NCOL = TERMS * NT;                 // accumulator columns: one group of NT per term
+constexpr int TMEM_COLS = 256;                   // two items in flight x two accumulators x 48 columns = 192, rounded up
+static_assert(2 * NACC * NCOL <= TMEM_COLS, "tensor memory");
 static_assert(SMEM <= 113 * 1024, "two blocks per multiprocessor");
 
 struct Ctl {
@@ -260,7 +264,7 @@ __global__ void __launch_bounds__(THREADS, 2)
     // ================= MMA warp: lane 0 issues both accumulators' MMAs =================
     // One issuing thread per block, as in every tcgen05 kernel this library has run for long: a variant with one issuing
     // warp per accumulator raised rare launch failures (about one in 150 back-to-back calls) that reading did not explain.
-    const uint32_t idesc = instr_desc_e4m3(NT);
+    const uint32_t idesc = instr_desc_e4m3(NCOL);
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
       const int a = it_no & 1;
       if (it_no >= 2 && !dead) dead = !wait_hot(&ctl.accfree[a], ((it_no >> 1) - 1) & 1, DRB_ERR_TMEM);
@@ -272,15 +276,11 @@ __global__ void __launch_bounds__(THREADS, 2)
         if (lane == 0) {
 #pragma unroll
           for (int w = 0; w < NACC; ++w) {
-            const uint32_t acc = tmem + (uint32_t)((a * NACC + w) * NT);
+            const uint32_t acc = tmem + (uint32_t)((a * NACC + w) * NCOL);
             const uint64_t ad = smem_desc(aring + (size_t)sa * A_STAGE + w * A_BYTES);
-            const unsigned char* bt = bring + (size_t)sb * B_STAGE + w * TERMS * BT_BYTES;
+            const uint64_t bd = smem_desc(bring + (size_t)sb * B_STAGE + w * TERMS * BT_BYTES);  // 48 rows: the three terms
 #pragma unroll
-            for (int j = 0; j < TERMS; ++j) {
-              const uint64_t bd = smem_desc(bt + j * BT_BYTES);
-#pragma unroll
-              for (int k32 = 0; k32 < KC / 32; ++k32) mma_e4m3(acc, ad + 2 * k32, bd + 2 * k32, idesc, step > 0 || j > 0 || k32 > 0);
-            }
+            for (int k32 = 0; k32 < KC / 32; ++k32) mma_e4m3(acc, ad + 2 * k32, bd + 2 * k32, idesc, step > 0 || k32 > 0);
           }
           mma_commit(&ctl.aempty[sa]);
           mma_commit(&ctl.bempty[sb]);
@@ -323,9 +323,18 @@ __global__ void __launch_bounds__(THREADS, 2)
       const int a = pno & 1;
       if (!dead) dead = !wait_hot(&ctl.accfull[a], (pno >> 1) & 1, DRB_ERR_TMEM);
       tc_fence_after();
-      uint32_t v0[16], v1[16];
-      tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)((a * NACC) * NT), v0);
-      tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)((a * NACC + 1) * NT), v1);
+      float g[NT], u[NT];
+#pragma unroll
+      for (int j = 0; j < TERMS; ++j) {  // the three terms' column groups add up
+        uint32_t v0[16], v1[16];
+        tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)((a * NACC) * NCOL + j * NT), v0);
+        tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)((a * NACC + 1) * NCOL + j * NT), v1);
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+          g[i] = j == 0 ? __uint_as_float(v0[i]) : g[i] + __uint_as_float(v0[i]);
+          u[i] = j == 0 ? __uint_as_float(v1[i]) : u[i] + __uint_as_float(v1[i]);
+        }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl.accfree[a]);
@@ -334,8 +343,7 @@ __global__ void __launch_bounds__(THREADS, 2)
 #pragma unroll
       for (int i = 0; i < NT; ++i)
         if (i < nt) {
-          const float g = __uint_as_float(v0[i]) * c0[i], u = __uint_as_float(v1[i]) * c1[i];
-          dst[(size_t)rows[i] * I + pit.mt * TILE_M + r] = f2h_sat(silu_f(g) * u);
+          dst[(size_t)rows[i] * I + pit.mt * TILE_M + r] = f2h_sat(silu_f(g[i] * c0[i]) * (u[i] * c1[i]));
         }
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl.tabempty[pno % NTAB]);
@@ -401,10 +409,11 @@ __global__ void __launch_bounds__(THREADS, 2)
 // ---- the down projection ------------------------------------------------------------------------------------------
 // K is only four chunks here and a tile is 64 KB, so a work item of one tile would spend more on its token tile, its
 // table entry and its hand-overs than on its weights. Instead the chunk's scale stays out of the token operand:
-// B'[t][k] = act[t][k] / c_t serves EVERY tile of the expert, each chunk of a tile gets an accumulator of its own (four
-// per tile, 16 columns each), and the epilogue forms c_t * sum_kb s[tile][kb] * acc_kb. A work item is (expert, group of
-// up to 16 tokens, four consecutive tiles): B' is prepared once per item (24 KB, two items' worth resident), the table
-// warp reads each token row once per item, and the weights stream through a ring of 16 KB boxes, one per chunk.
+// B'[t][k] = act[t][k] / c_t serves EVERY tile of the expert, each chunk of a tile has an accumulator of its own (four of
+// 48 columns, used as a ring: the epilogue drains chunk kb of one tile while the MMAs of the next chunks run), and the
+// epilogue forms c_t * sum_kb s[tile][kb] * acc_kb. A work item is (expert, group of up to 16 tokens, four consecutive
+// tiles): B' is prepared once per item (24 KB, two items' worth resident), the table warp reads each token row once per
+// item, and the weights stream through a ring of 16 KB boxes, one per chunk.
 namespace down {
 
 constexpr int NKB = I / KC;                 // 4 chunks = 4 accumulators per tile
@@ -414,13 +423,14 @@ constexpr int NSA = 3;                      // weight boxes in flight
 constexpr int BI_BYTES = NKB * TERMS * BT_BYTES;  // one item's token operand: 24 KB
 constexpr int TAB_SLOT = (NT + NT + TPI * NKB) * 4 + 16;  // token rows | c | scales [tile][chunk] | nt
 constexpr size_t SMEM = 1024 + CTL_BYTES + (size_t)NSA * A_BYTES + 2 * BI_BYTES + NTAB * TAB_SLOT + BASE_BYTES;
-constexpr int TMEM_COLS = 2 * NKB * NT;     // two tiles in flight: 128 columns
+constexpr int TMEM_COLS = 256;              // four accumulators of 48 columns = 192, rounded up
+static_assert(NKB * NCOL <= TMEM_COLS, "tensor memory");
 static_assert(SMEM <= 113 * 1024, "two blocks per multiprocessor");
 
 struct Ctl {
   uint64_t afull[NSA], aempty[NSA];    // a weight box landed / the MMAs that read it completed
   uint64_t bfull[2][NKB], bempty[2];   // a chunk of an item's token operand written (per prep warp) / the item's MMAs completed (per MMA warp)
-  uint64_t accfull[2], accfree[2];     // a tile's four accumulators complete (per MMA warp) / drained (per prep warp)
+  uint64_t accfull[NKB], accfree[NKB]; // a chunk's accumulator complete / drained (one arrival per prep warp)
   uint64_t tabfull[NTAB], tabempty[NTAB];
   uint32_t tmem_base;
 };
@@ -445,8 +455,8 @@ __global__ void __launch_bounds__(THREADS, 2)
     for (int s = 0; s < 2; ++s) {
       for (int kb = 0; kb < NKB; ++kb) mbar_init(&ctl.bfull[s][kb], PREP_WARPS);
       mbar_init(&ctl.bempty[s], 1);
-      mbar_init(&ctl.accfull[s], 1), mbar_init(&ctl.accfree[s], PREP_WARPS);
     }
+    for (int kb = 0; kb < NKB; ++kb) mbar_init(&ctl.accfull[kb], 1), mbar_init(&ctl.accfree[kb], PREP_WARPS);
     for (int s = 0; s < NTAB; ++s) mbar_init(&ctl.tabfull[s], 1), mbar_init(&ctl.tabempty[s], PREP_WARPS);
     mbar_fence_init();
   }
@@ -519,33 +529,26 @@ __global__ void __launch_bounds__(THREADS, 2)
       if (!dead) dead = !mbar_wait(&ctl.aempty[k % NSA], (k / NSA) & 1, DRB_ERR_EMPTY_WAIT);
   } else if (warp == MMA_WARP) {
     // ================= MMA warp: lane 0 issues; chunk kb of a tile goes into accumulator kb =================
-    const uint32_t idesc = instr_desc_e4m3(NT);
+    const uint32_t idesc = instr_desc_e4m3(NCOL);
     unsigned tl_no = 0;  // tiles so far
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
       const int ip = it_no & 1;
       for (int i = 0; i < TPI; ++i, ++tl_no) {
-        const int tp = tl_no & 1;
-        if (tl_no >= 2 && !dead) dead = !wait_hot(&ctl.accfree[tp], ((tl_no >> 1) - 1) & 1, DRB_ERR_TMEM);
         for (int kb = 0; kb < NKB; ++kb, ++ch_no) {
           const int sa = ch_no % NSA;
+          if (tl_no >= 1 && !dead) dead = !wait_hot(&ctl.accfree[kb], (tl_no - 1) & 1, DRB_ERR_TMEM);
           if (i == 0 && !dead) dead = !wait_hot(&ctl.bfull[ip][kb], (it_no >> 1) & 1, DRB_ERR_TMEM);
           if (!dead) dead = !wait_hot(&ctl.afull[sa], (ch_no / NSA) & 1, DRB_ERR_TMEM);
           tc_fence_after();
           if (lane == 0) {
-            const uint32_t acc = tmem + (uint32_t)((tp * NKB + kb) * NT);
+            const uint32_t acc = tmem + (uint32_t)(kb * NCOL);
             const uint64_t ad = smem_desc(aring + (size_t)sa * A_BYTES);
-            const unsigned char* bt = bbuf + (size_t)ip * BI_BYTES + kb * TERMS * BT_BYTES;
+            const uint64_t bd = smem_desc(bbuf + (size_t)ip * BI_BYTES + kb * TERMS * BT_BYTES);  // 48 rows: the three terms
 #pragma unroll
-            for (int j = 0; j < TERMS; ++j) {
-              const uint64_t bd = smem_desc(bt + j * BT_BYTES);
-#pragma unroll
-              for (int k32 = 0; k32 < KC / 32; ++k32) mma_e4m3(acc, ad + 2 * k32, bd + 2 * k32, idesc, j > 0 || k32 > 0);
-            }
+            for (int k32 = 0; k32 < KC / 32; ++k32) mma_e4m3(acc, ad + 2 * k32, bd + 2 * k32, idesc, k32 > 0);
             mma_commit(&ctl.aempty[sa]);
-            if (kb == NKB - 1) {
-              if (i == TPI - 1) mma_commit(&ctl.bempty[ip]);
-              mma_commit(&ctl.accfull[tp]);
-            }
+            if (i == TPI - 1 && kb == NKB - 1) mma_commit(&ctl.bempty[ip]);
+            mma_commit(&ctl.accfull[kb]);
           }
           __syncwarp();
         }
@@ -602,21 +605,23 @@ __global__ void __launch_bounds__(THREADS, 2)
       const int* rows = tab_row(tl.it_no);
       const float* cs = tab_c(tl.it_no);
       const float* sc = tab_s(tl.it_no) + (tl.mt % TPI) * NKB;
-      const int tp = tl.tl_no & 1;
-      if (!dead) dead = !wait_hot(&ctl.accfull[tp], (tl.tl_no >> 1) & 1, DRB_ERR_TMEM);
-      tc_fence_after();
       float sum[NT];
 #pragma unroll
       for (int kb = 0; kb < NKB; ++kb) {
-        uint32_t v[16];
-        tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)((tp * NKB + kb) * NT), v);
+        if (!dead) dead = !wait_hot(&ctl.accfull[kb], tl.tl_no & 1, DRB_ERR_TMEM);
+        tc_fence_after();
         const float s = sc[kb];
 #pragma unroll
-        for (int i = 0; i < NT; ++i) sum[i] = kb == 0 ? s * __uint_as_float(v[i]) : fmaf(s, __uint_as_float(v[i]), sum[i]);
+        for (int j = 0; j < TERMS; ++j) {  // the three terms' column groups add up
+          uint32_t v[16];
+          tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(kb * NCOL + j * NT), v);
+#pragma unroll
+          for (int i = 0; i < NT; ++i) sum[i] = (kb == 0 && j == 0) ? s * __uint_as_float(v[i]) : fmaf(s, __uint_as_float(v[i]), sum[i]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl.accfree[kb]);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl.accfree[tp]);
 #pragma unroll
       for (int i = 0; i < NT; ++i)
         if (i < nt) dst[(size_t)rows[i] * H + tl.mt * TILE_M + r] = sum[i] * cs[i];
@@ -625,8 +630,8 @@ __global__ void __launch_bounds__(THREADS, 2)
         if (lane == 0) mbar_arrive(&ctl.tabempty[tl.it_no % NTAB]);
       }
     };
-    Tile pend[2];
-    int npend = 0;
+    Tile pend = {};
+    bool have_pend = false;
     unsigned tl_no = 0;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
       const Item it = decode(item);
@@ -667,15 +672,15 @@ __global__ void __launch_bounds__(THREADS, 2)
         __syncwarp();
         if (lane == 0) mbar_arrive(&ctl.bfull[ip][kb]);
       }
-      // epilogues: the two tiles left over from the item before, then this item's first two
-      for (int i = 0; i < npend; ++i) epilogue(pend[i]);
-      for (int i = 0; i < TPI - 2; ++i, ++tl_no) epilogue(Tile{it.q * TPI + i, it_no, tl_no, false});
-      for (int i = TPI - 2; i < TPI; ++i, ++tl_no) pend[i - (TPI - 2)] = Tile{it.q * TPI + i, it_no, tl_no, i == TPI - 1};
-      npend = 2;
-      // the rows of pend[] are looked up in this item's table slot, which the table warp rewrites only after the
-      // last tile's epilogue has released it
+      // epilogues: the last tile of the item before (its MMAs ran while this item's operand was prepared), then this
+      // item's first three; the tile's rows are looked up in its item's table slot, which the table warp rewrites only
+      // after the last tile's epilogue has released it
+      if (have_pend) epilogue(pend);
+      for (int i = 0; i < TPI - 1; ++i, ++tl_no) epilogue(Tile{it.q * TPI + i, it_no, tl_no, false});
+      pend = Tile{it.q * TPI + TPI - 1, it_no, tl_no++, true};
+      have_pend = true;
     }
-    for (int i = 0; i < npend; ++i) epilogue(pend[i]);
+    if (have_pend) epilogue(pend);
     for (unsigned n = it_no > 2 ? it_no - 2 : 0; n < it_no; ++n)  // tail: see the loader's
       if (!dead) dead = !mbar_wait(&ctl.bempty[n & 1], (n >> 1) & 1, DRB_ERR_TMEM);
   }
