@@ -125,7 +125,11 @@ int dr_moe_permute(const int* idx, int rows, int topk, const int* offsets, int* 
 int dr_moe_prefill(const uint8_t* gu_q, const dr_half* gu_sm, const uint8_t* d_q, const dr_half* d_sm,
                    const dr_bf16* xp, const int* offsets, const int* counts, dr_bf16* act, float* y, int e, int h, int i,
                    dr_stream st);
-/* dr_moe_prefill over block-FP8 experts (layouts as dr_moe_decode_fp8). drama.cu:971-1109; ffi.rs:52-55 */
+/* dr_moe_prefill over block-FP8 experts (layouts as dr_moe_decode_fp8). The weight bytes reach the tensor cores as
+ * E4M3 (tiled TMA, tcgen05 kind::f8f6f4); the block scales ride on the token operand. Until its rows are written, y is
+ * scratch (its first floats hold every token row's largest magnitude), as act is. gu_w and d_w 16-byte aligned.
+ * Returns -3 if a tensor map cannot be encoded. e > 256, or DRB_FP8_DEQUANT=1 in the environment: the kernels that turn
+ * the weights into fp16 first. drama.cu:971-1109; ffi.rs:52-55 */
 int dr_moe_prefill_fp8(const uint8_t* gu_w, const float* gu_s, const uint8_t* d_w, const float* d_s, const dr_bf16* xp,
                        const int* offsets, const int* counts, dr_bf16* act, float* y, int e, int h, int i, dr_stream st);
 /* drama.cu:780-797; ffi.rs:70-73 */
