@@ -103,6 +103,15 @@ DRB_DEV bool mbar_wait(uint64_t* bar, unsigned parity, unsigned err_code, unsign
   return false;
 }
 
+// The same for a wait on a ring's step-to-step path: no sleep between polls (a sleeping waiter adds its wake-up time
+// to every hand-over of the ring), bounded all the same.
+DRB_DEV bool mbar_wait_hot(uint64_t* bar, unsigned parity, unsigned err_code) {
+  for (unsigned it = 0; it < (1u << 24); ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  atomicMax(&g_drb_error, err_code);
+  return false;
+}
+
 // Global -> shared bulk copy. dst, src 16-byte aligned; bytes a multiple of 16.
 DRB_DEV void bulk_g2s(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(

@@ -112,15 +112,6 @@ DRB_DEV void split3(float v0, float v1, uint32_t (&t)[TERMS]) {
   }
 }
 
-// A wait on the step-to-step path: polls without sleeping between polls (a sleeping waiter adds its wake-up time to every
-// hand-over of the ring), bounded all the same.
-DRB_DEV bool wait_hot(uint64_t* bar, unsigned parity, unsigned err_code) {
-  for (unsigned it = 0; it < (1u << 24); ++it)
-    if (mbar_try_wait(bar, parity)) return true;
-  atomicMax(&g_drb_error, err_code);
-  return false;
-}
-
 // ---- every token row's largest magnitude ------------------------------------------------------------------------
 // One warp per row of xp (bf16 [slots, H]); out[slot] = max |x|. The rows in use end at max_e (offsets[e] + counts[e]).
 // Runs ahead of the gate/up kernel, which would otherwise recompute it in every one of a token group's four tiles.
@@ -245,7 +236,7 @@ __global__ void __launch_bounds__(THREADS, 2)
       const Item it = decode(item);
       for (int step = 0; step < NSTEP; ++step, ++st_no) {
         const int s = st_no % NSA;
-        if (st_no >= NSA && !dead) dead = !wait_hot(&ctl.aempty[s], ((st_no / NSA) - 1) & 1, DRB_ERR_EMPTY_WAIT);
+        if (st_no >= NSA && !dead) dead = !mbar_wait_hot(&ctl.aempty[s], ((st_no / NSA) - 1) & 1, DRB_ERR_EMPTY_WAIT);
         if (lane == 0) {
           unsigned char* dstp = aring + (size_t)s * A_STAGE;
           mbar_expect_tx(&ctl.afull[s], A_STAGE);
@@ -267,11 +258,11 @@ __global__ void __launch_bounds__(THREADS, 2)
     const uint32_t idesc = instr_desc_e4m3(NCOL);
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
       const int a = it_no & 1;
-      if (it_no >= 2 && !dead) dead = !wait_hot(&ctl.accfree[a], ((it_no >> 1) - 1) & 1, DRB_ERR_TMEM);
+      if (it_no >= 2 && !dead) dead = !mbar_wait_hot(&ctl.accfree[a], ((it_no >> 1) - 1) & 1, DRB_ERR_TMEM);
       for (int step = 0; step < NSTEP; ++step, ++st_no) {
         const int sa = st_no % NSA, sb = st_no % NSB;
-        if (!dead) dead = !wait_hot(&ctl.bfull[sb], (st_no / NSB) & 1, DRB_ERR_TMEM);
-        if (!dead) dead = !wait_hot(&ctl.afull[sa], (st_no / NSA) & 1, DRB_ERR_TMEM);
+        if (!dead) dead = !mbar_wait_hot(&ctl.bfull[sb], (st_no / NSB) & 1, DRB_ERR_TMEM);
+        if (!dead) dead = !mbar_wait_hot(&ctl.afull[sa], (st_no / NSA) & 1, DRB_ERR_TMEM);
         tc_fence_after();
         if (lane == 0) {
 #pragma unroll
@@ -321,7 +312,7 @@ __global__ void __launch_bounds__(THREADS, 2)
       const int nt = tab_nt(pno)[0];
       const int* rows = tab_row(pno);
       const int a = pno & 1;
-      if (!dead) dead = !wait_hot(&ctl.accfull[a], (pno >> 1) & 1, DRB_ERR_TMEM);
+      if (!dead) dead = !mbar_wait_hot(&ctl.accfull[a], (pno >> 1) & 1, DRB_ERR_TMEM);
       tc_fence_after();
       float g[NT], u[NT];
 #pragma unroll
@@ -367,7 +358,7 @@ __global__ void __launch_bounds__(THREADS, 2)
         const uint32_t xs[8] = {xl.x, xl.y, xl.z, xl.w, xh.x, xh.y, xh.z, xh.w};
         if (live && step + 1 < NSTEP) xl = __ldg(rowp + (step + 1) * (KC / 8)), xh = __ldg(rowp + (step + 1) * (KC / 8) + 1);
         // the MMAs that read this stage NSB steps ago must have completed
-        if (st_no >= NSB && !dead) dead = !wait_hot(&ctl.bempty[sb], ((st_no / NSB) - 1) & 1, DRB_ERR_TMEM);
+        if (st_no >= NSB && !dead) dead = !mbar_wait_hot(&ctl.bempty[sb], ((st_no / NSB) - 1) & 1, DRB_ERR_TMEM);
         unsigned char* bt = bring + (size_t)sb * B_STAGE;
 #pragma unroll
         for (int w = 0; w < NACC; ++w) {
@@ -516,7 +507,7 @@ __global__ void __launch_bounds__(THREADS, 2)
       for (int i = 0; i < TPI; ++i)
         for (int kb = 0; kb < NKB; ++kb, ++ch_no) {
           const int s = ch_no % NSA;
-          if (ch_no >= NSA && !dead) dead = !wait_hot(&ctl.aempty[s], ((ch_no / NSA) - 1) & 1, DRB_ERR_EMPTY_WAIT);
+          if (ch_no >= NSA && !dead) dead = !mbar_wait_hot(&ctl.aempty[s], ((ch_no / NSA) - 1) & 1, DRB_ERR_EMPTY_WAIT);
           if (lane == 0) {
             mbar_expect_tx(&ctl.afull[s], A_BYTES);
             tma_load_2d(aring + (size_t)s * A_BYTES, &tm, kb * KC, it.e * H + (it.q * TPI + i) * TILE_M, &ctl.afull[s]);
@@ -536,9 +527,9 @@ __global__ void __launch_bounds__(THREADS, 2)
       for (int i = 0; i < TPI; ++i, ++tl_no) {
         for (int kb = 0; kb < NKB; ++kb, ++ch_no) {
           const int sa = ch_no % NSA;
-          if (tl_no >= 1 && !dead) dead = !wait_hot(&ctl.accfree[kb], (tl_no - 1) & 1, DRB_ERR_TMEM);
-          if (i == 0 && !dead) dead = !wait_hot(&ctl.bfull[ip][kb], (it_no >> 1) & 1, DRB_ERR_TMEM);
-          if (!dead) dead = !wait_hot(&ctl.afull[sa], (ch_no / NSA) & 1, DRB_ERR_TMEM);
+          if (tl_no >= 1 && !dead) dead = !mbar_wait_hot(&ctl.accfree[kb], (tl_no - 1) & 1, DRB_ERR_TMEM);
+          if (i == 0 && !dead) dead = !mbar_wait_hot(&ctl.bfull[ip][kb], (it_no >> 1) & 1, DRB_ERR_TMEM);
+          if (!dead) dead = !mbar_wait_hot(&ctl.afull[sa], (ch_no / NSA) & 1, DRB_ERR_TMEM);
           tc_fence_after();
           if (lane == 0) {
             const uint32_t acc = tmem + (uint32_t)(kb * NCOL);
@@ -608,7 +599,7 @@ __global__ void __launch_bounds__(THREADS, 2)
       float sum[NT];
 #pragma unroll
       for (int kb = 0; kb < NKB; ++kb) {
-        if (!dead) dead = !wait_hot(&ctl.accfull[kb], tl.tl_no & 1, DRB_ERR_TMEM);
+        if (!dead) dead = !mbar_wait_hot(&ctl.accfull[kb], tl.tl_no & 1, DRB_ERR_TMEM);
         tc_fence_after();
         const float s = sc[kb];
 #pragma unroll
