@@ -747,8 +747,9 @@ extern "C" int dr_moe_prefill_fp8(const uint8_t* gu_w, const float* gu_s, const 
   }();
   if (!dequant_route && E <= pf8::MAX_ITEM_SETS) {
     CUtensorMap tm_gu, tm_d;
-    if (pft::map_rows(&tm_gu, gu_w, (uint64_t)E * 2 * pf::I, pf::H) != 0) return -3;
-    if (pft::map_rows(&tm_d, d_w, (uint64_t)E * pf::H, pf::I) != 0) return -3;
+    // 256-byte L2 promotion: a chunk's box brings the next chunk's 128 bytes of every row into L2 with it
+    if (pft::map_rows(&tm_gu, gu_w, (uint64_t)E * 2 * pf::I, pf::H, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) != 0) return -3;
+    if (pft::map_rows(&tm_d, d_w, (uint64_t)E * pf::H, pf::I, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) != 0) return -3;
     const dim3 grid(2 * dev.sms), block(pf8::THREADS);
     // y is written last (by the down kernel); until then its first floats hold every token row's largest magnitude
     pf8::k_rowmax_bf16<<<2 * dev.sms, 256, 0, st>>>(xp, offsets, counts, E, y);

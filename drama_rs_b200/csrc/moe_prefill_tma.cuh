@@ -496,14 +496,15 @@ static cudaError_t resolve_encode() {
 }
 
 // Down projection: [rows, row_bytes] row-major, boxes of 128 rows x 128 bytes.
-static int map_rows(CUtensorMap* map, const void* p, uint64_t rows, uint64_t row_bytes) {
+static int map_rows(CUtensorMap* map, const void* p, uint64_t rows, uint64_t row_bytes,
+                    CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_128B) {
   if (!g_encode) return -3;
   const cuuint64_t dims[2] = {row_bytes, rows};
   const cuuint64_t strides[1] = {row_bytes};
   const cuuint32_t box[2] = {ROW_BYTES, TILE_M};
   const cuuint32_t estr[2] = {1, 1};
   return g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(p), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
+                  CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
              ? 0
              : -3;
 }
