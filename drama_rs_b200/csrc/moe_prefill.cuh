@@ -754,7 +754,7 @@ extern "C" int dr_moe_prefill_fp8(const uint8_t* gu_w, const float* gu_s, const 
     // y is written last (by the down kernel); until then its first floats hold every token row's largest magnitude
     pf8::k_rowmax_bf16<<<2 * dev.sms, 256, 0, st>>>(xp, offsets, counts, E, y);
     drb_launch(pf8::k_gate_up_fp8, grid, block, pf8::SMEM, st, false, tm_gu, gu_s, xp, (const float*)y, (__half*)act, offsets, counts, E);
-    drb_launch(pf8::down::k_down_fp8, grid, block, pf8::down::SMEM, st, false, tm_d, d_s, (const __half*)act, y, offsets, counts, E);
+    drb_launch(pf8::down::k_down_fp8, grid, dim3(pf8::down::THREADS), pf8::down::SMEM, st, false, tm_d, d_s, (const __half*)act, y, offsets, counts, E);
     return 0;
   }
   const dim3 grid(pfmma::BLOCKS_PER_SM * dev.sms), block(pfmma::THREADS);

@@ -403,14 +403,20 @@ __global__ void __launch_bounds__(THREADS, 2)
 // B'[t][k] = act[t][k] / c_t serves EVERY tile of the expert, each chunk of a tile has an accumulator of its own (four of
 // 48 columns, used as a ring: the epilogue drains chunk kb of one tile while the MMAs of the next chunks run), and the
 // epilogue forms c_t * sum_kb s[tile][kb] * acc_kb. A work item is (expert, group of up to 16 tokens, four consecutive
-// tiles): B' is prepared once per item (24 KB, two items' worth resident), the table warp reads each token row once per
-// item, and the weights stream through a ring of 16 KB boxes, one per chunk.
+// tiles): B' is prepared once per item (24 KB, two items' worth resident) by two operand warps that run an item ahead,
+// four epilogue warps do nothing but drain accumulators (the MMA warp waits for a free accumulator otherwise), the
+// table warp reads each token row once per item and runs two items ahead, and the weights stream through a ring of
+// 16 KB boxes, one per chunk.
 namespace down {
 
+constexpr int EPI_WARPS = 4, OPER_WARPS = 2;
+constexpr int OPER_WARP0 = EPI_WARPS, MMA_W = EPI_WARPS + OPER_WARPS, LOAD_W = MMA_W + 1, TABLE_W = MMA_W + 2;
+constexpr int THREADS = (TABLE_W + 1) * 32;  // 288
 constexpr int NKB = I / KC;                 // 4 chunks = 4 accumulators per tile
 constexpr int TPI = 4;                      // tiles per item
 constexpr int QPE = H / TILE_M / TPI;       // items per expert and token group: 4
 constexpr int NSA = 3;                      // weight boxes in flight
+constexpr int NTAB = 3;                     // table slots: the table warp runs two items ahead
 constexpr int BI_BYTES = NKB * TERMS * BT_BYTES;  // one item's token operand: 24 KB
 constexpr int TAB_SLOT = (NT + NT + TPI * NKB) * 4 + 16;  // token rows | c | scales [tile][chunk] | nt
 constexpr size_t SMEM = 1024 + CTL_BYTES + (size_t)NSA * A_BYTES + 2 * BI_BYTES + NTAB * TAB_SLOT + BASE_BYTES;
@@ -420,9 +426,9 @@ static_assert(SMEM <= 113 * 1024, "two blocks per multiprocessor");
 
 struct Ctl {
   uint64_t afull[NSA], aempty[NSA];    // a weight box landed / the MMAs that read it completed
-  uint64_t bfull[2][NKB], bempty[2];   // a chunk of an item's token operand written (per prep warp) / the item's MMAs completed (per MMA warp)
-  uint64_t accfull[NKB], accfree[NKB]; // a chunk's accumulator complete / drained (one arrival per prep warp)
-  uint64_t tabfull[NTAB], tabempty[NTAB];
+  uint64_t bfull[2][NKB], bempty[2];   // a chunk of an item's token operand written (one arrival per operand warp) / the item's MMAs completed
+  uint64_t accfull[NKB], accfree[NKB]; // a chunk's accumulator complete / drained (one arrival per epilogue warp)
+  uint64_t tabfull[NTAB], tabempty[NTAB];  // an item's table written / read for the last time (operand and epilogue warps)
   uint32_t tmem_base;
 };
 static_assert(sizeof(Ctl) <= CTL_BYTES, "control block");
@@ -444,14 +450,14 @@ __global__ void __launch_bounds__(THREADS, 2)
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSA; ++s) mbar_init(&ctl.afull[s], 1), mbar_init(&ctl.aempty[s], 1);
     for (int s = 0; s < 2; ++s) {
-      for (int kb = 0; kb < NKB; ++kb) mbar_init(&ctl.bfull[s][kb], PREP_WARPS);
+      for (int kb = 0; kb < NKB; ++kb) mbar_init(&ctl.bfull[s][kb], OPER_WARPS);
       mbar_init(&ctl.bempty[s], 1);
     }
-    for (int kb = 0; kb < NKB; ++kb) mbar_init(&ctl.accfull[kb], 1), mbar_init(&ctl.accfree[kb], PREP_WARPS);
-    for (int s = 0; s < NTAB; ++s) mbar_init(&ctl.tabfull[s], 1), mbar_init(&ctl.tabempty[s], PREP_WARPS);
+    for (int kb = 0; kb < NKB; ++kb) mbar_init(&ctl.accfull[kb], 1), mbar_init(&ctl.accfree[kb], EPI_WARPS);
+    for (int s = 0; s < NTAB; ++s) mbar_init(&ctl.tabfull[s], 1), mbar_init(&ctl.tabempty[s], EPI_WARPS + OPER_WARPS);
     mbar_fence_init();
   }
-  if (warp == MMA_WARP) tmem_alloc(&ctl.tmem_base, TMEM_COLS);
+  if (warp == MMA_W) tmem_alloc(&ctl.tmem_base, TMEM_COLS);
   if (warp == 0) {  // items per expert, exclusive prefix in base[]
     int carry = 0;
     for (int s0 = 0; s0 < E; s0 += 32) {
@@ -501,7 +507,8 @@ __global__ void __launch_bounds__(THREADS, 2)
   unsigned it_no = 0;  // items so far
   unsigned ch_no = 0;  // weight boxes so far (loader and MMA warp count alike)
 
-  if (warp == LOAD_WARP) {
+  if (warp == LOAD_W) {
+    // ================= loader: lane 0 requests a weight box per chunk =================
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
       const Item it = decode(item);
       for (int i = 0; i < TPI; ++i)
@@ -518,7 +525,7 @@ __global__ void __launch_bounds__(THREADS, 2)
     // Tail: the block must not end before the completion arrivals for its last boxes have landed.
     for (unsigned k = ch_no > NSA ? ch_no - NSA : 0; k < ch_no; ++k)
       if (!dead) dead = !mbar_wait(&ctl.aempty[k % NSA], (k / NSA) & 1, DRB_ERR_EMPTY_WAIT);
-  } else if (warp == MMA_WARP) {
+  } else if (warp == MMA_W) {
     // ================= MMA warp: lane 0 issues; chunk kb of a tile goes into accumulator kb =================
     const uint32_t idesc = instr_desc_e4m3(NCOL);
     unsigned tl_no = 0;  // tiles so far
@@ -545,8 +552,8 @@ __global__ void __launch_bounds__(THREADS, 2)
         }
       }
     }
-  } else if (warp == TABLE_WARP) {
-    // ================= table warp: one item ahead =================
+  } else if (warp == TABLE_W) {
+    // ================= table warp: two items ahead =================
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
       const Item it = decode(item);
       if (it_no >= NTAB && !dead) dead = !mbar_wait(&ctl.tabempty[it_no % NTAB], ((it_no / NTAB) - 1) & 1, DRB_ERR_EMPTY_WAIT);
@@ -580,104 +587,101 @@ __global__ void __launch_bounds__(THREADS, 2)
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl.tabfull[it_no % NTAB]);
     }
-  } else {
-    // ================= prep warps: the item's token operand, and every tile's epilogue =================
-    const int pt = threadIdx.x;
-    const int t = pt >> 3, c = pt & 7;
-    const int r = warp * 32 + lane;
-    const uint32_t b_off = swz_off(t, c);
-    struct Tile {
-      int mt;
-      unsigned it_no, tl_no;
-      bool last;
-    };
-    auto epilogue = [&](const Tile& tl) {
-      const int nt = tab_nt(tl.it_no)[0];
-      const int* rows = tab_row(tl.it_no);
-      const float* cs = tab_c(tl.it_no);
-      const float* sc = tab_s(tl.it_no) + (tl.mt % TPI) * NKB;
-      float sum[NT];
-#pragma unroll
-      for (int kb = 0; kb < NKB; ++kb) {
-        if (!dead) dead = !mbar_wait_hot(&ctl.accfull[kb], tl.tl_no & 1, DRB_ERR_TMEM);
-        tc_fence_after();
-        const float s = sc[kb];
-#pragma unroll
-        for (int j = 0; j < TERMS; ++j) {  // the three terms' column groups add up
-          uint32_t v[16];
-          tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(kb * NCOL + j * NT), v);
-#pragma unroll
-          for (int i = 0; i < NT; ++i) sum[i] = (kb == 0 && j == 0) ? s * __uint_as_float(v[i]) : fmaf(s, __uint_as_float(v[i]), sum[i]);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl.accfree[kb]);
-      }
-#pragma unroll
-      for (int i = 0; i < NT; ++i)
-        if (i < nt) dst[(size_t)rows[i] * H + tl.mt * TILE_M + r] = sum[i] * cs[i];
-      if (tl.last) {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl.tabempty[tl.it_no % NTAB]);
-      }
-    };
-    Tile pend = {};
-    bool have_pend = false;
-    unsigned tl_no = 0;
+  } else if (warp >= OPER_WARP0) {
+    // ================= operand warps: an item's token operand, three E4M3 terms of act / c_t =================
+    const int po = threadIdx.x - OPER_WARP0 * 32;  // 0 .. 63
+    const int c = po & 7, t0 = po >> 3;            // 16-input piece; tokens t0 and t0 + 8
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
-      const Item it = decode(item);
       const int ip = it_no & 1;
       if (!dead) dead = !mbar_wait(&ctl.tabfull[it_no % NTAB], (it_no / NTAB) & 1, DRB_ERR_FULL_WAIT);
       // the MMAs of the item before last read this buffer
       if (it_no >= 2 && !dead) dead = !mbar_wait(&ctl.bempty[ip], ((it_no >> 1) - 1) & 1, DRB_ERR_TMEM);
       const int nt = tab_nt(it_no)[0];
-      const bool live = t < nt;
-      const float inv_c = 1.f / tab_c(it_no)[t];
-      const uint4* rowp = reinterpret_cast<const uint4*>(src + (size_t)tab_row(it_no)[t] * I + 16 * c);
-      uint4 xl[NKB], xh[NKB];
 #pragma unroll
-      for (int kb = 0; kb < NKB; ++kb) {
-        xl[kb] = xh[kb] = make_uint4(0u, 0u, 0u, 0u);
-        if (live) xl[kb] = __ldcg(rowp + kb * (KC / 8)), xh[kb] = __ldcg(rowp + kb * (KC / 8) + 1);
-      }
+      for (int half = 0; half < 2; ++half) {
+        const int t = t0 + half * (NT / 2);
+        const bool live = t < nt;
+        const float inv_c = 1.f / tab_c(it_no)[t];
+        const uint4* rowp = reinterpret_cast<const uint4*>(src + (size_t)tab_row(it_no)[t] * I + 16 * c);
+        const uint32_t b_off = swz_off(t, c);
+        uint4 xl[NKB], xh[NKB];
 #pragma unroll
-      for (int kb = 0; kb < NKB; ++kb) {
-        const uint32_t xs[8] = {xl[kb].x, xl[kb].y, xl[kb].z, xl[kb].w, xh[kb].x, xh[kb].y, xh[kb].z, xh[kb].w};
-        uint32_t o[TERMS][4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint32_t pa[TERMS], pb[TERMS];
-          const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&xs[2 * q]));
-          const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&xs[2 * q + 1]));
-          split3(fa.x * inv_c, fa.y * inv_c, pa);
-          split3(fb.x * inv_c, fb.y * inv_c, pb);
-#pragma unroll
-          for (int j = 0; j < TERMS; ++j) o[j][q] = pa[j] | (pb[j] << 16);
+        for (int kb = 0; kb < NKB; ++kb) {
+          xl[kb] = xh[kb] = make_uint4(0u, 0u, 0u, 0u);
+          if (live) xl[kb] = __ldcg(rowp + kb * (KC / 8)), xh[kb] = __ldcg(rowp + kb * (KC / 8) + 1);
         }
-        if (live) {
-          unsigned char* bt = bbuf + (size_t)ip * BI_BYTES + kb * TERMS * BT_BYTES;
 #pragma unroll
-          for (int j = 0; j < TERMS; ++j) *reinterpret_cast<uint4*>(bt + j * BT_BYTES + b_off) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+        for (int kb = 0; kb < NKB; ++kb) {
+          const uint32_t xs[8] = {xl[kb].x, xl[kb].y, xl[kb].z, xl[kb].w, xh[kb].x, xh[kb].y, xh[kb].z, xh[kb].w};
+          uint32_t o[TERMS][4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t pa[TERMS], pb[TERMS];
+            const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&xs[2 * q]));
+            const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&xs[2 * q + 1]));
+            split3(fa.x * inv_c, fa.y * inv_c, pa);
+            split3(fb.x * inv_c, fb.y * inv_c, pb);
+#pragma unroll
+            for (int j = 0; j < TERMS; ++j) o[j][q] = pa[j] | (pb[j] << 16);
+          }
+          if (live) {
+            unsigned char* bt = bbuf + (size_t)ip * BI_BYTES + kb * TERMS * BT_BYTES;
+#pragma unroll
+            for (int j = 0; j < TERMS; ++j) *reinterpret_cast<uint4*>(bt + j * BT_BYTES + b_off) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+          }
         }
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl.bfull[ip][kb]);
       }
-      // epilogues: the last tile of the item before (its MMAs ran while this item's operand was prepared), then this
-      // item's first three; the tile's rows are looked up in its item's table slot, which the table warp rewrites only
-      // after the last tile's epilogue has released it
-      if (have_pend) epilogue(pend);
-      for (int i = 0; i < TPI - 1; ++i, ++tl_no) epilogue(Tile{it.q * TPI + i, it_no, tl_no, false});
-      pend = Tile{it.q * TPI + TPI - 1, it_no, tl_no++, true};
-      have_pend = true;
+      fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+      __syncwarp();
+      if (lane == 0) {
+#pragma unroll
+        for (int kb = 0; kb < NKB; ++kb) mbar_arrive(&ctl.bfull[ip][kb]);
+        mbar_arrive(&ctl.tabempty[it_no % NTAB]);
+      }
     }
-    if (have_pend) epilogue(pend);
     for (unsigned n = it_no > 2 ? it_no - 2 : 0; n < it_no; ++n)  // tail: see the loader's
       if (!dead) dead = !mbar_wait(&ctl.bempty[n & 1], (n >> 1) & 1, DRB_ERR_TMEM);
+  } else {
+    // ================= epilogue warps: drain every tile's four accumulators =================
+    const int r = warp * 32 + lane;  // tile row (warp = tensor-memory lane quarter)
+    unsigned tl_no = 0;
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it_no) {
+      const Item it = decode(item);
+      if (!dead) dead = !mbar_wait(&ctl.tabfull[it_no % NTAB], (it_no / NTAB) & 1, DRB_ERR_FULL_WAIT);
+      const int nt = tab_nt(it_no)[0];
+      const int* rows = tab_row(it_no);
+      const float* cs = tab_c(it_no);
+      for (int i = 0; i < TPI; ++i, ++tl_no) {
+        const float* sc = tab_s(it_no) + i * NKB;
+        const int mt = it.q * TPI + i;
+        float sum[NT];
+#pragma unroll
+        for (int kb = 0; kb < NKB; ++kb) {
+          if (!dead) dead = !mbar_wait_hot(&ctl.accfull[kb], tl_no & 1, DRB_ERR_TMEM);
+          tc_fence_after();
+          const float s = sc[kb];
+#pragma unroll
+          for (int j = 0; j < TERMS; ++j) {  // the three terms' column groups add up
+            uint32_t v[16];
+            tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(kb * NCOL + j * NT), v);
+#pragma unroll
+            for (int q = 0; q < NT; ++q) sum[q] = (kb == 0 && j == 0) ? s * __uint_as_float(v[q]) : fmaf(s, __uint_as_float(v[q]), sum[q]);
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctl.accfree[kb]);
+        }
+#pragma unroll
+        for (int q = 0; q < NT; ++q)
+          if (q < nt) dst[(size_t)rows[q] * H + mt * TILE_M + r] = sum[q] * cs[q];
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl.tabempty[it_no % NTAB]);
+    }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == MMA_WARP) tmem_dealloc(tmem, TMEM_COLS);
+  if (warp == MMA_W) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 }  // namespace down
