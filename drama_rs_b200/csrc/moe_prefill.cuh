@@ -739,12 +739,11 @@ extern "C" int dr_moe_prefill_fp8(const uint8_t* gu_w, const float* gu_s, const 
   if (E <= 0) return 0;
   const DrbDevice& dev = drb_device(st);
   if (!dev.ready) return -2;
-  // The weights reach the tensor cores as E4M3 (moe_prefill_fp8.cuh). DRB_FP8_DEQUANT=1 selects the earlier kernels,
-  // whose threads turn every weight into fp16 first (kept for comparison; same results within the parity bar).
-  static const bool dequant_route = [] {
-    const char* v = getenv("DRB_FP8_DEQUANT");
-    return v && v[0] == '1';
-  }();
+  // The weights reach the tensor cores as E4M3 (moe_prefill_fp8.cuh). DRB_FP8_DEQUANT=1 (read at every call) selects the
+  // earlier kernels, whose threads turn every weight into fp16 first: the route for more than 256 experts, kept
+  // selectable so that both can be compared and tested on the same inputs; same results within the parity bar.
+  const char* route = getenv("DRB_FP8_DEQUANT");
+  const bool dequant_route = route && route[0] == '1';
   if (!dequant_route && E <= pf8::MAX_ITEM_SETS) {
     CUtensorMap tm_gu, tm_d;
     // 256-byte L2 promotion: a chunk's box brings the next chunk's 128 bytes of every row into L2 with it

@@ -152,6 +152,14 @@ DRB_DEV float pow2_normaliser(float s) {
   return __uint_as_float((uint32_t)(254 - (e ? e : 1)) << 23);
 }
 
+// The power of two that brings a block row's LARGEST scale into [1, 2): every scale of the row times it is at most 2,
+// so an E4M3 weight (at most 448) times its normalised scale stays inside fp16 however far the row's scales are apart.
+DRB_DEV float block_row_normaliser(const float* scales, int n) {
+  float m = 0.f;
+  for (int i = 0; i < n; ++i) m = fmaxf(m, fabsf(__ldg(scales + i)));
+  return pow2_normaliser(m);
+}
+
 // Two floats -> packed fp16 (lo, hi), round to nearest, clamped to the largest finite fp16: the operands of the
 // tensor-core path are fp16, whose range ends at 65504 where bf16 and fp32 carry on. An outlier beyond it then
 // degrades (it is clamped) instead of turning a token's whole output row into NaN through an infinity.
@@ -231,7 +239,7 @@ struct SharedExpert {
 // GEMM = 0: gate/up (+ SwiGLU, fp16 out);  GEMM = 1: down (fp32 out).
 // FMT = 0: int4 experts: Q [E, R, K/2] nibbles, SM [E, R, K/64] (scale, min);  R = 2I, K = H for gate/up;  R = H, K = I for down.
 // FMT = 1: block-FP8 experts: Q [E, R, K] E4M3 bytes, SM = f32 scales [E, R/128, K/128]. A row block's scales are
-//   brought into fp16 range by the power of two that normalises the block's first scale (the weights times the
+//   brought into fp16 range by the power of two that normalises the block row's largest scale (the weights times the
 //   scaled scale round once to fp16); the epilogue multiplies the row's result by the inverse power, exactly.
 //   src: gate/up: xp bf16 [slots, H] (or, with row_of, the unpermuted rows [rows, H] and row_of[slot]; fp16 rows when
 //        src_f16 is set: three more significant bits than bf16, which the 1e-3 bar against fp32 rows needs);  down: act fp16 [slots, I]
@@ -361,7 +369,7 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
       const __half2* smrow = SM + ((size_t)e * R + wrow) * (K / 64);
       const float* sfrow = SF + ((size_t)e * (R / 128) + (wrow >> 7)) * (K / 128);  // FMT 1: this row block's scales
       const __half* ssrow = sh.s + (size_t)wrow * (K / 128);                        // shared expert: this row's scales
-      const float norm = (FMT == 1 && !shd) ? pow2_normaliser(__ldg(sfrow)) : 1.f;
+      const float norm = (FMT == 1 && !shd) ? block_row_normaliser(sfrow, K / 128) : 1.f;
       const unsigned char* asrc = static_cast<const unsigned char*>(shd ? sh.src : src);
       void* adst = shd ? sh.dst : dst;
       const int nl = shd ? NL_S : NL_R;
@@ -474,7 +482,7 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
         float unnorm = 1.f;
         if (FMT == 1 && !shd) {
           const int erow = GEMM == 0 ? (r & 1) * I + mt * (TILE_M / 2) + (r >> 1) : mt * TILE_M + r;
-          unnorm = 1.f / pow2_normaliser(__ldg(SF + ((size_t)e * (R / 128) + (erow >> 7)) * (K / 128)));
+          unnorm = 1.f / block_row_normaliser(SF + ((size_t)e * (R / 128) + (erow >> 7)) * (K / 128), K / 128);
         }
         for (int c0 = (warp >> 2) * 16; c0 < N; c0 += 4 * PRODUCER_WARPS) {  // each set of four warps takes every (PRODUCER_WARPS / 4)-th 16-column group
           uint32_t v[16];

@@ -76,11 +76,14 @@ def test_moe_decode_fp8_rejects_other_shapes(st):
                                NULL, 1e-6, NULL, 0, st.raw) == -1
 
 
-def test_moe_prefill_fp8_grouped_kernel(st):
-    """dr_moe_prefill_fp8 on hand-made groups (one expert with more tokens than one accumulator holds, empty experts,
+@pytest.mark.parametrize("route", ["e4m3", "fp16"])
+def test_moe_prefill_fp8_grouped_kernel(st, route, monkeypatch):
+    """Both routes of dr_moe_prefill_fp8 (E4M3 weights straight into the tensor cores; dequantised to fp16 first, the route
+    for more than 256 experts) on hand-made groups (one expert with more tokens than one accumulator holds, empty experts,
     groups of 1, 16 and 17 tokens; scales spread over four orders of magnitude): every output row against the fp64
     expert on the same bf16 row, and against the reference's own kernel."""
     l = ffi.lib()
+    monkeypatch.setenv("DRB_FP8_DEQUANT", "1" if route == "fp16" else "0")
     shape = synth.MoeShape(experts=16)
     host = synth.make_layer(9, shape)
     f8h = synth.make_fp8_experts(9, shape)
@@ -110,6 +113,7 @@ def test_moe_prefill_fp8_grouped_kernel(st):
 
     y = run(l)
     assert device_error_word() == 0
+    assert np.isfinite(y).all()  # max() below would let a NaN row pass
     assert not y[zero_row].any()
     x = synth.bf16_bits_to_f32(xb).astype(np.float64)
     y_ref = run(C.CDLL(REF_LIB)) if os.path.exists(REF_LIB) else None
@@ -126,8 +130,10 @@ def test_moe_prefill_fp8_grouped_kernel(st):
             worst_ref = max(worst_ref, float((np.linalg.norm(y_ref[rows] - ref, axis=1) / nrm).max()))
     # three-term E4M3 token operands (about twelve bits) and an fp16 intermediate here, bf16 intermediate in the reference
     # kernel: a few 1e-4 / 1e-3 per row
-    print(f"dr_moe_prefill_fp8 worst per-row rel-L2 {worst:.3e} (the reference's kernel {worst_ref:.3e})")
-    assert worst <= 8e-4, worst
+    print(f"dr_moe_prefill_fp8 ({route}) worst per-row rel-L2 {worst:.3e} (the reference's kernel {worst_ref:.3e})")
+    # measured: 3.3e-4 (e4m3), 1.1e-3 (fp16: a weight times its scale is rounded to fp16, and under a row's largest scale
+    # the small scales' products are fp16 subnormals), the reference's kernel 2.4e-3
+    assert worst <= (8e-4 if route == "e4m3" else 2e-3), worst
     assert worst_ref <= 6e-3, worst_ref
 
 

@@ -291,6 +291,7 @@ def test_moe_prefill_grouped_kernel_direct(st, layers):
         rows = slice(offsets[e], offsets[e] + counts[e])
         ref = orc.expert_forward(host, e, x[rows], np.float64)
         rel = np.linalg.norm(y[rows] - ref, axis=1) / np.linalg.norm(ref, axis=1)
+        assert np.isfinite(rel).all()  # max() below would let a NaN row pass
         worst = max(worst, float(rel.max()))
     # fp16 weights and fp16 intermediate: a few 1e-4 per row
     assert worst <= 8e-4, worst
