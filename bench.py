@@ -155,9 +155,9 @@ def cpu_decode_baseline(budget_s: float = 15.0) -> dict:
     us = float(np.median(times) / LAYERS * 1e6)
     return {"value": us, "unit": "us/layer", "cores": cores, "kind": "port",
             "sample": f"median of {len(times)} steps of the {LAYERS}-layer stack (2 seeded config-0 layers alternating), plain-C "
-                      f"restatement of the reference's CUDA decode kernels with OpenMP; it stands in for both CPU rows of "
-                      f"BASELINE.md (HF block 2.8 ms/layer, tools/reference.py 65.7 ms/layer on 8 threads): the reference has no "
-                      f"CPU engine and its PyTorch path does not travel to the GPU box",
+                      f"restatement of the reference's CUDA decode kernels with OpenMP; it stands in for the reference's two "
+                      f"PyTorch CPU paths (HF block 2.8 ms/layer, tools/reference.py 65.7 ms/layer on 8 threads): the reference has no "
+                      f"CPU engine, and a checkout of it is not assumed where this runs",
             "min_us_per_layer": float(min(times) / LAYERS * 1e6), "max_us_per_layer": float(max(times) / LAYERS * 1e6)}
 
 
