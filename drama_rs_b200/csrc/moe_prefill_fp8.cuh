@@ -10,7 +10,7 @@
 // The 8-bit MMA kind takes both operands as 8-bit floats, so B' is written as three E4M3 terms (value, residual,
 // residual of the residual: about twelve significant bits, what fp16 operands carry). The three terms of a token are
 // three ROWS of the token operand (rows t, 16 + t, 32 + t of a 48-row tile), so one MMA of N = 48 multiplies all three
-// and the epilogue adds the three column groups: a third of the MMA issues (an issue costs its thread ~150 cycles, and
+// and the epilogue adds the three column groups: a third of the MMA issues (an issue costs its thread about 100 cycles, and
 // one thread per block issues), for 48 accumulator columns instead of 16.
 // A gate/up item holds two accumulators, the 128 gate rows of units [128 mt, +128) and their 128 up rows (two block
 // rows with their own scales, hence two B' tiles per chunk); SiLU(gate) * up is formed in the epilogue by the thread
@@ -70,9 +70,9 @@ static_assert(2 * NACC * NCOL <= TMEM_COLS, "tensor memory");
 static_assert(SMEM <= 113 * 1024, "two blocks per multiprocessor");
 
 struct Ctl {
-  uint64_t afull[4], aempty[4];     // A stage landed (TMA) / its MMAs completed (one commit per MMA warp at work)
+  uint64_t afull[4], aempty[4];     // A stage landed (TMA) / its MMAs completed
   uint64_t bfull[3], bempty[3];     // B' stage written (one arrival per prep warp) / its MMAs completed
-  uint64_t accfull[2], accfree[2];  // an item's accumulators complete (one commit per MMA warp) / drained (per prep warp)
+  uint64_t accfull[2], accfree[2];  // an item's accumulators complete / drained (one arrival per prep warp)
   uint64_t tabfull[NTAB], tabempty[NTAB];
   uint32_t tmem_base;
 };
