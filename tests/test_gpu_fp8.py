@@ -137,6 +137,36 @@ def test_moe_prefill_fp8_grouped_kernel(st, route, monkeypatch):
     assert worst_ref <= 6e-3, worst_ref
 
 
+def test_moe_prefill_fp8_256_experts(st):
+    """The model's own expert count with Zipf-like group sizes (every expert hit, a few of them with several 16-token
+    groups): seven experts' rows against the fp64 expert, every row finite."""
+    l = ffi.lib()
+    shape = synth.MoeShape(experts=256)
+    host = synth.make_fp8_experts(12, shape)
+    f8 = Fp8Experts.upload(host, st)
+    rng = np.random.Generator(np.random.PCG64(80))
+    counts = np.minimum(1 + (300.0 / np.arange(1, 257) ** 1.1).astype(np.int32), 300).astype(np.int32)[rng.permutation(256)]
+    offsets = (np.cumsum(counts) - counts).astype(np.int32)
+    n = int(counts.sum())
+    xb = synth.f32_to_bf16_bits(rng.standard_normal((n, 2048), dtype=np.float32))
+    dxp, dcnt, doff = DevBuf.from_array(xb, st), DevBuf.from_array(counts, st), DevBuf.from_array(offsets, st)
+    dact, dy = DevBuf(n * 512 * 2), DevBuf(n * 2048 * 4)
+    dy.fill(0xFF, st)
+    launched(l.dr_moe_prefill_fp8(f8.gu_w.at(0), f8.gu_s.at(0), f8.d_w.at(0), f8.d_s.at(0), dxp.at(0), doff.at(0), dcnt.at(0),
+                                  dact.at(0), dy.at(0), 256, 2048, 512, st.raw), "moe_prefill_fp8")
+    st.sync()
+    assert device_error_word() == 0
+    y = dy.download(np.float32, n * 2048, st).reshape(n, 2048)
+    assert np.isfinite(y).all()
+    x = synth.bf16_bits_to_f32(xb).astype(np.float64)
+    order = np.argsort(counts)
+    for e in (*order[-3:], *order[:2], 0, 255):  # the three largest groups, two of the smallest, the first and last expert
+        rows = slice(offsets[e], offsets[e] + counts[e])
+        ref = orc.expert_forward(host, int(e), x[rows], np.float64)
+        rel = np.linalg.norm(y[rows] - ref, axis=1) / np.linalg.norm(ref, axis=1)
+        assert np.isfinite(rel).all() and rel.max() <= 8e-4, (int(e), float(rel.max()))
+
+
 def test_moe_prefill_fp8_back_to_back(st):
     """Two hundred calls queued without a synchronisation between them (a block of one launch starts on a multiprocessor
     the moment a block of the launch before has left it): same bits every time, error word clear."""
