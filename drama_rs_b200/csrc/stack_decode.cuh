@@ -670,7 +670,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         // block waited for its rows (a shared block fetches them after it has published its own).
         if (i == 1 && routed_blk) fetch_shared_act(tag);
         wait_full(&ctl.gfull[u / PU], par, poll_limit, abort_flag);
-                if (shared_blk) {
+        if (shared_blk) {
           const uint4* gr = reinterpret_cast<const uint4*>(gst + (size_t)u * H);
           const uint4* ur = reinterpret_cast<const uint4*>(gst + (size_t)(UNITS + u) * H);
           const __half* gs = reinterpret_cast<const __half*>(gst + (size_t)2 * UNITS * H + (size_t)u * SSROW);
