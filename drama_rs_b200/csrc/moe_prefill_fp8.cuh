@@ -560,17 +560,18 @@ __global__ void __launch_bounds__(THREADS, 2)
       const int cnt = __ldg(counts + it.e), off = __ldg(offsets + it.e);
       const int nt = min(NT, cnt - it.n0);
       if (lane < TPI * NKB) tab_s(it_no)[lane] = __ldg(S + ((size_t)it.e * (H / TILE_M) + it.q * TPI) * NKB + lane);
-      // every token row's largest magnitude, four rows per round trip (fp16 with the sign cleared orders like an integer)
-      for (int t0 = 0; t0 < NT; t0 += 4) {
-        uint4 v[4][2];
+      // every token row's largest magnitude, eight rows per round trip (fp16 with the sign cleared orders like an integer)
+      constexpr int TB = 8;
+      for (int t0 = 0; t0 < NT; t0 += TB) {
+        uint4 v[TB][2];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < TB; ++u) {
           const int row = off + it.n0 + (t0 + u < nt ? t0 + u : 0);
           const uint4* p = reinterpret_cast<const uint4*>(src + (size_t)row * I);
           v[u][0] = __ldcg(p + lane), v[u][1] = __ldcg(p + 32 + lane);
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < TB; ++u) {
           const uint32_t wv[8] = {v[u][0].x, v[u][0].y, v[u][0].z, v[u][0].w, v[u][1].x, v[u][1].y, v[u][1].z, v[u][1].w};
           uint32_t m = 0u;
 #pragma unroll
